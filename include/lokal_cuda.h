@@ -1,0 +1,236 @@
+/*
+ * lokal_cuda.h -- C ABI of the B200 (sm_100a) implementation of lokal's fused
+ * per-token layer ops: residual-add + RMSNorm (incl. per-head qk-norm), RoPE of
+ * q/k with the bias fold, SiLU(gate)*up, and embedding gather with GGUF
+ * Q8_0 / Q4_K row dequantisation.
+ *
+ * This is the boundary a `-b cuda` backend of the reference binds through FFI:
+ * plain pointers and sizes, no C++ or framework types. Each entry point names
+ * the reference interface it stands in for (paths are within the reference
+ * project).
+ *
+ * Conventions
+ *   - Every function returns a lokal_status (0 = ok). On failure the context
+ *     keeps a message readable with lokal_cuda_last_error().
+ *   - Ops take DEVICE pointers and are asynchronous on the given stream (NULL =
+ *     the legacy default stream), the way the reference encodes a whole step
+ *     and waits once (src/gpu/metal.rs:2679-2681). lokal_cuda_stream_sync is
+ *     the blocking call. The lokal_cuda_host_* functions take HOST slices,
+ *     mirror the CPU signatures in src/math.rs / src/model.rs / src/gguf, and
+ *     block until the result is in the caller's buffer.
+ *   - Unsupported cases are refused by name with an error code; there is no
+ *     CPU fallback anywhere in this library.
+ *   - Element types use the on-disk GGUF ids (src/gguf/dequant.rs:21-41), for
+ *     activations as well as for tables.
+ *   - eps and theta are f32, as in the reference config (src/config.rs:19-21).
+ *   - Head geometry is always passed explicitly (n_heads, head_dim, rot_dim),
+ *     never derived from the hidden size (src/lowmem/mod.rs:62-101).
+ */
+#ifndef LOKAL_CUDA_H
+#define LOKAL_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LOKAL_API __attribute__((visibility("default")))
+#else
+#define LOKAL_API
+#endif
+
+typedef enum lokal_status {
+    LOKAL_OK = 0,
+    LOKAL_ERR_BAD_ARG = 1,     /* null pointer, zero/odd dimension, inconsistent sizes */
+    LOKAL_ERR_UNSUPPORTED = 2, /* element type or combination this path does not cover */
+    LOKAL_ERR_MISALIGNED = 3,  /* pointer not aligned to its element size */
+    LOKAL_ERR_CUDA = 4,        /* a CUDA runtime call failed; message has the detail */
+    LOKAL_ERR_ID_RANGE = 5,    /* a token id was >= vocab (row zero-filled on the device) */
+    LOKAL_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up */
+    LOKAL_ERR_NO_DEVICE = 7    /* no usable CUDA device */
+} lokal_status;
+
+/* GGUF tensor type ids (src/gguf/dequant.rs:21-41; BF16 = 30 per ggml.h). */
+typedef enum lokal_type {
+    LOKAL_F32 = 0,
+    LOKAL_F16 = 1,
+    LOKAL_Q8_0 = 8,
+    LOKAL_Q4_K = 12,
+    LOKAL_BF16 = 30
+} lokal_type;
+
+typedef struct lokal_cuda_ctx lokal_cuda_ctx; /* one per device; thread-safe after creation */
+typedef void* lokal_cuda_stream;              /* a cudaStream_t */
+typedef struct lokal_cuda_graph lokal_cuda_graph;
+
+/* ---- context, memory, streams --------------------------------------------
+ * Stand in for engine creation on the backend seam (src/engine.rs:76-111,
+ * checklist src/gpu/mod.rs:3-13): weights resident, one submission per step. */
+LOKAL_API int lokal_cuda_create(int device, lokal_cuda_ctx** out);
+LOKAL_API void lokal_cuda_destroy(lokal_cuda_ctx* ctx);
+LOKAL_API const char* lokal_cuda_last_error(const lokal_cuda_ctx* ctx);
+LOKAL_API const char* lokal_cuda_version(void);
+LOKAL_API int lokal_cuda_device_count(void);
+
+LOKAL_API int lokal_cuda_malloc(lokal_cuda_ctx* ctx, size_t bytes, void** dptr);
+LOKAL_API int lokal_cuda_free(lokal_cuda_ctx* ctx, void* dptr);
+LOKAL_API int lokal_cuda_host_alloc(lokal_cuda_ctx* ctx, size_t bytes, void** hptr); /* pinned */
+LOKAL_API int lokal_cuda_host_free(lokal_cuda_ctx* ctx, void* hptr);
+LOKAL_API int lokal_cuda_memcpy_h2d(lokal_cuda_ctx* ctx, lokal_cuda_stream s, void* dst, const void* src, size_t bytes);
+LOKAL_API int lokal_cuda_memcpy_d2h(lokal_cuda_ctx* ctx, lokal_cuda_stream s, void* dst, const void* src, size_t bytes);
+LOKAL_API int lokal_cuda_stream_create(lokal_cuda_ctx* ctx, lokal_cuda_stream* out);
+LOKAL_API int lokal_cuda_stream_destroy(lokal_cuda_ctx* ctx, lokal_cuda_stream s);
+/* Blocks until the stream drains, then reports (and clears) any device-side
+ * error word: LOKAL_ERR_ID_RANGE / LOKAL_ERR_TIMEOUT (cf. the command-buffer
+ * status check of src/lowmem/pool.rs:1291-1320). */
+LOKAL_API int lokal_cuda_stream_sync(lokal_cuda_ctx* ctx, lokal_cuda_stream s);
+
+/* Capture every op issued on `s` between begin and end into one replayable
+ * submission ("encode everything, submit once", src/gpu/metal.rs:2517, 2679). */
+LOKAL_API int lokal_cuda_graph_begin(lokal_cuda_ctx* ctx, lokal_cuda_stream s);
+LOKAL_API int lokal_cuda_graph_end(lokal_cuda_ctx* ctx, lokal_cuda_stream s, lokal_cuda_graph** out);
+LOKAL_API int lokal_cuda_graph_launch(lokal_cuda_ctx* ctx, lokal_cuda_graph* g, lokal_cuda_stream s);
+LOKAL_API int lokal_cuda_graph_destroy(lokal_cuda_ctx* ctx, lokal_cuda_graph* g);
+
+/* ---- GGUF block geometry: GgmlType::{blk_elems, blk_bytes, row_bytes}
+ * (src/gguf/dequant.rs:81-119). Return 0 for a type outside this path. */
+LOKAL_API size_t lokal_cuda_blk_elems(int ggml_type);
+LOKAL_API size_t lokal_cuda_blk_bytes(int ggml_type);
+LOKAL_API size_t lokal_cuda_row_bytes(int ggml_type, size_t n);
+
+/* ---- RMSNorm --------------------------------------------------------------
+ * math::rmsnorm (src/math.rs:45-49) over `rows` rows of `dim`; GPU twins
+ * rmsnorm / rmsnorm_hf (src/gpu/kernels.metal:2262, 2341), host encoders
+ * enc_rmsnorm / enc_rmsnorm_dim / enc_rmsnorm_hf (src/gpu/metal.rs:1181-1256),
+ * NormParams{dim, eps} (src/gpu/metal.rs:90-93).
+ *   y[r][i] = (x[r][i] * scale_r) * w[i],  scale_r = 1 / sqrt(mean(x_r^2) + eps)
+ * x, y: `dtype` (F32 / F16 / BF16; math in f32, one rounding on store). y may
+ * alias x. w: `w_dtype`, `dim` entries. y_h: optional second copy of y in
+ * `h_dtype` (F16 or BF16), only with dtype F32; NULL to skip. */
+LOKAL_API int lokal_cuda_rmsnorm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* x, const void* w, void* y,
+                                 void* y_h, size_t rows, size_t dim, float eps, int dtype, int w_dtype, int h_dtype);
+
+/* Residual add (src/model.rs:235-237, 253-255; GPU twin add_inplace,
+ * src/gpu/kernels.metal:3591) fused with the RMSNorm that follows it:
+ *   x[r] += delta[r]   (in place, f32 add, stored in `dtype`)
+ *   xn[r] = rmsnorm(x[r] + delta[r], w, eps)   (from the unrounded f32 sum) */
+LOKAL_API int lokal_cuda_add_rmsnorm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, void* x_inout, const void* delta,
+                                     const void* w, void* xn, void* xn_h, size_t rows, size_t dim, float eps,
+                                     int dtype, int w_dtype, int h_dtype);
+
+/* ---- RoPE -----------------------------------------------------------------
+ * model::rope (src/model.rs:268-279): pair (i, i + rot/2) of every head turned
+ * by angle pos * theta^(-(2 i)/rot). GPU twins rope / rope_h / rope_qk_prefill /
+ * rope_qk_decode / rope_qk_batch (src/gpu/kernels.metal:2401-2555, 3380);
+ * parameter blocks RopeParams, RopeQkParams, RopeQkPrefillParams,
+ * RopeQkBatchParams, RowMeta (src/gpu/metal.rs:59-131).
+ *
+ * The (cos, sin) of a row's angles are the same for every head and every
+ * layer of a step, so they are built once into a table:
+ *   cos_sin[r][0 .. rot/2) = cos(pos_r * f_i),  cos_sin[r][rot/2 .. rot) = sin(pos_r * f_i)
+ * f_i = powf(theta, -(2 i)/rot) is evaluated on the HOST by this call with
+ * the C library's powf (the function the reference's CPU path reaches through
+ * Rust std), so the angle is one f32 multiply on both sides.
+ * positions: device int32[rows] (batched decode, BatchRow.pos of
+ * src/engine.rs:30-34) or NULL for pos0 + r (prefill). cos_sin: device f32,
+ * rows * rot_dim entries, 16-byte aligned. rot_dim even, <= 1024. */
+LOKAL_API int lokal_cuda_rope_table(lokal_cuda_ctx* ctx, lokal_cuda_stream s, float theta, uint32_t rot_dim,
+                                    const int32_t* positions, int64_t pos0, size_t rows, float* cos_sin);
+
+/* One launch for q and k of `rows` token rows. Per head, in the reference's
+ * order (src/model.rs:208-226): v = raw (+ bias, Linear::forward
+ * src/model.rs:27-35; GPU twins bias_add src/gpu/kernels.metal:2131 and the
+ * matmul_tb store epilogue :2106-2114) -> per-head rmsnorm with a weight of
+ * head_dim entries shared by all heads (src/model.rs:213-221) when a norm
+ * weight is given -> rotate the first rot_dim dims; dims rot_dim..head_dim
+ * pass through (bit-identical when there is no bias and no norm). */
+typedef struct lokal_qk_rope_params {
+    void* q;               /* [rows][n_q_heads*head_dim] at q_row_stride; NULL = skip q */
+    void* k;               /* [rows][n_kv_heads*head_dim] at k_row_stride; NULL = skip k */
+    void* q_out;           /* NULL = in place */
+    void* k_out;           /* NULL = in place; rows addressed through k_out_rows if given */
+    const void* q_bias;    /* [n_q_heads*head_dim] in w_dtype, or NULL */
+    const void* k_bias;    /* [n_kv_heads*head_dim] in w_dtype, or NULL */
+    const void* q_norm_w;  /* [head_dim] in w_dtype, or NULL */
+    const void* k_norm_w;  /* [head_dim] in w_dtype, or NULL */
+    const float* cos_sin;  /* table from lokal_cuda_rope_table, row r for token row r */
+    const uint32_t* k_out_rows; /* optional device array: output row index of token row r in k_out
+                                   (a KV-cache row, (slot*max_seq+pos) in src/gpu/kernels.metal:3411) */
+    uint64_t rows;
+    uint32_t n_q_heads, n_kv_heads, head_dim, rot_dim;
+    uint64_t q_row_stride, k_row_stride, q_out_row_stride, k_out_row_stride; /* in elements */
+    float eps;             /* rms_norm_eps of the layer, used by the per-head norm */
+    int32_t q_dtype, k_dtype, w_dtype; /* lokal_type; q F32 with k F16 is the reference GPU layout */
+} lokal_qk_rope_params;
+
+LOKAL_API int lokal_cuda_qk_rope(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_qk_rope_params* p);
+
+/* Same op with the reference's own argument list (pos0 or per-row positions
+ * plus theta): the table is built into scratch memory owned by the context
+ * (grown on demand with cudaMalloc) and consumed by the same launch sequence.
+ * Calls on one context that overlap on the device share that scratch. */
+LOKAL_API int lokal_cuda_qk_rope_pos(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_qk_rope_params* p,
+                                     float theta, const int32_t* positions, int64_t pos0);
+
+/* ---- SwiGLU ---------------------------------------------------------------
+ * inner_i = (g_i / (1 + exp(-g_i))) * u_i (src/math.rs:68-70, src/model.rs:245-248;
+ * GPU twins silu_mul / silu_mul_hf src/gpu/kernels.metal:3533, 3548; host
+ * enc_elementwise src/gpu/metal.rs:1527; ElemParams{dim} :150-152).
+ * out may alias gate (the reference writes in place). out_h: optional second
+ * copy in h_dtype (F16/BF16), only with dtype F32. n = total elements. */
+LOKAL_API int lokal_cuda_swiglu(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* gate, const void* up, void* out,
+                                void* out_h, size_t n, int dtype, int h_dtype);
+
+/* ---- Embedding gather + row dequant -----------------------------------------
+ * LowMemSession::embed_gather (src/lowmem/forward.rs:275-307), the quant
+ * prefill's Source::Ids arm (src/gpu/metal.rs:3160-3184), the dense lookup
+ * (src/model.rs:200-202) and the GPU twin `embed` (src/gpu/kernels.metal:30);
+ * row addressing and range check of LowMemSource::read_rows
+ * (src/lowmem/mod.rs:654-668); decode = gguf::dequant_row_ref Q8_0 / Q4_K /
+ * F16 / F32 arms (src/gguf/dequant.rs:191-239, 462-483), bit for bit.
+ *   out[i][0..dim) = dequant(table row ids[i])
+ * table: device bytes, vocab rows of row_bytes(type, dim), 16-byte aligned.
+ * ids: device u32[n]. out: `out_dtype` F32, or F16 / BF16 (the exact f32 value
+ * rounded once, nearest-even). An id >= vocab zero-fills its row and raises
+ * LOKAL_ERR_ID_RANGE at the next lokal_cuda_stream_sync. dim must be a whole
+ * number of blocks (src/gguf/container.rs:220-226). */
+LOKAL_API int lokal_cuda_embed_gather(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* table, int ggml_type,
+                                      size_t vocab, size_t dim, const uint32_t* ids, size_t n, void* out,
+                                      int out_dtype);
+
+/* Dequantise `rows` consecutive rows: the bit-for-bit gate kernel
+ * lm_dequant_oracle (src/gpu/kernels.metal:1417-1428, LmDeqParams :1411). */
+LOKAL_API int lokal_cuda_dequant_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, int ggml_type, const void* src,
+                                      size_t rows, size_t cols, void* out, int out_dtype);
+
+/* ---- Token-row sharding over GPUs ---------------------------------------------
+ * Rows are independent, so GPU `rank` of `n_gpus` owns the contiguous block
+ * [row0, row0+count); no exchange happens on the path. The reference has no
+ * multi-device code; this has no counterpart there. */
+LOKAL_API int lokal_cuda_shard_rows(size_t n_rows, int n_gpus, int rank, size_t* row0, size_t* count);
+
+/* ---- Host-slice mirrors of the reference's CPU signatures ---------------------
+ * Inputs and outputs are HOST memory; each call stages through buffers owned
+ * by the context, runs the device op and waits for the result. */
+/* math::rmsnorm(x, weight, eps) -> y (src/math.rs:45), f32, rows x dim. */
+LOKAL_API int lokal_cuda_host_rmsnorm(lokal_cuda_ctx* ctx, const float* x, const float* w, float eps, size_t rows,
+                                      size_t dim, float* y);
+/* model::rope(x, pos, head_dim, theta) in place on one row of whole heads (src/model.rs:268). */
+LOKAL_API int lokal_cuda_host_rope(lokal_cuda_ctx* ctx, float* x, size_t n, size_t pos, size_t head_dim, float theta);
+/* the SwiGLU line silu(g) * u (src/model.rs:247-248). */
+LOKAL_API int lokal_cuda_host_swiglu(lokal_cuda_ctx* ctx, const float* gate, const float* up, size_t n, float* out);
+/* gguf::dequant_row_ref(ty, src, out) (src/gguf/dequant.rs:191); a size
+ * mismatch, where the reference panics, returns LOKAL_ERR_BAD_ARG. */
+LOKAL_API int lokal_cuda_host_dequant_row(lokal_cuda_ctx* ctx, int ggml_type, const uint8_t* src, size_t src_len,
+                                          float* out, size_t n);
+/* embed_gather with a DEVICE-resident table and host ids / host f32 output. */
+LOKAL_API int lokal_cuda_host_embed_gather(lokal_cuda_ctx* ctx, const void* table_dev, int ggml_type, size_t vocab,
+                                           size_t dim, const uint32_t* ids, size_t n, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOKAL_CUDA_H */

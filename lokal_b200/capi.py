@@ -1,0 +1,111 @@
+"""ctypes binding of liblokal_cuda.so -- the same C ABI a Rust `-b cuda` backend binds.
+
+The library is the product; this module only declares its symbols. There is no
+CPU fallback: if the shared library is missing or a CUDA device cannot be
+opened, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import _build
+
+# lokal_type (GGUF tensor type ids)
+F32, F16, Q8_0, Q4_K, BF16 = 0, 1, 8, 12, 30
+
+# lokal_status
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_CUDA, ERR_ID_RANGE, ERR_TIMEOUT, ERR_NO_DEVICE = range(8)
+STATUS_NAMES = {
+    OK: "LOKAL_OK", ERR_BAD_ARG: "LOKAL_ERR_BAD_ARG", ERR_UNSUPPORTED: "LOKAL_ERR_UNSUPPORTED",
+    ERR_MISALIGNED: "LOKAL_ERR_MISALIGNED", ERR_CUDA: "LOKAL_ERR_CUDA", ERR_ID_RANGE: "LOKAL_ERR_ID_RANGE",
+    ERR_TIMEOUT: "LOKAL_ERR_TIMEOUT", ERR_NO_DEVICE: "LOKAL_ERR_NO_DEVICE",
+}
+
+
+class QkRopeParams(C.Structure):
+    """Mirror of lokal_qk_rope_params (include/lokal_cuda.h), field for field."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("q_out", C.c_void_p), ("k_out", C.c_void_p),
+        ("q_bias", C.c_void_p), ("k_bias", C.c_void_p), ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p),
+        ("cos_sin", C.c_void_p), ("k_out_rows", C.c_void_p),
+        ("rows", C.c_uint64),
+        ("n_q_heads", C.c_uint32), ("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("rot_dim", C.c_uint32),
+        ("q_row_stride", C.c_uint64), ("k_row_stride", C.c_uint64),
+        ("q_out_row_stride", C.c_uint64), ("k_out_row_stride", C.c_uint64),
+        ("eps", C.c_float),
+        ("q_dtype", C.c_int32), ("k_dtype", C.c_int32), ("w_dtype", C.c_int32),
+    ]
+
+
+_vp, _sz, _f, _i, _u32, _i64 = C.c_void_p, C.c_size_t, C.c_float, C.c_int, C.c_uint32, C.c_int64
+_pp = C.POINTER(C.c_void_p)
+
+# name -> (restype, argtypes); every symbol include/lokal_cuda.h declares.
+SIGNATURES = {
+    "lokal_cuda_create": (_i, [_i, _pp]),
+    "lokal_cuda_destroy": (None, [_vp]),
+    "lokal_cuda_last_error": (C.c_char_p, [_vp]),
+    "lokal_cuda_version": (C.c_char_p, []),
+    "lokal_cuda_device_count": (_i, []),
+    "lokal_cuda_malloc": (_i, [_vp, _sz, _pp]),
+    "lokal_cuda_free": (_i, [_vp, _vp]),
+    "lokal_cuda_host_alloc": (_i, [_vp, _sz, _pp]),
+    "lokal_cuda_host_free": (_i, [_vp, _vp]),
+    "lokal_cuda_memcpy_h2d": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "lokal_cuda_memcpy_d2h": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "lokal_cuda_stream_create": (_i, [_vp, _pp]),
+    "lokal_cuda_stream_destroy": (_i, [_vp, _vp]),
+    "lokal_cuda_stream_sync": (_i, [_vp, _vp]),
+    "lokal_cuda_graph_begin": (_i, [_vp, _vp]),
+    "lokal_cuda_graph_end": (_i, [_vp, _vp, _pp]),
+    "lokal_cuda_graph_launch": (_i, [_vp, _vp, _vp]),
+    "lokal_cuda_graph_destroy": (_i, [_vp, _vp]),
+    "lokal_cuda_blk_elems": (_sz, [_i]),
+    "lokal_cuda_blk_bytes": (_sz, [_i]),
+    "lokal_cuda_row_bytes": (_sz, [_i, _sz]),
+    "lokal_cuda_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _i, _i]),
+    "lokal_cuda_add_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _i, _i]),
+    "lokal_cuda_rope_table": (_i, [_vp, _vp, _f, _u32, _vp, _i64, _sz, _vp]),
+    "lokal_cuda_qk_rope": (_i, [_vp, _vp, C.POINTER(QkRopeParams)]),
+    "lokal_cuda_qk_rope_pos": (_i, [_vp, _vp, C.POINTER(QkRopeParams), _f, _vp, _i64]),
+    "lokal_cuda_swiglu": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i]),
+    "lokal_cuda_embed_gather": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _vp, _sz, _vp, _i]),
+    "lokal_cuda_dequant_rows": (_i, [_vp, _vp, _i, _vp, _sz, _sz, _vp, _i]),
+    "lokal_cuda_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
+    "lokal_cuda_host_rmsnorm": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp]),
+    "lokal_cuda_host_rope": (_i, [_vp, _vp, _sz, _sz, _sz, _f]),
+    "lokal_cuda_host_swiglu": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "lokal_cuda_host_dequant_row": (_i, [_vp, _i, _vp, _sz, _vp, _sz]),
+    "lokal_cuda_host_embed_gather": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _sz, _vp]),
+}
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.SO
+
+
+def load() -> C.CDLL:
+    """dlopen liblokal_cuda.so (building it first if the sources are newer) and type every symbol."""
+    global _lib
+    if _lib is None:
+        if _build.needs_build():
+            _build.build()
+        if not os.path.exists(_build.SO):
+            raise RuntimeError("liblokal_cuda.so is missing and could not be built; there is no CPU fallback")
+        lib = C.CDLL(_build.SO)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the header and the library disagree
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+class LokalCudaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+        self.message = message

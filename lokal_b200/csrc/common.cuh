@@ -1,0 +1,273 @@
+// Shared device helpers and the context object of liblokal_cuda.
+//
+// All kernels here are HBM-bound streaming kernels for sm_100a: 128-bit
+// coalesced accesses, rows kept in registers between the reduction and the
+// scaled store (one pass over HBM), streaming cache hints on data touched
+// once. f32 arithmetic follows the reference's expression shapes; the library
+// is compiled with -fmad=false so multiplies and adds are rounded separately,
+// as in the reference's Rust code, and sqrt/div are the IEEE versions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "../../include/lokal_cuda.h"
+
+namespace lokal {
+
+constexpr int kSmCountB200 = 148;
+
+// Device-side error word bits (read back by lokal_cuda_stream_sync).
+enum : unsigned { kErrIdRange = 1u, kErrTimeout = 2u };
+
+}  // namespace lokal
+
+struct lokal_cuda_ctx {
+    int device = 0;
+    int sm_count = lokal::kSmCountB200;
+    unsigned* err_word = nullptr;      // device, 4 bytes
+    unsigned* err_word_host = nullptr; // pinned, 4 bytes
+    // scratch for calls that build their own cos/sin table or stage host slices
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    void* staging = nullptr;  // pinned host
+    size_t staging_bytes = 0;
+    cudaStream_t host_stream = nullptr;
+    std::mutex mu;  // guards scratch growth and the host-slice calls
+    mutable std::mutex err_mu;
+    std::string last_error;
+
+    int fail(int code, const char* fmt, ...) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        std::lock_guard<std::mutex> g(err_mu);
+        last_error = buf;
+        return code;
+    }
+};
+
+struct lokal_cuda_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+#define LOKAL_CUDA_TRY(ctx, expr)                                                                  \
+    do {                                                                                           \
+        cudaError_t e__ = (expr);                                                                  \
+        if (e__ != cudaSuccess)                                                                    \
+            return (ctx)->fail(LOKAL_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));   \
+    } while (0)
+
+#define LOKAL_CHECK_LAUNCH(ctx, what)                                                              \
+    do {                                                                                           \
+        cudaError_t e__ = cudaGetLastError();                                                      \
+        if (e__ != cudaSuccess)                                                                    \
+            return (ctx)->fail(LOKAL_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e__)); \
+    } while (0)
+
+namespace lokal {
+
+// RAII device selection for every entry point.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+inline bool is_act_type(int t) { return t == LOKAL_F32 || t == LOKAL_F16 || t == LOKAL_BF16; }
+inline size_t type_size(int t) { return t == LOKAL_F32 ? 4 : 2; }
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---------------------------------------------------------------------------
+// 16-byte vector access
+// ---------------------------------------------------------------------------
+
+template <typename T>
+struct VecOf;  // elements per 16-byte vector
+template <>
+struct VecOf<float> {
+    static constexpr int N = 4;
+};
+template <>
+struct VecOf<__half> {
+    static constexpr int N = 8;
+};
+template <>
+struct VecOf<__nv_bfloat16> {
+    static constexpr int N = 8;
+};
+
+// Streaming (touched-once) loads/stores: evict-first so the per-layer activation
+// streams do not push the small replicated weights and tables out of L2.
+__device__ __forceinline__ uint4 ld_stream(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void st_stream(void* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+__device__ __forceinline__ uint4 ld_keep(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& v, float (&f)[VecOf<T>::N]);
+
+template <>
+__device__ __forceinline__ void unpack16<float>(const uint4& v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+}
+template <>
+__device__ __forceinline__ void unpack16<__half>(const uint4& v, float (&f)[8]) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        float2 t = __half22float2(h);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+template <>
+__device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& v, float (&f)[8]) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack16(const float (&f)[VecOf<T>::N]);
+
+template <>
+__device__ __forceinline__ uint4 pack16<float>(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+template <>
+__device__ __forceinline__ uint4 pack16<__half>(const float (&f)[8]) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *reinterpret_cast<unsigned*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ uint4 pack16<__nv_bfloat16>(const float (&f)[8]) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *reinterpret_cast<unsigned*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Scalar element access by runtime type (weights, biases: small, cache-resident).
+__device__ __forceinline__ float load_as_f32(const void* p, int type, size_t i) {
+    if (type == LOKAL_F32) return __ldg(reinterpret_cast<const float*>(p) + i);
+    unsigned short b = __ldg(reinterpret_cast<const unsigned short*>(p) + i);
+    if (type == LOKAL_F16) return __half2float(__ushort_as_half(b));
+    return __uint_as_float(static_cast<unsigned>(b) << 16);
+}
+
+// N consecutive elements starting at element index i (i % N == 0 and the base
+// 16-byte aligned when vec_ok; otherwise scalar loads).
+template <int N>
+__device__ __forceinline__ void load_w(const void* p, int type, size_t i, bool vec_ok, float (&f)[N]) {
+    if (vec_ok) {
+        if (type == LOKAL_F32) {
+#pragma unroll
+            for (int j = 0; j < N / 4; j++) {
+                float t[4];
+                unpack16<float>(ld_keep(reinterpret_cast<const float*>(p) + i + 4 * j), t);
+#pragma unroll
+                for (int k = 0; k < 4; k++) f[4 * j + k] = t[k];
+            }
+        } else if constexpr (N >= 8) {
+#pragma unroll
+            for (int j = 0; j < N / 8; j++) {
+                float t[8];
+                uint4 v = ld_keep(reinterpret_cast<const unsigned short*>(p) + i + 8 * j);
+                if (type == LOKAL_F16) unpack16<__half>(v, t);
+                else unpack16<__nv_bfloat16>(v, t);
+#pragma unroll
+                for (int k = 0; k < 8; k++) f[8 * j + k] = t[k];
+            }
+        } else {  // N == 4 halves: one 8-byte load
+            uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(p) + i));
+            const unsigned w[2] = {v.x, v.y};
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                if (type == LOKAL_F16) {
+                    float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+                    f[2 * k] = t.x;
+                    f[2 * k + 1] = t.y;
+                } else {
+                    f[2 * k] = __uint_as_float(w[k] << 16);
+                    f[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < N; j++) f[j] = load_as_f32(p, type, i + j);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+inline unsigned ceil_div(size_t a, size_t b) { return static_cast<unsigned>((a + b - 1) / b); }
+
+}  // namespace lokal
+
+// Launchers implemented in the per-op translation units.
+namespace lokal {
+int launch_norm(lokal_cuda_ctx* ctx, cudaStream_t s, void* x, const void* delta, const void* w, void* xn, void* xn_h,
+                size_t rows, size_t dim, float eps, int dtype, int w_dtype, int h_dtype);
+int launch_rope_table(lokal_cuda_ctx* ctx, cudaStream_t s, float theta, uint32_t rot_dim, const int32_t* positions,
+                      int64_t pos0, size_t rows, float* cos_sin);
+int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_params& p);
+int launch_swiglu(lokal_cuda_ctx* ctx, cudaStream_t s, const void* gate, const void* up, void* out, void* out_h,
+                  size_t n, int dtype, int h_dtype);
+int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int ggml_type, size_t vocab, size_t dim,
+                  const uint32_t* ids, size_t n, void* out, int out_dtype);
+}  // namespace lokal

@@ -1,0 +1,259 @@
+// RMSNorm and fused residual-add + RMSNorm over token rows.
+//
+// Semantics follow math::rmsnorm (src/math.rs:45-49 of the reference):
+//   mean_sq = sum(x_i^2) / n;  scale = 1 / sqrt(mean_sq + eps);  y_i = (x_i * scale) * w_i
+// preceded, when a delta is given, by the residual add x_i += delta_i
+// (src/model.rs:235-237, 253-255). The sum of squares is reduced in parallel
+// (lane partials, warp shuffle, then shared memory across warps), so it differs
+// from the reference's 8-lane order in the last bits of the scale only.
+//
+// Kernel shape: one warp per row (rows kept in registers, no barrier) while
+// there are enough rows to fill the machine, otherwise one CTA per row. Each
+// thread owns up to VPT 16-byte vectors of the row; x and delta are read once,
+// x' and xn written once: 4*dim*sizeof(T) bytes of HBM traffic per row.
+#include "common.cuh"
+
+namespace lokal {
+namespace {
+
+struct NormArgs {
+    const void* x;
+    const void* delta;  // may be null
+    const void* w;
+    void* x_out;  // where x + delta goes (null when no delta)
+    void* xn;
+    void* xn_h;  // may be null
+    size_t rows;
+    unsigned dim;
+    unsigned nvec;
+    float eps;
+    int w_dtype;
+    int h_dtype;
+    int w_vec_ok;
+};
+
+template <typename T, int N>
+__device__ __forceinline__ void store_h_copy(void* base, int h_dtype, size_t elem, const float (&y)[N]) {
+    // second copy of the row in f16 / bf16 (only used with f32 rows: N == 4 -> 8 bytes)
+    unsigned w[N / 2];
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) {
+        if (h_dtype == LOKAL_F16) {
+            __half2 h = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
+            w[i] = *reinterpret_cast<unsigned*>(&h);
+        } else {
+            __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+            w[i] = *reinterpret_cast<unsigned*>(&h);
+        }
+    }
+    unsigned short* p = reinterpret_cast<unsigned short*>(base) + elem;
+    if (N == 4) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+    else {
+#pragma unroll
+        for (int i = 0; i < N / 2; i++) reinterpret_cast<unsigned*>(p)[i] = w[i];
+    }
+}
+
+template <typename T, int VPT, bool CTA_MODE>
+__global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const NormArgs a) {
+    constexpr int N = VecOf<T>::N;
+    const unsigned tpr = CTA_MODE ? blockDim.x : 32u;
+    const unsigned t = CTA_MODE ? threadIdx.x : (threadIdx.x & 31u);
+    const size_t row = CTA_MODE ? static_cast<size_t>(blockIdx.x)
+                                : static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (!CTA_MODE && row >= a.rows) return;  // whole warps leave together
+
+    const T* xr = reinterpret_cast<const T*>(a.x) + row * a.dim;
+    const T* dr = a.delta ? reinterpret_cast<const T*>(a.delta) + row * a.dim : nullptr;
+
+    // All loads of the row are issued before any is consumed.
+    uint4 xv[VPT], dv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const unsigned idx = t + j * tpr;
+        if (idx < a.nvec) {
+            xv[j] = ld_stream(xr + static_cast<size_t>(idx) * N);
+            if (dr) dv[j] = ld_stream(dr + static_cast<size_t>(idx) * N);
+        }
+    }
+
+    float v[VPT][N];
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const unsigned idx = t + j * tpr;
+        if (idx < a.nvec) {
+            unpack16<T>(xv[j], v[j]);
+            if (dr) {
+                float d[N];
+                unpack16<T>(dv[j], d);
+#pragma unroll
+                for (int e = 0; e < N; e++) v[j][e] = v[j][e] + d[e];
+                T* xo = reinterpret_cast<T*>(a.x_out) + row * a.dim;
+                *reinterpret_cast<uint4*>(xo + static_cast<size_t>(idx) * N) = pack16<T>(v[j]);
+            }
+#pragma unroll
+            for (int e = 0; e < N; e++) acc += v[j][e] * v[j][e];
+        }
+    }
+
+    acc = warp_sum(acc);
+    if (CTA_MODE) {
+        __shared__ float partial[32];
+        const unsigned warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+        if ((threadIdx.x & 31u) == 0) partial[warp] = acc;
+        __syncthreads();
+        float total = 0.0f;
+        for (unsigned wv = 0; wv < nwarps; wv++) total += partial[wv];
+        acc = total;
+    }
+    const float mean_sq = acc / static_cast<float>(a.dim);
+    const float scale = 1.0f / sqrtf(mean_sq + a.eps);
+
+    T* yr = reinterpret_cast<T*>(a.xn) + row * a.dim;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const unsigned idx = t + j * tpr;
+        if (idx < a.nvec) {
+            float wv[N];
+            load_w<N>(a.w, a.w_dtype, static_cast<size_t>(idx) * N, a.w_vec_ok, wv);
+            float y[N];
+#pragma unroll
+            for (int e = 0; e < N; e++) y[e] = (v[j][e] * scale) * wv[e];
+            *reinterpret_cast<uint4*>(yr + static_cast<size_t>(idx) * N) = pack16<T>(y);
+            if (a.xn_h) store_h_copy<T, N>(a.xn_h, a.h_dtype, row * a.dim + static_cast<size_t>(idx) * N, y);
+        }
+    }
+}
+
+// Any dim, any alignment: one CTA per row, scalar accesses, the row is read
+// twice (the second read hits L1/L2).
+template <typename T>
+__global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a) {
+    const size_t row = blockIdx.x;
+    const T* xr = reinterpret_cast<const T*>(a.x) + row * a.dim;
+    const T* dr = a.delta ? reinterpret_cast<const T*>(a.delta) + row * a.dim : nullptr;
+    float acc = 0.0f;
+    for (unsigned i = threadIdx.x; i < a.dim; i += blockDim.x) {
+        float v = to_f32<T>(xr[i]);
+        if (dr) v = v + to_f32<T>(dr[i]);
+        acc += v * v;
+    }
+    acc = warp_sum(acc);
+    __shared__ float partial[32];
+    const unsigned warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    if ((threadIdx.x & 31u) == 0) partial[warp] = acc;
+    __syncthreads();
+    float total = 0.0f;
+    for (unsigned wv = 0; wv < nwarps; wv++) total += partial[wv];
+    const float mean_sq = total / static_cast<float>(a.dim);
+    const float scale = 1.0f / sqrtf(mean_sq + a.eps);
+    T* yr = reinterpret_cast<T*>(a.xn) + row * a.dim;
+    T* xo = dr ? reinterpret_cast<T*>(a.x_out) + row * a.dim : nullptr;
+    for (unsigned i = threadIdx.x; i < a.dim; i += blockDim.x) {
+        float v = to_f32<T>(xr[i]);
+        if (dr) {
+            v = v + to_f32<T>(dr[i]);
+            xo[i] = from_f32<T>(v);
+        }
+        const float y = (v * scale) * load_as_f32(a.w, a.w_dtype, i);
+        yr[i] = from_f32<T>(y);
+        if (a.xn_h) {
+            unsigned short* hp = reinterpret_cast<unsigned short*>(a.xn_h) + row * a.dim + i;
+            *hp = a.h_dtype == LOKAL_F16 ? __half_as_ushort(__float2half_rn(y))
+                                         : __bfloat16_as_ushort(__float2bfloat16_rn(y));
+        }
+    }
+}
+
+template <typename T, bool CTA_MODE>
+cudaError_t launch_vec(const NormArgs& a, unsigned tpr, unsigned vpt, cudaStream_t s) {
+    dim3 grid, block;
+    if (CTA_MODE) {
+        grid = dim3(static_cast<unsigned>(a.rows));
+        block = dim3(tpr);
+    } else {
+        block = dim3(256);
+        grid = dim3(ceil_div(a.rows, 8));
+    }
+    switch (vpt) {
+        case 1: norm_rows_kernel<T, 1, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+        case 2: norm_rows_kernel<T, 2, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+        case 3: norm_rows_kernel<T, 3, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+        case 4: norm_rows_kernel<T, 4, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+        case 5: norm_rows_kernel<T, 5, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+        case 6: norm_rows_kernel<T, 6, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+        default: norm_rows_kernel<T, 8, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+    }
+    return cudaGetLastError();
+}
+
+template <typename T>
+int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, NormArgs a, bool ptrs_aligned) {
+    constexpr unsigned N = VecOf<T>::N;
+    const bool vec = ptrs_aligned && a.dim % N == 0 && a.dim / N <= 1024u * 8u;
+    if (!vec) {
+        norm_rows_generic_kernel<T><<<static_cast<unsigned>(a.rows), 256, 0, s>>>(a);
+        LOKAL_CHECK_LAUNCH(ctx, "norm_rows_generic_kernel");
+        return LOKAL_OK;
+    }
+    a.nvec = a.dim / N;
+    // Threads per row: a warp while rows alone fill the machine; otherwise split
+    // each row over more threads so small batches still cover all SMs.
+    const size_t target_threads = static_cast<size_t>(ctx->sm_count) * 1024;
+    unsigned tpr = 32;
+    while (tpr < 1024 && tpr < a.nvec && a.rows * tpr < target_threads) tpr *= 2;
+    if (tpr == 32 && a.nvec > 32u * 8u) tpr = 64;
+    // A CTA of up to 1024 threads has 64 registers per thread: keep its share of the row small.
+    while (tpr > 32 && tpr < 1024 && (a.nvec + tpr - 1) / tpr > 2) tpr *= 2;
+    unsigned vpt = (a.nvec + tpr - 1) / tpr;
+    if (vpt == 7) vpt = 8;
+    cudaError_t e = tpr == 32 ? launch_vec<T, false>(a, tpr, vpt, s) : launch_vec<T, true>(a, tpr, vpt, s);
+    if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "launch of norm_rows_kernel failed: %s", cudaGetErrorString(e));
+    return LOKAL_OK;
+}
+
+}  // namespace
+
+int launch_norm(lokal_cuda_ctx* ctx, cudaStream_t s, void* x, const void* delta, const void* w, void* xn, void* xn_h,
+                size_t rows, size_t dim, float eps, int dtype, int w_dtype, int h_dtype) {
+    if (!x || !w || !xn) return ctx->fail(LOKAL_ERR_BAD_ARG, "rmsnorm: x, w and the output must be non-null");
+    if (dim == 0 || dim > 0x7fffffffu) return ctx->fail(LOKAL_ERR_BAD_ARG, "rmsnorm: dim %zu out of range", dim);
+    if (rows > 0x7fffffffu) return ctx->fail(LOKAL_ERR_BAD_ARG, "rmsnorm: rows %zu out of range", rows);
+    if (!is_act_type(dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "rmsnorm: row type %d is not F32/F16/BF16", dtype);
+    if (!is_act_type(w_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "rmsnorm: weight type %d is not F32/F16/BF16", w_dtype);
+    if (xn_h) {
+        if (dtype != LOKAL_F32) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "rmsnorm: the half copy needs F32 rows");
+        if (h_dtype != LOKAL_F16 && h_dtype != LOKAL_BF16)
+            return ctx->fail(LOKAL_ERR_UNSUPPORTED, "rmsnorm: half-copy type %d is not F16/BF16", h_dtype);
+        if (!aligned_to(xn_h, 2)) return ctx->fail(LOKAL_ERR_MISALIGNED, "rmsnorm: half copy is not 2-byte aligned");
+    }
+    const size_t es = type_size(dtype);
+    if (!aligned_to(x, es) || !aligned_to(xn, es) || (delta && !aligned_to(delta, es)) ||
+        !aligned_to(w, type_size(w_dtype)))
+        return ctx->fail(LOKAL_ERR_MISALIGNED, "rmsnorm: a pointer is not aligned to its element size");
+    if (rows == 0) return LOKAL_OK;
+
+    NormArgs a{};
+    a.x = x;
+    a.delta = delta;
+    a.w = w;
+    a.x_out = delta ? x : nullptr;
+    a.xn = xn;
+    a.xn_h = xn_h;
+    a.rows = rows;
+    a.dim = static_cast<unsigned>(dim);
+    a.eps = eps;
+    a.w_dtype = w_dtype;
+    a.h_dtype = h_dtype;
+    a.w_vec_ok = aligned_to(w, 16);
+    const bool aligned = aligned_to(x, 16) && aligned_to(xn, 16) && (!delta || aligned_to(delta, 16)) &&
+                         (!xn_h || aligned_to(xn_h, 8)) && (dim * es) % 16 == 0;
+    switch (dtype) {
+        case LOKAL_F32: return launch_typed<float>(ctx, s, a, aligned);
+        case LOKAL_F16: return launch_typed<__half>(ctx, s, a, aligned);
+        default: return launch_typed<__nv_bfloat16>(ctx, s, a, aligned);
+    }
+}
+
+}  // namespace lokal

@@ -1,0 +1,408 @@
+// RoPE: the per-step (cos, sin) table and the fused bias + per-head RMSNorm +
+// pair rotation of q and k in one HBM pass.
+//
+// Reference semantics (model::rope, src/model.rs:268-279): within each head,
+// element i pairs with i + rot/2; angle = pos * theta^(-(2 i)/rot);
+//   out[i]         = a * cos - b * sin
+//   out[i + rot/2] = a * sin + b * cos
+// with four separately rounded products. Before the rotation, in the order of
+// src/model.rs:208-226: bias add (Linear::forward, :27-35), then per-head
+// rmsnorm with a head_dim-long weight shared by all heads (:213-221).
+//
+// The angle's frequency comes from the host's powf (see lokal_cuda_rope_table
+// in the header), the angle itself is one f32 multiply on the device, and
+// sincosf is the accurate CUDA version (this library is never built with
+// fast-math). Because positions are shared by all heads and all layers of a
+// step, (cos, sin) live in a small table that stays L2-resident; the q/k
+// kernel is then a pure streaming kernel: every q/k element is read once and
+// written once.
+#include "common.cuh"
+
+#include <cmath>
+
+namespace lokal {
+namespace {
+
+constexpr unsigned kMaxRot = 1024;
+
+struct TableArgs {
+    float inv_freq[kMaxRot / 2];
+    const int32_t* positions;
+    long long pos0;
+    unsigned long long rows;
+    unsigned half;
+    float* out;
+};
+
+__global__ void __launch_bounds__(256) rope_table_kernel(const __grid_constant__ TableArgs a) {
+    const unsigned long long gid = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= a.rows * a.half) return;
+    const unsigned long long row = gid / a.half;
+    const unsigned i = static_cast<unsigned>(gid % a.half);
+    const long long pos = a.positions ? static_cast<long long>(a.positions[row]) : a.pos0 + static_cast<long long>(row);
+    const float angle = static_cast<float>(pos) * a.inv_freq[i];
+    float sn, cs;
+    sincosf(angle, &sn, &cs);
+    float* o = a.out + row * (2ull * a.half);
+    o[i] = cs;
+    o[a.half + i] = sn;
+}
+
+struct QkArgs {
+    const void* q;
+    const void* k;
+    void* q_out;
+    void* k_out;
+    const void* q_bias;
+    const void* k_bias;
+    const void* q_norm_w;
+    const void* k_norm_w;
+    const float* cos_sin;
+    const uint32_t* k_out_rows;
+    unsigned long long rows;
+    unsigned n_q, n_kv, head_dim, rot_dim;
+    unsigned long long q_stride, k_stride, q_out_stride, k_out_stride;
+    float eps;
+    int w_dtype;
+    int w_vec_ok;      // bias / norm pointers are 16-byte aligned
+    unsigned chunks;   // head slots of a row, in groups of (32 / lanes-per-head)
+    unsigned cpw;      // chunks handled by one warp
+    unsigned wpr;      // warps per row
+};
+
+// Fast path: rot_dim == head_dim == HD, 16-byte aligned rows. A group of LPH
+// lanes owns one head: each lane holds N elements of the first half and the N
+// partner elements of the second half.
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) qk_rope_kernel(const QkArgs a) {
+    constexpr int N = VecOf<T>::N;
+    constexpr int HALF = HD / 2;
+    constexpr int LPH = HALF / N;   // lanes per head
+    constexpr int HPW = 32 / LPH;   // heads per warp pass
+    static_assert(LPH >= 1 && LPH <= 32 && (LPH & (LPH - 1)) == 0, "head must map onto a power-of-two lane group");
+
+    const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const unsigned long long row = warp / a.wpr;
+    if (row >= a.rows) return;
+    const unsigned first_chunk = static_cast<unsigned>(warp % a.wpr) * a.cpw;
+    const unsigned lane = threadIdx.x & 31u;
+    const unsigned sub = lane % LPH;
+    const unsigned hsel = lane / LPH;
+    const unsigned slots = a.n_q + a.n_kv;
+
+    float cs[N], sn[N];
+    {
+        const float* tr = a.cos_sin + row * HD;
+#pragma unroll
+        for (int j = 0; j < N / 4; j++) {
+            float t[4];
+            unpack16<float>(ld_keep(tr + sub * N + 4 * j), t);
+#pragma unroll
+            for (int e = 0; e < 4; e++) cs[4 * j + e] = t[e];
+            unpack16<float>(ld_keep(tr + HALF + sub * N + 4 * j), t);
+#pragma unroll
+            for (int e = 0; e < 4; e++) sn[4 * j + e] = t[e];
+        }
+    }
+
+    for (unsigned c = first_chunk; c < first_chunk + a.cpw && c < a.chunks; c++) {
+        const unsigned slot = c * HPW + hsel;
+        const bool live = slot < slots;
+        const bool is_q = slot < a.n_q;
+        const unsigned head = is_q ? slot : slot - a.n_q;
+        const T* src = is_q ? reinterpret_cast<const T*>(a.q) + row * a.q_stride
+                            : reinterpret_cast<const T*>(a.k) + row * a.k_stride;
+        src += static_cast<size_t>(head) * HD + sub * N;
+        float va[N], vb[N];
+        if (live) {
+            const uint4 lo = ld_stream(src), hi = ld_stream(src + HALF);
+            unpack16<T>(lo, va);
+            unpack16<T>(hi, vb);
+        } else {
+#pragma unroll
+            for (int e = 0; e < N; e++) va[e] = vb[e] = 0.0f;
+        }
+        const void* bias = is_q ? a.q_bias : a.k_bias;
+        if (bias && live) {
+            float ba[N], bb[N];
+            load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + sub * N, a.w_vec_ok, ba);
+            load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + HALF + sub * N, a.w_vec_ok, bb);
+#pragma unroll
+            for (int e = 0; e < N; e++) {
+                va[e] = va[e] + ba[e];
+                vb[e] = vb[e] + bb[e];
+            }
+        }
+        // Uniform over the warp: the q and k norm weights are either both given or both absent per slot kind,
+        // and every lane takes part in the shuffles.
+        const bool any_norm = (a.q_norm_w != nullptr) || (a.k_norm_w != nullptr);
+        if (any_norm) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < N; e++) ss += va[e] * va[e];
+#pragma unroll
+            for (int e = 0; e < N; e++) ss += vb[e] * vb[e];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const void* nw = is_q ? a.q_norm_w : a.k_norm_w;
+            if (nw && live) {
+                const float mean_sq = ss / static_cast<float>(HD);
+                const float scale = 1.0f / sqrtf(mean_sq + a.eps);
+                float wa[N], wb[N];
+                load_w<N>(nw, a.w_dtype, sub * N, a.w_vec_ok, wa);
+                load_w<N>(nw, a.w_dtype, HALF + sub * N, a.w_vec_ok, wb);
+#pragma unroll
+                for (int e = 0; e < N; e++) {
+                    va[e] = (va[e] * scale) * wa[e];
+                    vb[e] = (vb[e] * scale) * wb[e];
+                }
+            }
+        }
+        if (live) {
+            float oa[N], ob[N];
+#pragma unroll
+            for (int e = 0; e < N; e++) {
+                oa[e] = va[e] * cs[e] - vb[e] * sn[e];
+                ob[e] = va[e] * sn[e] + vb[e] * cs[e];
+            }
+            T* dst;
+            if (is_q) {
+                dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride;
+            } else {
+                const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
+                dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride;
+            }
+            dst += static_cast<size_t>(head) * HD + sub * N;
+            *reinterpret_cast<uint4*>(dst) = pack16<T>(oa);
+            *reinterpret_cast<uint4*>(dst + HALF) = pack16<T>(ob);
+        }
+    }
+}
+
+// Any head_dim, any even rot_dim <= head_dim, any alignment: one warp per
+// (row, head). Dims rot_dim..head_dim are not rotated (partial RoPE,
+// src/gpu/kernels.metal:2401-2425); they are rewritten only when a bias or a
+// norm changed them or the output is a different buffer.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_rope_generic_kernel(const QkArgs a) {
+    const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const unsigned slots = a.n_q + a.n_kv;
+    const unsigned long long row = warp / slots;
+    if (row >= a.rows) return;
+    const unsigned slot = static_cast<unsigned>(warp % slots);
+    const unsigned lane = threadIdx.x & 31u;
+    const bool is_q = slot < a.n_q;
+    const unsigned head = is_q ? slot : slot - a.n_q;
+    const unsigned hd = a.head_dim, half = a.rot_dim / 2;
+    const T* src = (is_q ? reinterpret_cast<const T*>(a.q) + row * a.q_stride
+                         : reinterpret_cast<const T*>(a.k) + row * a.k_stride) + static_cast<size_t>(head) * hd;
+    T* dst;
+    if (is_q) {
+        dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride;
+    } else {
+        const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(a.k_out_rows[row]) : row;
+        dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride;
+    }
+    dst += static_cast<size_t>(head) * hd;
+    const void* bias = is_q ? a.q_bias : a.k_bias;
+    const void* nw = is_q ? a.q_norm_w : a.k_norm_w;
+    const size_t boff = static_cast<size_t>(head) * hd;
+
+    float scale = 1.0f;
+    if (nw) {
+        float ss = 0.0f;
+        for (unsigned i = lane; i < hd; i += 32) {
+            float v = to_f32<T>(src[i]);
+            if (bias) v = v + load_as_f32(bias, a.w_dtype, boff + i);
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / static_cast<float>(hd) + a.eps);
+    }
+    auto fetch = [&](unsigned i) {
+        float v = to_f32<T>(src[i]);
+        if (bias) v = v + load_as_f32(bias, a.w_dtype, boff + i);
+        if (nw) v = (v * scale) * load_as_f32(nw, a.w_dtype, i);
+        return v;
+    };
+    const float* tr = a.cos_sin + row * a.rot_dim;
+    for (unsigned i = lane; i < half; i += 32) {
+        const float va = fetch(i), vb = fetch(i + half);
+        const float cs = tr[i], sn = tr[half + i];
+        dst[i] = from_f32<T>(va * cs - vb * sn);
+        dst[i + half] = from_f32<T>(va * sn + vb * cs);
+    }
+    const bool rewrite_tail = bias || nw || (static_cast<const void*>(dst) != static_cast<const void*>(src));
+    if (rewrite_tail) {
+        for (unsigned i = a.rot_dim + lane; i < hd; i += 32) dst[i] = from_f32<T>(fetch(i));
+    }
+}
+
+template <typename T>
+int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
+    constexpr unsigned N = VecOf<T>::N;
+    const unsigned slots = a.n_q + a.n_kv;
+    if (slots == 0 || a.rows == 0) return LOKAL_OK;
+    const bool fast = fast_ok && a.rot_dim == a.head_dim && (a.head_dim == 64 || a.head_dim == 128 || a.head_dim == 256);
+    if (!fast) {
+        const unsigned long long warps = a.rows * slots;
+        const unsigned long long blocks = (warps + 7) / 8;
+        if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many head rows for one launch");
+        qk_rope_generic_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+        LOKAL_CHECK_LAUNCH(ctx, "qk_rope_generic_kernel");
+        return LOKAL_OK;
+    }
+    const unsigned lph = (a.head_dim / 2) / N, hpw = 32 / lph;
+    a.chunks = (slots + hpw - 1) / hpw;
+    // One warp per row while rows alone fill the machine; otherwise split a row's heads over several warps.
+    const unsigned long long want_warps = static_cast<unsigned long long>(ctx->sm_count) * 16;
+    unsigned wpr = 1;
+    if (a.rows < want_warps) {
+        wpr = static_cast<unsigned>((want_warps + a.rows - 1) / a.rows);
+        if (wpr > a.chunks) wpr = a.chunks;
+    }
+    a.cpw = (a.chunks + wpr - 1) / wpr;
+    a.wpr = (a.chunks + a.cpw - 1) / a.cpw;
+    const unsigned long long warps = a.rows * a.wpr;
+    const unsigned long long blocks = (warps + 7) / 8;
+    if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many rows for one launch");
+    const unsigned grid = static_cast<unsigned>(blocks);
+    switch (a.head_dim) {
+        case 64: qk_rope_kernel<T, 64><<<grid, 256, 0, s>>>(a); break;
+        case 128: qk_rope_kernel<T, 128><<<grid, 256, 0, s>>>(a); break;
+        default: qk_rope_kernel<T, 256><<<grid, 256, 0, s>>>(a); break;
+    }
+    LOKAL_CHECK_LAUNCH(ctx, "qk_rope_kernel");
+    return LOKAL_OK;
+}
+
+int launch_by_type(lokal_cuda_ctx* ctx, cudaStream_t s, const QkArgs& a, int dtype, bool fast_ok) {
+    switch (dtype) {
+        case LOKAL_F32: return launch_one<float>(ctx, s, a, fast_ok);
+        case LOKAL_F16: return launch_one<__half>(ctx, s, a, fast_ok);
+        default: return launch_one<__nv_bfloat16>(ctx, s, a, fast_ok);
+    }
+}
+
+}  // namespace
+
+int launch_rope_table(lokal_cuda_ctx* ctx, cudaStream_t s, float theta, uint32_t rot_dim, const int32_t* positions,
+                      int64_t pos0, size_t rows, float* cos_sin) {
+    if (!cos_sin) return ctx->fail(LOKAL_ERR_BAD_ARG, "rope_table: output is null");
+    if (rot_dim == 0 || (rot_dim & 1u) || rot_dim > kMaxRot)
+        return ctx->fail(LOKAL_ERR_BAD_ARG, "rope_table: rot_dim %u must be even and <= %u", rot_dim, kMaxRot);
+    if (!aligned_to(cos_sin, 16) || (positions && !aligned_to(positions, 4)))
+        return ctx->fail(LOKAL_ERR_MISALIGNED, "rope_table: table must be 16-byte aligned, positions 4-byte aligned");
+    if (!positions && pos0 < 0) return ctx->fail(LOKAL_ERR_BAD_ARG, "rope_table: pos0 is negative");
+    if (rows == 0) return LOKAL_OK;
+    TableArgs a;
+    const unsigned half = rot_dim / 2;
+    // theta.powf(-(2 i) / rot) in f32, as src/model.rs:272 evaluates it, through the host C library.
+    for (unsigned i = 0; i < half; i++) a.inv_freq[i] = powf(theta, -(2.0f * static_cast<float>(i)) / static_cast<float>(rot_dim));
+    for (unsigned i = half; i < kMaxRot / 2; i++) a.inv_freq[i] = 0.0f;
+    a.positions = positions;
+    a.pos0 = pos0;
+    a.rows = rows;
+    a.half = half;
+    a.out = cos_sin;
+    const unsigned long long total = static_cast<unsigned long long>(rows) * half;
+    const unsigned long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "rope_table: too many rows for one launch");
+    rope_table_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+    LOKAL_CHECK_LAUNCH(ctx, "rope_table_kernel");
+    return LOKAL_OK;
+}
+
+int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_params& p) {
+    if (!p.cos_sin) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: cos_sin table is null");
+    if (!p.q && !p.k) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: both q and k are null");
+    if (p.head_dim == 0 || (p.head_dim & 1u)) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: head_dim %u must be even and non-zero", p.head_dim);
+    if (p.rot_dim == 0 || (p.rot_dim & 1u) || p.rot_dim > p.head_dim || p.rot_dim > kMaxRot)
+        return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: rot_dim %u must be even, non-zero and <= head_dim %u", p.rot_dim, p.head_dim);
+    if (p.q && p.n_q_heads == 0) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: q given with zero heads");
+    if (p.k && p.n_kv_heads == 0) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: k given with zero heads");
+    if (p.q && !is_act_type(p.q_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "qk_rope: q type %d is not F32/F16/BF16", p.q_dtype);
+    if (p.k && !is_act_type(p.k_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "qk_rope: k type %d is not F32/F16/BF16", p.k_dtype);
+    const bool has_w = p.q_bias || p.k_bias || p.q_norm_w || p.k_norm_w;
+    if (has_w && !is_act_type(p.w_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "qk_rope: weight type %d is not F32/F16/BF16", p.w_dtype);
+    const unsigned long long q_w = static_cast<unsigned long long>(p.n_q_heads) * p.head_dim;
+    const unsigned long long k_w = static_cast<unsigned long long>(p.n_kv_heads) * p.head_dim;
+    if (p.q && p.q_row_stride < q_w) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: q_row_stride %llu < n_q_heads*head_dim %llu", (unsigned long long)p.q_row_stride, q_w);
+    if (p.k && p.k_row_stride < k_w) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: k_row_stride %llu < n_kv_heads*head_dim %llu", (unsigned long long)p.k_row_stride, k_w);
+    if (p.q && p.q_out && p.q_out_row_stride < q_w) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: q_out_row_stride too small");
+    if (p.k && p.k_out && p.k_out_row_stride < k_w) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: k_out_row_stride too small");
+    if (p.k_out_rows && !p.k_out) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: k_out_rows needs k_out");
+    const size_t wes = has_w ? type_size(p.w_dtype) : 1;
+    const void* wptrs[4] = {p.q_bias, p.k_bias, p.q_norm_w, p.k_norm_w};
+    bool w_vec = true;
+    for (const void* wp : wptrs) {
+        if (wp && !aligned_to(wp, wes)) return ctx->fail(LOKAL_ERR_MISALIGNED, "qk_rope: a weight pointer is not aligned to its element size");
+        if (wp && !aligned_to(wp, 16)) w_vec = false;
+    }
+    if (!aligned_to(p.cos_sin, 4) || (p.k_out_rows && !aligned_to(p.k_out_rows, 4)))
+        return ctx->fail(LOKAL_ERR_MISALIGNED, "qk_rope: table or row-index pointer is not 4-byte aligned");
+
+    QkArgs a{};
+    a.q_bias = p.q_bias;
+    a.k_bias = p.k_bias;
+    a.q_norm_w = p.q_norm_w;
+    a.k_norm_w = p.k_norm_w;
+    a.cos_sin = p.cos_sin;
+    a.k_out_rows = p.k_out_rows;
+    a.rows = p.rows;
+    a.head_dim = p.head_dim;
+    a.rot_dim = p.rot_dim;
+    a.eps = p.eps;
+    a.w_dtype = p.w_dtype;
+    a.w_vec_ok = w_vec;
+    a.q_stride = p.q_row_stride;
+    a.k_stride = p.k_row_stride;
+    a.q_out = p.q_out ? p.q_out : p.q;
+    a.k_out = p.k_out ? p.k_out : p.k;
+    a.q_out_stride = p.q_out ? p.q_out_row_stride : p.q_row_stride;
+    a.k_out_stride = p.k_out ? p.k_out_row_stride : p.k_row_stride;
+
+    auto tensor_fast = [&](const void* in, const void* out, unsigned long long in_stride, unsigned long long out_stride, int dtype) {
+        const size_t es = type_size(dtype);
+        return aligned_to(in, 16) && aligned_to(out, 16) && (in_stride * es) % 16 == 0 && (out_stride * es) % 16 == 0 &&
+               (static_cast<size_t>(p.head_dim) * es) % 32 == 0;
+    };
+    if (p.q && (!aligned_to(p.q, type_size(p.q_dtype)) || !aligned_to(a.q_out, type_size(p.q_dtype))))
+        return ctx->fail(LOKAL_ERR_MISALIGNED, "qk_rope: q is not aligned to its element size");
+    if (p.k && (!aligned_to(p.k, type_size(p.k_dtype)) || !aligned_to(a.k_out, type_size(p.k_dtype))))
+        return ctx->fail(LOKAL_ERR_MISALIGNED, "qk_rope: k is not aligned to its element size");
+    const bool table_fast = aligned_to(p.cos_sin, 16) && (static_cast<size_t>(p.rot_dim) * 4) % 32 == 0;
+
+    if (p.q && p.k && p.q_dtype == p.k_dtype) {
+        a.q = p.q;
+        a.k = p.k;
+        a.n_q = p.n_q_heads;
+        a.n_kv = p.n_kv_heads;
+        const bool fast = table_fast && tensor_fast(p.q, a.q_out, a.q_stride, a.q_out_stride, p.q_dtype) &&
+                          tensor_fast(p.k, a.k_out, a.k_stride, a.k_out_stride, p.k_dtype);
+        return launch_by_type(ctx, s, a, p.q_dtype, fast);
+    }
+    // q and k of different types (the reference GPU layout: f32 q, f16 k in the cache): one launch each.
+    if (p.q) {
+        QkArgs aq = a;
+        aq.q = p.q;
+        aq.k = nullptr;
+        aq.n_q = p.n_q_heads;
+        aq.n_kv = 0;
+        const bool fast = table_fast && tensor_fast(p.q, a.q_out, a.q_stride, a.q_out_stride, p.q_dtype);
+        int rc = launch_by_type(ctx, s, aq, p.q_dtype, fast);
+        if (rc != LOKAL_OK) return rc;
+    }
+    if (p.k) {
+        QkArgs ak = a;
+        ak.q = nullptr;
+        ak.k = p.k;
+        ak.n_q = 0;
+        ak.n_kv = p.n_kv_heads;
+        const bool fast = table_fast && tensor_fast(p.k, a.k_out, a.k_stride, a.k_out_stride, p.k_dtype);
+        return launch_by_type(ctx, s, ak, p.k_dtype, fast);
+    }
+    return LOKAL_OK;
+}
+
+}  // namespace lokal

@@ -1,0 +1,151 @@
+// SwiGLU activation: inner_i = (g_i / (1 + exp(-g_i))) * u_i
+// (math::silu, src/math.rs:68-70, and the SwiGLU line src/model.rs:245-248 of
+// the reference; note the expression shape is g / (1 + exp(-g)), not
+// g * sigmoid(g), which rounds differently).
+//
+// Pure streaming kernel: two 16-byte loads and one 16-byte store per thread
+// per step, 3 * sizeof(T) bytes of HBM traffic per element. f32 rows use the
+// accurate expf and IEEE division (the result has to hold to about one ulp);
+// 16-bit rows are rounded to 11 or 8 significant bits on store, so they use
+// the hardware exp2 / reciprocal approximations (relative error ~1e-6), which
+// keeps the kernel memory-bound instead of issue-bound.
+#include "common.cuh"
+
+namespace lokal {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    if (sizeof(T) == 4) {
+        return (g / (1.0f + expf(-g))) * u;
+    } else {
+        const float e = __expf(-g);
+        return __fdividef(g, 1.0f + e) * u;
+    }
+}
+
+struct SwigluArgs {
+    const void* gate;
+    const void* up;
+    void* out;
+    void* out_h;
+    unsigned long long nvec;  // whole 16-byte vectors
+    unsigned long long n;     // elements
+    int h_dtype;
+};
+
+constexpr int kSwigluUnroll = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
+    constexpr int N = VecOf<T>::N;
+    const T* g = reinterpret_cast<const T*>(a.gate);
+    const T* u = reinterpret_cast<const T*>(a.up);
+    T* o = reinterpret_cast<T*>(a.out);
+    // Each CTA owns a contiguous tile of kSwigluUnroll * blockDim vectors; a thread's
+    // vectors are blockDim apart so every load instruction of a warp is one 512-byte run.
+    const unsigned long long base = static_cast<unsigned long long>(blockIdx.x) * (blockDim.x * kSwigluUnroll) + threadIdx.x;
+    uint4 gv[kSwigluUnroll], uv[kSwigluUnroll];
+#pragma unroll
+    for (int j = 0; j < kSwigluUnroll; j++) {
+        const unsigned long long v = base + static_cast<unsigned long long>(j) * blockDim.x;
+        if (v < a.nvec) {
+            gv[j] = ld_stream(g + v * N);
+            uv[j] = ld_stream(u + v * N);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kSwigluUnroll; j++) {
+        const unsigned long long v = base + static_cast<unsigned long long>(j) * blockDim.x;
+        if (v < a.nvec) {
+            float gf[N], uf[N], y[N];
+            unpack16<T>(gv[j], gf);
+            unpack16<T>(uv[j], uf);
+#pragma unroll
+            for (int e = 0; e < N; e++) y[e] = silu_mul<T>(gf[e], uf[e]);
+            *reinterpret_cast<uint4*>(o + v * N) = pack16<T>(y);
+            if (sizeof(T) == 4 && a.out_h) {
+                unsigned w[2];
+                if (a.h_dtype == LOKAL_F16) {
+                    __half2 h0 = __floats2half2_rn(y[0], y[1]), h1 = __floats2half2_rn(y[2], y[3]);
+                    w[0] = *reinterpret_cast<unsigned*>(&h0);
+                    w[1] = *reinterpret_cast<unsigned*>(&h1);
+                } else {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(y[0], y[1]), h1 = __floats2bfloat162_rn(y[2], y[3]);
+                    w[0] = *reinterpret_cast<unsigned*>(&h0);
+                    w[1] = *reinterpret_cast<unsigned*>(&h1);
+                }
+                *reinterpret_cast<uint2*>(reinterpret_cast<unsigned short*>(a.out_h) + v * N) = make_uint2(w[0], w[1]);
+            }
+        }
+    }
+}
+
+// Elements [first, n): the ragged tail, or everything when pointers are not 16-byte aligned.
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_scalar_kernel(const SwigluArgs a, unsigned long long first) {
+    const unsigned long long i = first + static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= a.n) return;
+    const float g = to_f32<T>(reinterpret_cast<const T*>(a.gate)[i]);
+    const float u = to_f32<T>(reinterpret_cast<const T*>(a.up)[i]);
+    const float y = silu_mul<T>(g, u);
+    reinterpret_cast<T*>(a.out)[i] = from_f32<T>(y);
+    if (a.out_h) {
+        reinterpret_cast<unsigned short*>(a.out_h)[i] =
+            a.h_dtype == LOKAL_F16 ? __half_as_ushort(__float2half_rn(y)) : __bfloat16_as_ushort(__float2bfloat16_rn(y));
+    }
+}
+
+template <typename T>
+int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, SwigluArgs a, bool aligned) {
+    constexpr unsigned N = VecOf<T>::N;
+    a.nvec = aligned ? a.n / N : 0;
+    if (a.nvec) {
+        const unsigned long long per_cta = 256ull * kSwigluUnroll;
+        const unsigned long long blocks = (a.nvec + per_cta - 1) / per_cta;
+        if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "swiglu: too many elements for one launch");
+        swiglu_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+        LOKAL_CHECK_LAUNCH(ctx, "swiglu_kernel");
+    }
+    const unsigned long long first = a.nvec * N;
+    if (first < a.n) {
+        const unsigned long long blocks = (a.n - first + 255) / 256;
+        if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "swiglu: too many elements for one launch");
+        swiglu_scalar_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a, first);
+        LOKAL_CHECK_LAUNCH(ctx, "swiglu_scalar_kernel");
+    }
+    return LOKAL_OK;
+}
+
+}  // namespace
+
+int launch_swiglu(lokal_cuda_ctx* ctx, cudaStream_t s, const void* gate, const void* up, void* out, void* out_h,
+                  size_t n, int dtype, int h_dtype) {
+    if (!gate || !up || !out) return ctx->fail(LOKAL_ERR_BAD_ARG, "swiglu: gate, up and out must be non-null");
+    if (!is_act_type(dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "swiglu: element type %d is not F32/F16/BF16", dtype);
+    if (out_h) {
+        if (dtype != LOKAL_F32) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "swiglu: the half copy needs F32 elements");
+        if (h_dtype != LOKAL_F16 && h_dtype != LOKAL_BF16)
+            return ctx->fail(LOKAL_ERR_UNSUPPORTED, "swiglu: half-copy type %d is not F16/BF16", h_dtype);
+        if (!aligned_to(out_h, 2)) return ctx->fail(LOKAL_ERR_MISALIGNED, "swiglu: half copy is not 2-byte aligned");
+    }
+    const size_t es = type_size(dtype);
+    if (!aligned_to(gate, es) || !aligned_to(up, es) || !aligned_to(out, es))
+        return ctx->fail(LOKAL_ERR_MISALIGNED, "swiglu: a pointer is not aligned to its element size");
+    if (n == 0) return LOKAL_OK;
+    SwigluArgs a{};
+    a.gate = gate;
+    a.up = up;
+    a.out = out;
+    a.out_h = out_h;
+    a.n = n;
+    a.h_dtype = h_dtype;
+    const bool aligned = aligned_to(gate, 16) && aligned_to(up, 16) && aligned_to(out, 16) && (!out_h || aligned_to(out_h, 8));
+    switch (dtype) {
+        case LOKAL_F32: return launch_typed<float>(ctx, s, a, aligned);
+        case LOKAL_F16: return launch_typed<__half>(ctx, s, a, aligned);
+        default: return launch_typed<__nv_bfloat16>(ctx, s, a, aligned);
+    }
+}
+
+}  // namespace lokal

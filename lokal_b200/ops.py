@@ -1,0 +1,244 @@
+"""Host-side handle over the C ABI, named after the reference's ops.
+
+`Context` owns one `lokal_cuda_ctx` (one per GPU). Device buffers are passed
+as anything with a ``data_ptr()`` (torch tensors are used by the tests and the
+benchmark purely as device allocations) or as raw integer addresses. Every
+method forwards to exactly one C entry point; errors come back as
+`LokalCudaError` carrying the library's status code and message. Nothing here
+computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+from .capi import BF16, F16, F32, Q4_K, Q8_0, LokalCudaError, QkRopeParams
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data
+    raise TypeError(f"cannot take the address of {type(x)!r}")
+
+
+_TORCH_TYPES = None
+
+
+def dtype_id(x) -> int:
+    """lokal_type of a torch tensor's dtype."""
+    global _TORCH_TYPES
+    if _TORCH_TYPES is None:
+        import torch
+        _TORCH_TYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+    return _TORCH_TYPES[x.dtype]
+
+
+class Context:
+    def __init__(self, device: int = 0):
+        self._lib = capi.load()
+        h = C.c_void_p()
+        rc = self._lib.lokal_cuda_create(device, C.byref(h))
+        if rc != capi.OK:
+            raise LokalCudaError(rc, f"lokal_cuda_create(device={device}) failed")
+        self._h = h
+        self.device = device
+
+    # -- plumbing ---------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.lokal_cuda_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    @property
+    def handle(self):
+        return self._h
+
+    def _check(self, rc: int):
+        if rc != capi.OK:
+            raise LokalCudaError(rc, self._lib.lokal_cuda_last_error(self._h).decode())
+
+    def version(self) -> str:
+        return self._lib.lokal_cuda_version().decode()
+
+    def stream_create(self) -> int:
+        s = C.c_void_p()
+        self._check(self._lib.lokal_cuda_stream_create(self._h, C.byref(s)))
+        return s.value
+
+    def stream_destroy(self, s):
+        self._check(self._lib.lokal_cuda_stream_destroy(self._h, s))
+
+    def stream_sync(self, s=None):
+        self._check(self._lib.lokal_cuda_stream_sync(self._h, s))
+
+    def malloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self._check(self._lib.lokal_cuda_malloc(self._h, nbytes, C.byref(p)))
+        return p.value or 0
+
+    def free(self, p):
+        self._check(self._lib.lokal_cuda_free(self._h, p))
+
+    def host_alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self._check(self._lib.lokal_cuda_host_alloc(self._h, nbytes, C.byref(p)))
+        return p.value or 0
+
+    def host_free(self, p):
+        self._check(self._lib.lokal_cuda_host_free(self._h, p))
+
+    def memcpy_h2d(self, dst, src, nbytes: int, stream=None):
+        self._check(self._lib.lokal_cuda_memcpy_h2d(self._h, stream, _ptr(dst), _ptr(src), nbytes))
+
+    def memcpy_d2h(self, dst, src, nbytes: int, stream=None):
+        self._check(self._lib.lokal_cuda_memcpy_d2h(self._h, stream, _ptr(dst), _ptr(src), nbytes))
+
+    def graph_begin(self, stream):
+        self._check(self._lib.lokal_cuda_graph_begin(self._h, stream))
+
+    def graph_end(self, stream) -> int:
+        g = C.c_void_p()
+        self._check(self._lib.lokal_cuda_graph_end(self._h, stream, C.byref(g)))
+        return g.value
+
+    def graph_launch(self, graph, stream):
+        self._check(self._lib.lokal_cuda_graph_launch(self._h, graph, stream))
+
+    def graph_destroy(self, graph):
+        self._check(self._lib.lokal_cuda_graph_destroy(self._h, graph))
+
+    # -- ops on device memory ------------------------------------------------
+    def rmsnorm(self, x, w, y, *, rows, dim, eps, dtype, w_dtype=F32, y_h=None, h_dtype=F16, stream=None):
+        self._check(self._lib.lokal_cuda_rmsnorm(self._h, stream, _ptr(x), _ptr(w), _ptr(y), _ptr(y_h), rows, dim,
+                                                 eps, dtype, w_dtype, h_dtype))
+
+    def add_rmsnorm(self, x_inout, delta, w, xn, *, rows, dim, eps, dtype, w_dtype=F32, xn_h=None, h_dtype=F16,
+                    stream=None):
+        self._check(self._lib.lokal_cuda_add_rmsnorm(self._h, stream, _ptr(x_inout), _ptr(delta), _ptr(w), _ptr(xn),
+                                                     _ptr(xn_h), rows, dim, eps, dtype, w_dtype, h_dtype))
+
+    def rope_table(self, cos_sin, *, theta, rot_dim, rows, positions=None, pos0=0, stream=None):
+        self._check(self._lib.lokal_cuda_rope_table(self._h, stream, theta, rot_dim, _ptr(positions), pos0, rows,
+                                                    _ptr(cos_sin)))
+
+    @staticmethod
+    def qk_rope_params(*, q=None, k=None, q_out=None, k_out=None, q_bias=None, k_bias=None, q_norm_w=None,
+                       k_norm_w=None, cos_sin=None, k_out_rows=None, rows, n_q_heads, n_kv_heads, head_dim,
+                       rot_dim=None, q_row_stride=None, k_row_stride=None, q_out_row_stride=None,
+                       k_out_row_stride=None, eps=0.0, q_dtype=F32, k_dtype=None, w_dtype=F32) -> QkRopeParams:
+        p = QkRopeParams()
+        p.q, p.k, p.q_out, p.k_out = _ptr(q), _ptr(k), _ptr(q_out), _ptr(k_out)
+        p.q_bias, p.k_bias, p.q_norm_w, p.k_norm_w = _ptr(q_bias), _ptr(k_bias), _ptr(q_norm_w), _ptr(k_norm_w)
+        p.cos_sin, p.k_out_rows = _ptr(cos_sin), _ptr(k_out_rows)
+        p.rows = rows
+        p.n_q_heads, p.n_kv_heads, p.head_dim = n_q_heads, n_kv_heads, head_dim
+        p.rot_dim = head_dim if rot_dim is None else rot_dim
+        p.q_row_stride = n_q_heads * head_dim if q_row_stride is None else q_row_stride
+        p.k_row_stride = n_kv_heads * head_dim if k_row_stride is None else k_row_stride
+        p.q_out_row_stride = p.q_row_stride if q_out_row_stride is None else q_out_row_stride
+        p.k_out_row_stride = p.k_row_stride if k_out_row_stride is None else k_out_row_stride
+        p.eps = eps
+        p.q_dtype = q_dtype
+        p.k_dtype = q_dtype if k_dtype is None else k_dtype
+        p.w_dtype = w_dtype
+        return p
+
+    def qk_rope(self, params: QkRopeParams, stream=None):
+        self._check(self._lib.lokal_cuda_qk_rope(self._h, stream, C.byref(params)))
+
+    def qk_rope_pos(self, params: QkRopeParams, *, theta, positions=None, pos0=0, stream=None):
+        self._check(self._lib.lokal_cuda_qk_rope_pos(self._h, stream, C.byref(params), theta, _ptr(positions), pos0))
+
+    def swiglu(self, gate, up, out, *, n, dtype, out_h=None, h_dtype=F16, stream=None):
+        self._check(self._lib.lokal_cuda_swiglu(self._h, stream, _ptr(gate), _ptr(up), _ptr(out), _ptr(out_h), n,
+                                                dtype, h_dtype))
+
+    def embed_gather(self, table, ids, out, *, ggml_type, vocab, dim, n, out_dtype=F32, stream=None):
+        self._check(self._lib.lokal_cuda_embed_gather(self._h, stream, _ptr(table), ggml_type, vocab, dim, _ptr(ids),
+                                                      n, _ptr(out), out_dtype))
+
+    def dequant_rows(self, src, out, *, ggml_type, rows, cols, out_dtype=F32, stream=None):
+        self._check(self._lib.lokal_cuda_dequant_rows(self._h, stream, ggml_type, _ptr(src), rows, cols, _ptr(out),
+                                                      out_dtype))
+
+    # -- host-slice mirrors of the reference's CPU signatures ----------------------
+    def host_rmsnorm(self, x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+        """math::rmsnorm(x, weight, eps) -> new vector; x may be [dim] or [rows, dim]."""
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        rows, dim = (1, x.shape[0]) if x.ndim == 1 else x.shape
+        if w.size != dim:
+            raise ValueError("weight length differs from the row length")
+        y = np.empty_like(x)
+        self._check(self._lib.lokal_cuda_host_rmsnorm(self._h, _ptr(x), _ptr(w), eps, rows, dim, _ptr(y)))
+        return y
+
+    def host_rope(self, x: np.ndarray, pos: int, head_dim: int, theta: float) -> np.ndarray:
+        """model::rope(x, pos, head_dim, theta), returned as a rotated copy."""
+        x = np.ascontiguousarray(x, np.float32).copy()
+        self._check(self._lib.lokal_cuda_host_rope(self._h, _ptr(x), x.size, pos, head_dim, theta))
+        return x
+
+    def host_swiglu(self, gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+        gate = np.ascontiguousarray(gate, np.float32)
+        up = np.ascontiguousarray(up, np.float32)
+        if gate.size != up.size:
+            raise ValueError("gate and up differ in length")
+        out = np.empty_like(gate)
+        self._check(self._lib.lokal_cuda_host_swiglu(self._h, _ptr(gate), _ptr(up), gate.size, _ptr(out)))
+        return out
+
+    def host_dequant_row(self, ggml_type: int, src: np.ndarray, n: int) -> np.ndarray:
+        """gguf::dequant_row_ref(ty, src, out[n])."""
+        src = np.ascontiguousarray(src, np.uint8)
+        out = np.empty(n, np.float32)
+        self._check(self._lib.lokal_cuda_host_dequant_row(self._h, ggml_type, _ptr(src), src.size, _ptr(out), n))
+        return out
+
+    def host_embed_gather(self, table_dev, ggml_type: int, vocab: int, dim: int, ids: np.ndarray) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, np.uint32)
+        out = np.empty((ids.size, dim), np.float32)
+        self._check(self._lib.lokal_cuda_host_embed_gather(self._h, _ptr(table_dev), ggml_type, vocab, dim, _ptr(ids),
+                                                           ids.size, _ptr(out)))
+        return out
+
+
+def blk_elems(ggml_type: int) -> int:
+    return capi.load().lokal_cuda_blk_elems(ggml_type)
+
+
+def blk_bytes(ggml_type: int) -> int:
+    return capi.load().lokal_cuda_blk_bytes(ggml_type)
+
+
+def row_bytes(ggml_type: int, n: int) -> int:
+    return capi.load().lokal_cuda_row_bytes(ggml_type, n)
+
+
+def shard_rows(n_rows: int, n_gpus: int, rank: int) -> tuple[int, int]:
+    """Contiguous row block [row0, row0+count) that GPU `rank` of `n_gpus` owns."""
+    r0, cnt = C.c_size_t(), C.c_size_t()
+    rc = capi.load().lokal_cuda_shard_rows(n_rows, n_gpus, rank, C.byref(r0), C.byref(cnt))
+    if rc != capi.OK:
+        raise LokalCudaError(rc, f"shard_rows({n_rows}, {n_gpus}, {rank})")
+    return r0.value, cnt.value

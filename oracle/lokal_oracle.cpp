@@ -1,0 +1,628 @@
+// CPU oracle for lokal's fused per-token layer ops.
+//
+// TEST INFRASTRUCTURE ONLY. This file is a plain C++ restatement of the
+// reference's CPU algorithm for the hot path; it is the checker the CUDA
+// library is compared against and the timed CPU baseline. Nothing in the
+// shipped package may call it: only the test suite, the smoke check and the
+// benchmark's CPU-baseline leg load this library.
+//
+// Parity status:
+//   * GGUF Q8_0 / Q4_K dequant, block-size table, embedding gather: PINNED by
+//     the reference's own known-answer vectors (src/gguf/dequant.rs:567-577,
+//     683-730, 768-780) and by a second, independently written per-element
+//     decoder in this file (the index form of src/gpu/kernels.metal:77-81,
+//     108-116, 889-904).
+//   * rmsnorm / dot: pinned by src/math.rs:86-108 (dot tail vector, all-3s row).
+//   * RoPE and SiLU: PARITY UNPINNED at the libm boundary. The reference calls
+//     the platform libm (powf, sinf, cosf, expf) through Rust std and holds no
+//     test that fixes those bits; on Linux that libm is glibc, the same one
+//     this file links, so the restated results are what the Rust code would
+//     produce on this machine.
+//
+// Arithmetic rules that make this a faithful restatement (the file must be
+// built with -ffp-contract=off and without -ffast-math): every f32 multiply,
+// add, subtract, divide and sqrt is separately rounded (Rust never contracts
+// to FMA), association follows the reference expression by expression.
+//
+// Third-party arithmetic restated here: the `half` crate, version 2.7.1
+// (Cargo.lock:966-968) -- f16/bf16 <-> f32 conversions, done below as bit
+// manipulation with round-to-nearest-even, gradual underflow and overflow to
+// infinity, which is that crate's published behaviour.
+
+#include <cmath>
+#include <cstddef>
+#include <cstdint>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#define ORACLE_API extern "C" __attribute__((visibility("default")))
+
+// ---------------------------------------------------------------------------
+// half / bf16 conversions (crate `half` 2.7.1 semantics)
+// ---------------------------------------------------------------------------
+
+static inline float bits_to_f32(uint32_t u) {
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+
+static inline uint32_t f32_to_bits(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    return u;
+}
+
+// f16 bits -> f32, exact (src/gguf/dequant.rs:135-137 uses f16::to_f32).
+static inline float f16_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    if (exp == 0) {
+        if (man == 0) return bits_to_f32(sign);
+        // subnormal: value = man * 2^-24, exactly representable in f32
+        float v = (float)man * 5.9604644775390625e-08f;  // 2^-24
+        return sign ? -v : v;
+    }
+    if (exp == 31) return bits_to_f32(sign | 0x7F800000u | (man << 13));
+    return bits_to_f32(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+// f32 -> f16 bits, round to nearest even, overflow to infinity, gradual
+// underflow (src/gpu/metal.rs:723 uses f16::from_f32).
+static inline uint16_t f32_to_f16(float f) {
+    uint32_t x = f32_to_bits(f);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t exp = (x >> 23) & 0xFFu;
+    uint32_t man = x & 0x7FFFFFu;
+    if (exp == 255) {  // inf / nan (keep a quiet nan payload bit)
+        return (uint16_t)(sign | 0x7C00u | (man ? (0x200u | (man >> 13)) : 0u));
+    }
+    int32_t e = (int32_t)exp - 127 + 15;
+    if (e >= 31) return (uint16_t)(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;  // rounds to zero
+        man |= 0x800000u;                    // implicit leading one
+        uint32_t shift = (uint32_t)(14 - e); // 14..24
+        uint32_t half_man = man >> shift;
+        uint32_t rem = man & ((1u << shift) - 1u);
+        uint32_t halfway = 1u << (shift - 1);
+        if (rem > halfway || (rem == halfway && (half_man & 1u))) half_man++;
+        return (uint16_t)(sign | half_man);
+    }
+    uint32_t half_bits = ((uint32_t)e << 10) | (man >> 13);
+    uint32_t rem = man & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (half_bits & 1u))) half_bits++;  // may carry into exp/inf
+    return (uint16_t)(sign | half_bits);
+}
+
+// bf16 bits -> f32 is an exact shift (src/weights.rs:57-60).
+static inline float bf16_to_f32(uint16_t b) { return bits_to_f32((uint32_t)b << 16); }
+
+// f32 -> bf16 bits, round to nearest even.
+static inline uint16_t f32_to_bf16(float f) {
+    uint32_t x = f32_to_bits(f);
+    if ((x & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((x >> 16) | 0x0040u);  // nan stays nan
+    uint32_t round_bit = 0x8000u;
+    if ((x & round_bit) != 0 && (x & (3u * round_bit - 1u)) != 0) return (uint16_t)((x >> 16) + 1u);
+    return (uint16_t)(x >> 16);
+}
+
+ORACLE_API float lokal_ref_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+ORACLE_API uint16_t lokal_ref_f32_to_f16(float f) { return f32_to_f16(f); }
+ORACLE_API float lokal_ref_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }
+ORACLE_API uint16_t lokal_ref_f32_to_bf16(float f) { return f32_to_bf16(f); }
+
+ORACLE_API void lokal_ref_f32_to_f16_array(const float* x, size_t n, uint16_t* out) {
+    for (size_t i = 0; i < n; i++) out[i] = f32_to_f16(x[i]);
+}
+ORACLE_API void lokal_ref_f32_to_bf16_array(const float* x, size_t n, uint16_t* out) {
+    for (size_t i = 0; i < n; i++) out[i] = f32_to_bf16(x[i]);
+}
+ORACLE_API void lokal_ref_f16_to_f32_array(const uint16_t* x, size_t n, float* out) {
+    for (size_t i = 0; i < n; i++) out[i] = f16_to_f32(x[i]);
+}
+ORACLE_API void lokal_ref_bf16_to_f32_array(const uint16_t* x, size_t n, float* out) {
+    for (size_t i = 0; i < n; i++) out[i] = bf16_to_f32(x[i]);
+}
+
+// ---------------------------------------------------------------------------
+// math.rs leaf ops
+// ---------------------------------------------------------------------------
+
+// src/math.rs:25-38 -- eight independent lane accumulators over chunks of 8,
+// lanes summed in index order, then the tail added sequentially.
+static float ref_dot(const float* a, const float* b, size_t n) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    size_t chunks = n / 8;
+    for (size_t c = 0; c < chunks; c++) {
+        for (size_t i = 0; i < 8; i++) {
+            float p = a[c * 8 + i] * b[c * 8 + i];
+            acc[i] = acc[i] + p;
+        }
+    }
+    float sum = 0.0f;
+    for (size_t i = 0; i < 8; i++) sum = sum + acc[i];
+    for (size_t i = chunks * 8; i < n; i++) {
+        float p = a[i] * b[i];
+        sum = sum + p;
+    }
+    return sum;
+}
+
+// src/math.rs:45-49 -- y_i = (x_i * scale) * w_i with scale = 1/sqrt(mean+eps).
+static void ref_rmsnorm(const float* x, const float* w, float eps, size_t n, float* y) {
+    float mean_sq = ref_dot(x, x, n) / (float)n;
+    float scale = 1.0f / std::sqrt(mean_sq + eps);
+    for (size_t i = 0; i < n; i++) {
+        float t = x[i] * scale;
+        y[i] = t * w[i];
+    }
+}
+
+// src/math.rs:68-70 -- x / (1 + exp(-x)).
+static inline float ref_silu(float x) { return x / (1.0f + std::exp(-x)); }
+
+// src/model.rs:268-279, with the rotated prefix `rot_dim` of the GPU twin
+// (src/gpu/kernels.metal:2401-2425). rot_dim == head_dim is the CPU function
+// itself: pairs (i, i + rot/2), freq = theta^(-(2 i)/rot), angle = pos * freq.
+// powf and sincos are recomputed for every head, as the reference does.
+static void ref_rope(float* x, size_t n, size_t pos, size_t head_dim, size_t rot_dim, float theta) {
+    size_t half = rot_dim / 2;
+    for (size_t h0 = 0; h0 + head_dim <= n; h0 += head_dim) {
+        float* head = x + h0;
+        for (size_t i = 0; i < half; i++) {
+            float freq = std::pow(theta, -(2.0f * (float)i) / (float)rot_dim);
+            float angle = (float)pos * freq;
+            float s = std::sin(angle), c = std::cos(angle);
+            float a = head[i], b = head[i + half];
+            float ac = a * c, bs = b * s, as = a * s, bc = b * c;
+            head[i] = ac - bs;
+            head[i + half] = as + bc;
+        }
+    }
+}
+
+ORACLE_API float lokal_ref_dot(const float* a, const float* b, size_t n) { return ref_dot(a, b, n); }
+ORACLE_API void lokal_ref_rmsnorm(const float* x, const float* w, float eps, size_t n, float* y) {
+    ref_rmsnorm(x, w, eps, n, y);
+}
+ORACLE_API float lokal_ref_silu(float x) { return ref_silu(x); }
+ORACLE_API void lokal_ref_rope(float* x, size_t n, size_t pos, size_t head_dim, float theta) {
+    ref_rope(x, n, pos, head_dim, head_dim, theta);
+}
+ORACLE_API void lokal_ref_rope_partial(float* x, size_t n, size_t pos, size_t head_dim, size_t rot_dim,
+                                       float theta) {
+    ref_rope(x, n, pos, head_dim, rot_dim, theta);
+}
+
+// inv-freq vector theta^(-(2 i)/rot) exactly as ref_rope evaluates it.
+ORACLE_API void lokal_ref_inv_freq(float theta, size_t rot_dim, float* out) {
+    for (size_t i = 0; i < rot_dim / 2; i++) out[i] = std::pow(theta, -(2.0f * (float)i) / (float)rot_dim);
+}
+
+// (cos, sin) rows for given positions: out[row][0..half) = cos, [half..rot) = sin.
+ORACLE_API void lokal_ref_rope_table(float theta, size_t rot_dim, const int32_t* positions, int64_t pos0,
+                                     size_t rows, float* out) {
+    size_t half = rot_dim / 2;
+    for (size_t r = 0; r < rows; r++) {
+        size_t pos = positions ? (size_t)positions[r] : (size_t)(pos0 + (int64_t)r);
+        for (size_t i = 0; i < half; i++) {
+            float freq = std::pow(theta, -(2.0f * (float)i) / (float)rot_dim);
+            float angle = (float)pos * freq;
+            out[r * rot_dim + i] = std::cos(angle);
+            out[r * rot_dim + half + i] = std::sin(angle);
+        }
+    }
+}
+
+// Self-check hook: do sincosf and the sinf/cosf pair agree bit for bit on x?
+ORACLE_API int lokal_ref_sincos_spellings_agree(float x) {
+    float s, c;
+    sincosf(x, &s, &c);
+    float s2 = std::sin(x), c2 = std::cos(x);
+    return f32_to_bits(s) == f32_to_bits(s2) && f32_to_bits(c) == f32_to_bits(c2);
+}
+
+// ---------------------------------------------------------------------------
+// Row-batched composites (definition = the reference's steps in model.rs order)
+// ---------------------------------------------------------------------------
+
+template <typename F>
+static void parallel_rows(size_t rows, int threads, F fn) {
+    if (threads <= 1 || rows < 2) {
+        fn((size_t)0, rows);
+        return;
+    }
+    size_t nt = (size_t)threads < rows ? (size_t)threads : rows;
+    std::vector<std::thread> pool;
+    size_t per = (rows + nt - 1) / nt;
+    for (size_t t = 0; t < nt; t++) {
+        size_t r0 = t * per, r1 = r0 + per < rows ? r0 + per : rows;
+        if (r0 >= r1) break;
+        pool.emplace_back([=] { fn(r0, r1); });
+    }
+    for (auto& th : pool) th.join();
+}
+
+// x' = x + delta (src/model.rs:235-237, 253-255); xn = rmsnorm(x', w, eps)
+// (src/math.rs:45-49). delta may be null (plain rmsnorm, x untouched).
+ORACLE_API void lokal_ref_add_rmsnorm_rows(float* x, const float* delta, const float* w, float* xn, size_t rows,
+                                           size_t dim, float eps, int threads) {
+    parallel_rows(rows, threads, [=](size_t r0, size_t r1) {
+        for (size_t r = r0; r < r1; r++) {
+            float* xr = x + r * dim;
+            if (delta) {
+                const float* dr = delta + r * dim;
+                for (size_t i = 0; i < dim; i++) xr[i] = xr[i] + dr[i];
+            }
+            ref_rmsnorm(xr, w, eps, dim, xn + r * dim);
+        }
+    });
+}
+
+// One q or k row: bias add (src/model.rs:29-33), per-head rmsnorm with a
+// weight of head_dim entries shared by all heads (src/model.rs:213-221), then
+// rope (src/model.rs:225-226). bias / norm_w may be null.
+static void ref_qk_row(float* v, size_t n_heads, size_t head_dim, size_t rot_dim, const float* bias,
+                       const float* norm_w, float eps, size_t pos, float theta, std::vector<float>& tmp) {
+    size_t n = n_heads * head_dim;
+    if (bias) {
+        for (size_t i = 0; i < n; i++) v[i] = v[i] + bias[i];
+    }
+    if (norm_w) {
+        tmp.resize(head_dim);
+        for (size_t h = 0; h < n_heads; h++) {
+            ref_rmsnorm(v + h * head_dim, norm_w, eps, head_dim, tmp.data());
+            std::memcpy(v + h * head_dim, tmp.data(), head_dim * sizeof(float));
+        }
+    }
+    ref_rope(v, n, pos, head_dim, rot_dim, theta);
+}
+
+ORACLE_API void lokal_ref_qk_rope_rows(float* q, float* k, const float* q_bias, const float* k_bias,
+                                       const float* q_norm_w, const float* k_norm_w, const int32_t* positions,
+                                       int64_t pos0, size_t rows, size_t n_q_heads, size_t n_kv_heads,
+                                       size_t head_dim, size_t rot_dim, float eps, float theta, int threads) {
+    parallel_rows(rows, threads, [=](size_t r0, size_t r1) {
+        std::vector<float> tmp;
+        for (size_t r = r0; r < r1; r++) {
+            size_t pos = positions ? (size_t)positions[r] : (size_t)(pos0 + (int64_t)r);
+            if (q) ref_qk_row(q + r * n_q_heads * head_dim, n_q_heads, head_dim, rot_dim, q_bias, q_norm_w, eps, pos,
+                              theta, tmp);
+            if (k) ref_qk_row(k + r * n_kv_heads * head_dim, n_kv_heads, head_dim, rot_dim, k_bias, k_norm_w, eps,
+                              pos, theta, tmp);
+        }
+    });
+}
+
+// inner_i = silu(gate_i) * up_i (src/model.rs:245-248).
+ORACLE_API void lokal_ref_swiglu(const float* gate, const float* up, size_t n, float* out, int threads) {
+    parallel_rows(n, threads, [=](size_t i0, size_t i1) {
+        for (size_t i = i0; i < i1; i++) out[i] = ref_silu(gate[i]) * up[i];
+    });
+}
+
+// ---------------------------------------------------------------------------
+// GGUF block formats (src/gguf/dequant.rs:21-41, 81-119)
+// ---------------------------------------------------------------------------
+
+enum : uint32_t { GGML_F32 = 0, GGML_F16 = 1, GGML_Q8_0 = 8, GGML_Q4_K = 12, GGML_BF16 = 30 };
+
+ORACLE_API size_t lokal_ref_blk_elems(uint32_t ty) {
+    switch (ty) {
+        case GGML_F32: case GGML_F16: case GGML_BF16: return 1;
+        case GGML_Q8_0: return 32;
+        case GGML_Q4_K: return 256;
+        default: return 0;
+    }
+}
+
+ORACLE_API size_t lokal_ref_blk_bytes(uint32_t ty) {
+    switch (ty) {
+        case GGML_F32: return 4;
+        case GGML_F16: case GGML_BF16: return 2;
+        case GGML_Q8_0: return 2 + 32;
+        case GGML_Q4_K: return 2 + 2 + 12 + 128;
+        default: return 0;
+    }
+}
+
+// n / blk_elems * blk_bytes with integer division (src/gguf/dequant.rs:117-119).
+ORACLE_API size_t lokal_ref_row_bytes(uint32_t ty, size_t n) {
+    size_t be = lokal_ref_blk_elems(ty);
+    return be ? n / be * lokal_ref_blk_bytes(ty) : 0;
+}
+
+static inline float f16_bits_at(const uint8_t* src, size_t off) {
+    return f16_to_f32((uint16_t)(src[off] | (src[off + 1] << 8)));
+}
+
+// src/gguf/dequant.rs:141-150.
+static inline void scale_min_k4(size_t j, const uint8_t* q, uint8_t* sc, uint8_t* mn) {
+    if (j < 4) {
+        *sc = q[j] & 63;
+        *mn = q[j + 4] & 63;
+    } else {
+        *sc = (uint8_t)((q[j + 4] & 0x0F) | ((q[j - 4] >> 6) << 4));
+        *mn = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    }
+}
+
+// Sequential row decode (src/gguf/dequant.rs:191-239, 462-483). Returns 0, or
+// -1 where the reference would panic on a src/out size mismatch (:192), or -2
+// for a type outside this path.
+ORACLE_API int lokal_ref_dequant_row(uint32_t ty, const uint8_t* src, size_t src_len, float* out, size_t n) {
+    if (lokal_ref_blk_elems(ty) == 0) return -2;
+    if (src_len != lokal_ref_row_bytes(ty, n)) return -1;
+    switch (ty) {
+        case GGML_F32:
+            for (size_t i = 0; i < n; i++) {
+                uint32_t u = (uint32_t)src[4 * i] | ((uint32_t)src[4 * i + 1] << 8) | ((uint32_t)src[4 * i + 2] << 16) |
+                             ((uint32_t)src[4 * i + 3] << 24);
+                out[i] = bits_to_f32(u);
+            }
+            return 0;
+        case GGML_F16:
+            for (size_t i = 0; i < n; i++) out[i] = f16_bits_at(src, 2 * i);
+            return 0;
+        case GGML_BF16:
+            for (size_t i = 0; i < n; i++) out[i] = bf16_to_f32((uint16_t)(src[2 * i] | (src[2 * i + 1] << 8)));
+            return 0;
+        case GGML_Q8_0:
+            for (size_t b = 0; b < n / 32; b++) {
+                const uint8_t* blk = src + b * 34;
+                float d = f16_bits_at(blk, 0);
+                float* y = out + b * 32;
+                for (size_t j = 0; j < 32; j++) y[j] = (float)(int8_t)blk[2 + j] * d;
+            }
+            return 0;
+        case GGML_Q4_K:
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 144;
+                float d = f16_bits_at(blk, 0);
+                float dmin = f16_bits_at(blk, 2);
+                const uint8_t* scales = blk + 4;
+                const uint8_t* qs = blk + 16;
+                float* y = out + b * 256;
+                size_t is = 0;
+                for (size_t j = 0; j < 256; j += 64) {
+                    const uint8_t* q = qs + j / 2;
+                    uint8_t sc, m;
+                    scale_min_k4(is, scales, &sc, &m);
+                    float d1 = d * (float)sc, m1 = dmin * (float)m;
+                    scale_min_k4(is + 1, scales, &sc, &m);
+                    float d2 = d * (float)sc, m2 = dmin * (float)m;
+                    for (size_t l = 0; l < 32; l++) {
+                        float lo = d1 * (float)(q[l] & 0x0F);
+                        float hi = d2 * (float)(q[l] >> 4);
+                        y[j + l] = lo - m1;
+                        y[j + 32 + l] = hi - m2;
+                    }
+                    is += 2;
+                }
+            }
+            return 0;
+    }
+    return -2;
+}
+
+// Second, independently written decoder: random access to one element, the
+// index form of src/gpu/kernels.metal:77-81 (Q8_0) and :889-904 (Q4_K) with
+// its own scale unpack (:108-116). Used to cross-check the sequential decode.
+ORACLE_API float lokal_ref_dequant_elem(uint32_t ty, const uint8_t* row, size_t col) {
+    if (ty == GGML_Q8_0) {
+        const uint8_t* b = row + (col >> 5) * 34;
+        uint16_t hb = (uint16_t)(b[0] | (b[1] << 8));
+        float d = f16_to_f32(hb);
+        int q = (int)b[2 + (col & 31)];
+        if (q > 127) q -= 256;
+        return (float)q * d;
+    }
+    if (ty == GGML_Q4_K) {
+        const uint8_t* b = row + (col >> 8) * 144;
+        float d = f16_to_f32((uint16_t)(b[0] | (b[1] << 8)));
+        float dmin = f16_to_f32((uint16_t)(b[2] | (b[3] << 8)));
+        const uint8_t* s = b + 4;
+        size_t ib = col & 255;
+        size_t j = ib >> 5;
+        unsigned sc, mn;
+        if (j < 4) {
+            sc = s[j] & 63u;
+            mn = s[j + 4] & 63u;
+        } else {
+            sc = (s[j + 4] & 0xFu) | ((unsigned)(s[j - 4] >> 6) << 4);
+            mn = ((unsigned)s[j + 4] >> 4) | ((unsigned)(s[j] >> 6) << 4);
+        }
+        float d1 = d * (float)sc;
+        float m1 = dmin * (float)mn;
+        uint8_t byte = b[16 + (ib >> 6) * 32 + (ib & 31)];
+        unsigned q = (ib & 32) ? (unsigned)(byte >> 4) : (unsigned)(byte & 0xF);
+        float p = d1 * (float)q;
+        return p - m1;
+    }
+    if (ty == GGML_F16) return f16_to_f32((uint16_t)(row[2 * col] | (row[2 * col + 1] << 8)));
+    if (ty == GGML_BF16) return bf16_to_f32((uint16_t)(row[2 * col] | (row[2 * col + 1] << 8)));
+    if (ty == GGML_F32) {
+        uint32_t u;
+        std::memcpy(&u, row + 4 * col, 4);
+        return bits_to_f32(u);
+    }
+    return std::nanf("");
+}
+
+// Embedding gather with per-row dequant (src/lowmem/forward.rs:275-307; row
+// lookup and range check src/lowmem/mod.rs:654-668). Returns 0, or 1 + the
+// index of the first id that is out of range (the reference returns Err).
+ORACLE_API int64_t lokal_ref_embed_gather(const uint8_t* table, uint32_t ty, size_t vocab, size_t dim,
+                                          const uint32_t* ids, size_t n, float* out, int threads) {
+    size_t rb = lokal_ref_row_bytes(ty, dim);
+    if (rb == 0) return -1;
+    for (size_t i = 0; i < n; i++) {
+        if ((size_t)ids[i] + 1 > vocab) return (int64_t)i + 1;
+    }
+    parallel_rows(n, threads, [=](size_t i0, size_t i1) {
+        for (size_t i = i0; i < i1; i++) {
+            lokal_ref_dequant_row(ty, table + (size_t)ids[i] * rb, rb, out + i * dim, dim);
+        }
+    });
+    return 0;
+}
+
+// Adversarial block generator of the reference's bit-for-bit dequant gate
+// (src/lowmem/pool.rs:1079-1195), Q8_0 and Q4_K arms: block variant
+// (row*n_blocks+blk)%4 in {all zero, LCG bytes + smallest subnormal scale,
+// LCG bytes + negative subnormal scale, LCG bytes + max f16 scale with
+// max-magnitude quants}. `out` holds n_rows*n_blocks*blk_bytes bytes.
+ORACLE_API int lokal_ref_adversarial_rows(uint32_t ty, size_t n_blocks, size_t n_rows, uint8_t* out) {
+    if (ty != GGML_Q8_0 && ty != GGML_Q4_K) return -2;
+    size_t bb = lokal_ref_blk_bytes(ty);
+    uint32_t lcg = 0x2545F491u;
+    const uint8_t scale_bytes[4][2] = {{0x00, 0x00}, {0x01, 0x00}, {0xFF, 0x83}, {0xFF, 0x7B}};
+    for (size_t row = 0; row < n_rows; row++) {
+        for (size_t blk = 0; blk < n_blocks; blk++) {
+            size_t variant = (row * n_blocks + blk) % 4;
+            uint8_t* b = out + (row * n_blocks + blk) * bb;
+            std::memset(b, 0, bb);
+            if (variant == 0) continue;
+            for (size_t i = 0; i < bb; i++) {
+                lcg = lcg * 1664525u + 1013904223u;
+                b[i] = (uint8_t)(lcg >> 16);
+            }
+            b[0] = scale_bytes[variant][0];
+            b[1] = scale_bytes[variant][1];
+            if (ty == GGML_Q4_K) {
+                b[2] = scale_bytes[3 - variant + 1][0];
+                b[3] = scale_bytes[3 - variant + 1][1];
+            }
+            if (variant == 3) {
+                if (ty == GGML_Q8_0) std::memset(b + 2, 0x80, 32);
+                else std::memset(b + 4, 0xFF, 140);
+            }
+        }
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Timed CPU baseline: the per-token layer ops of one forward pass, in the
+// order src/model.rs:205-256 runs them, with the projections and attention
+// (out of scope) replaced by caller-provided buffers. Each worker walks its
+// tokens one at a time through all layers, allocating a fresh vector per op
+// as the reference does (src/math.rs:48, src/model.rs:247).
+// ---------------------------------------------------------------------------
+
+struct LayerPassArgs {
+    uint64_t rows, layers, hidden, inter, n_q_heads, n_kv_heads, head_dim;
+    float eps, theta;
+    int32_t has_bias, has_qk_norm;
+    const int32_t* positions;  // null -> pos0 + row
+    int64_t pos0;
+    // tables / weights
+    const uint8_t* embed_table;  // may be null (x starts from x0)
+    uint32_t embed_type;
+    uint64_t vocab;
+    const uint32_t* ids;
+    const float* norm_w;     // [layers][2][hidden]
+    const float* final_w;    // [hidden]
+    const float* q_bias;     // [layers][nq*hd] or null
+    const float* k_bias;     // [layers][nkv*hd] or null
+    const float* q_norm_w;   // [layers][hd] or null
+    const float* k_norm_w;   // [layers][hd] or null
+    // per-layer activations produced by the out-of-scope projections,
+    // indexed [layer][row][...]; layer stride given in elements
+    const float* delta_att;  // [layers][rows][hidden]
+    const float* delta_mlp;  // [layers][rows][hidden]
+    const float* q;          // [layers][rows][nq*hd]
+    const float* k;          // [layers][rows][nkv*hd]
+    const float* gate;       // [layers][rows][inter]
+    const float* up;         // [layers][rows][inter]
+    uint64_t layer_period;   // layers of distinct data; layer l uses l % layer_period
+    float* out;              // [rows][hidden] final normed hidden
+    float* sink;             // [threads] checksum so nothing is optimised away
+};
+
+ORACLE_API void lokal_ref_layer_pass(const LayerPassArgs* ap, int threads) {
+    const LayerPassArgs a = *ap;
+    size_t H = a.hidden, I = a.inter, QD = a.n_q_heads * a.head_dim, KD = a.n_kv_heads * a.head_dim;
+    std::vector<float> sinks((size_t)(threads > 0 ? threads : 1), 0.0f);
+    size_t nt = threads > 1 ? (size_t)threads : 1;
+    size_t per = (a.rows + nt - 1) / nt;
+    auto work = [&](size_t tix, size_t r0, size_t r1) {
+        float sink = 0.0f;
+        size_t rb = a.embed_table ? lokal_ref_row_bytes(a.embed_type, H) : 0;
+        for (size_t r = r0; r < r1; r++) {
+            size_t pos = a.positions ? (size_t)a.positions[r] : (size_t)(a.pos0 + (int64_t)r);
+            std::vector<float> x(H, 0.0f);
+            if (a.embed_table) lokal_ref_dequant_row(a.embed_type, a.embed_table + (size_t)a.ids[r] * rb, rb, x.data(), H);
+            for (size_t l = 0; l < a.layers; l++) {
+                size_t ld = l % a.layer_period;
+                // input norm (the residual from the previous MLP was added below)
+                std::vector<float> xn(H);
+                ref_rmsnorm(x.data(), a.norm_w + (l * 2 + 0) * H, a.eps, H, xn.data());
+                sink += xn[0];
+                // q / k: bias, per-head norm, rope
+                std::vector<float> q(a.q + (ld * a.rows + r) * QD, a.q + (ld * a.rows + r) * QD + QD);
+                std::vector<float> k(a.k + (ld * a.rows + r) * KD, a.k + (ld * a.rows + r) * KD + KD);
+                if (a.has_bias) {
+                    const float* qb = a.q_bias + l * QD;
+                    const float* kb = a.k_bias + l * KD;
+                    for (size_t i = 0; i < QD; i++) q[i] += qb[i];
+                    for (size_t i = 0; i < KD; i++) k[i] += kb[i];
+                }
+                if (a.has_qk_norm) {
+                    for (size_t h = 0; h < a.n_q_heads; h++) {
+                        std::vector<float> normed(a.head_dim);
+                        ref_rmsnorm(q.data() + h * a.head_dim, a.q_norm_w + l * a.head_dim, a.eps, a.head_dim, normed.data());
+                        std::memcpy(q.data() + h * a.head_dim, normed.data(), a.head_dim * 4);
+                    }
+                    for (size_t h = 0; h < a.n_kv_heads; h++) {
+                        std::vector<float> normed(a.head_dim);
+                        ref_rmsnorm(k.data() + h * a.head_dim, a.k_norm_w + l * a.head_dim, a.eps, a.head_dim, normed.data());
+                        std::memcpy(k.data() + h * a.head_dim, normed.data(), a.head_dim * 4);
+                    }
+                }
+                ref_rope(q.data(), QD, pos, a.head_dim, a.head_dim, a.theta);
+                ref_rope(k.data(), KD, pos, a.head_dim, a.head_dim, a.theta);
+                sink += q[0] + k[0];
+                // attention residual
+                const float* da = a.delta_att + (ld * a.rows + r) * H;
+                for (size_t i = 0; i < H; i++) x[i] += da[i];
+                // post-attention norm
+                std::vector<float> xn2(H);
+                ref_rmsnorm(x.data(), a.norm_w + (l * 2 + 1) * H, a.eps, H, xn2.data());
+                sink += xn2[0];
+                // SwiGLU
+                const float* g = a.gate + (ld * a.rows + r) * I;
+                const float* u = a.up + (ld * a.rows + r) * I;
+                std::vector<float> inner(I);
+                for (size_t i = 0; i < I; i++) inner[i] = ref_silu(g[i]) * u[i];
+                sink += inner[0];
+                // MLP residual
+                const float* dm = a.delta_mlp + (ld * a.rows + r) * H;
+                for (size_t i = 0; i < H; i++) x[i] += dm[i];
+            }
+            ref_rmsnorm(x.data(), a.final_w, a.eps, H, a.out + r * H);
+        }
+        sinks[tix] = sink;
+    };
+    if (nt == 1) {
+        work(0, 0, a.rows);
+    } else {
+        std::vector<std::thread> pool;
+        for (size_t t = 0; t < nt; t++) {
+            size_t r0 = t * per, r1 = r0 + per < a.rows ? r0 + per : a.rows;
+            if (r0 >= r1) break;
+            pool.emplace_back(work, t, r0, r1);
+        }
+        for (auto& th : pool) th.join();
+    }
+    if (a.sink) {
+        float s = 0;
+        for (float v : sinks) s += v;
+        *a.sink = s;
+    }
+}
+
+ORACLE_API unsigned lokal_ref_hardware_threads(void) { return std::thread::hardware_concurrency(); }

@@ -1,0 +1,106 @@
+"""The C ABI without a GPU: the library loads, exports every symbol the header declares, the ctypes
+mirror of the parameter struct matches the header field for field, and host-only helpers behave."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import lokal_b200
+from lokal_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = open(os.path.join(ROOT, "include", "lokal_cuda.h")).read()
+
+
+def declared_functions():
+    return re.findall(r"LOKAL_API\s+[\w\s\*]+?\b(lokal_cuda_\w+)\s*\(", HEADER)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = capi.load()
+    names = declared_functions()
+    assert len(names) >= 30 and len(set(names)) == len(names)
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/lokal_cuda.h but not exported"
+    assert set(names) == set(capi.SIGNATURES), "ctypes signatures and the header disagree"
+
+
+def test_param_struct_mirror_matches_header():
+    # the same guard the reference keeps between its shader structs and their Rust mirrors
+    # (src/gpu/metal.rs:4448-4589), here between the C header and the ctypes binding
+    body = re.search(r"typedef struct lokal_qk_rope_params \{(.*?)\} lokal_qk_rope_params;", HEADER, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    ctype = {"void*": C.c_void_p, "const void*": C.c_void_p, "const float*": C.c_void_p, "const uint32_t*": C.c_void_p,
+             "uint64_t": C.c_uint64, "uint32_t": C.c_uint32, "float": C.c_float, "int32_t": C.c_int32}
+    for stmt in body.split(";"):
+        stmt = " ".join(stmt.split())
+        if not stmt:
+            continue
+        m = re.match(r"((?:const )?\w+\*?)\s+(.*)", stmt)
+        ty, names = m.group(1), [n.strip() for n in m.group(2).split(",")]
+        for n in names:
+            fields.append((n, ctype[ty]))
+    assert fields == [(n, t) for n, t in capi.QkRopeParams._fields_]
+    assert C.sizeof(capi.QkRopeParams) == 10 * 8 + 8 + 4 * 4 + 4 * 8 + 4 + 3 * 4
+
+
+def test_enums_match_header_and_gguf_ids():
+    for name, val in re.findall(r"(LOKAL_(?:ERR_)?\w+) = (\d+)", HEADER):
+        if name.startswith("LOKAL_ERR") or name == "LOKAL_OK":
+            assert getattr(capi, name[len("LOKAL_"):]) == int(val)
+    assert (capi.F32, capi.F16, capi.Q8_0, capi.Q4_K, capi.BF16) == (0, 1, 8, 12, 30)  # src/gguf/dequant.rs:21-41
+
+
+def test_block_geometry_matches_reference_table():
+    # src/gguf/dequant.rs:567-577
+    assert lokal_b200.blk_bytes(capi.Q8_0) == 34 and lokal_b200.blk_bytes(capi.Q4_K) == 144
+    assert lokal_b200.blk_elems(capi.Q8_0) == 32 and lokal_b200.blk_elems(capi.Q4_K) == 256
+    assert lokal_b200.row_bytes(capi.Q4_K, 512) == 288 and lokal_b200.row_bytes(capi.Q8_0, 896) == 952
+    assert lokal_b200.row_bytes(capi.F16, 10) == 20 and lokal_b200.row_bytes(capi.BF16, 10) == 20
+    assert lokal_b200.blk_elems(14) == 0 and lokal_b200.row_bytes(14, 256) == 0
+
+
+def test_shard_rows_partitions_every_row_once():
+    for n_rows in (0, 1, 7, 8, 255, 256, 8192, 65536):
+        for g in (1, 2, 3, 4, 8):
+            spans = [lokal_b200.shard_rows(n_rows, g, r) for r in range(g)]
+            assert sum(c for _, c in spans) == n_rows
+            pos = 0
+            for r0, c in spans:
+                assert r0 == pos or c == 0
+                pos += c
+            assert max(c for _, c in spans) - min(c for _, c in spans) <= -(-n_rows // g)
+    assert lokal_b200.shard_rows(8192, 8, 3) == (3072, 1024)
+    with pytest.raises(lokal_b200.LokalCudaError):
+        lokal_b200.shard_rows(10, 0, 0)
+    with pytest.raises(lokal_b200.LokalCudaError):
+        lokal_b200.shard_rows(10, 2, 2)
+
+
+def test_no_cpu_fallback_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    assert capi.load().lokal_cuda_device_count() == 0
+    with pytest.raises(lokal_b200.LokalCudaError) as e:
+        lokal_b200.Context(0)
+    assert e.value.status == capi.ERR_NO_DEVICE
+
+
+def test_null_context_is_refused_not_dereferenced():
+    lib = capi.load()
+    assert lib.lokal_cuda_stream_sync(None, None) == capi.ERR_BAD_ARG
+    assert lib.lokal_cuda_swiglu(None, None, None, None, None, None, 0, 0, 0) == capi.ERR_BAD_ARG
+    assert lib.lokal_cuda_last_error(None) == b"null context"
+    assert b"sm_100a" in lib.lokal_cuda_version()
+
+
+def test_product_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "lokal_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("lm_dequant_oracle", ""), f"{f} mentions the oracle"

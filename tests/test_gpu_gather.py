@@ -1,0 +1,208 @@
+"""Embedding gather + GGUF row dequant through the C ABI: bit-exact against the CPU oracle."""
+import numpy as np
+import pytest
+
+import synth
+from synth import BF16, F16, F32, Q4_K, Q8_0
+
+pytestmark = pytest.mark.gpu
+
+
+def f16b(v):
+    return np.array([v], np.float16).view(np.uint8)
+
+
+def gather(ctx, dev, table, ty, vocab, dim, ids, out_dtype=F32):
+    dt = dev.put(table)
+    di = dev.put(np.asarray(ids, np.uint32))
+    out = dev.empty((len(ids) + 1, dim), out_dtype, fill=4.0)
+    ctx.embed_gather(dt, di, out, ggml_type=ty, vocab=vocab, dim=dim, n=len(ids), out_dtype=out_dtype)
+    ctx.stream_sync()
+    res = dev.get(out)
+    assert (res[-1] == 4.0).all(), "wrote past the last row"
+    return res[:-1]
+
+
+def dequant(ctx, dev, src, ty, rows, cols, out_dtype=F32):
+    out = dev.empty((rows, cols), out_dtype, fill=4.0)
+    ctx.dequant_rows(dev.put(src), out, ggml_type=ty, rows=rows, cols=cols, out_dtype=out_dtype)
+    ctx.stream_sync()
+    return dev.get(out)
+
+
+def test_reference_hand_vectors(ctx, dev):
+    # src/gguf/dequant.rs:683-692
+    blk = np.zeros(34, np.uint8)
+    blk[:2] = f16b(0.5)
+    blk[2] = np.uint8(256 - 7)
+    blk[33] = 100
+    y = dequant(ctx, dev, blk, Q8_0, 1, 32)[0]
+    assert y[0] == -3.5 and y[31] == 50.0 and (y[1:31] == 0).all()
+    # src/gguf/dequant.rs:714-730
+    blk = np.zeros(144, np.uint8)
+    blk[:2] = f16b(1.0)
+    blk[2:4] = f16b(0.5)
+    blk[4], blk[8], blk[16] = 3, 2, 0x51
+    y = dequant(ctx, dev, blk, Q4_K, 1, 256)[0]
+    assert y[0] == 2.0 and y[1] == -1.0 and y[32] == 0.0
+
+
+@pytest.mark.parametrize("ty", [Q8_0, Q4_K])
+@pytest.mark.parametrize("out_dtype", [F32, F16, BF16])
+def test_adversarial_blocks_bit_for_bit(ctx, dev, oracle, ty, out_dtype):
+    # src/lowmem/pool.rs:1079-1195: zero blocks, subnormal scales of both signs, max f16 scale with
+    # max-magnitude quants, dense LCG bytes; 8 blocks x 3 rows as in the reference's gate.
+    nb, rows = 8, 3
+    cols = nb * oracle.blk_elems(ty)
+    src = oracle.adversarial_rows(ty, nb, rows)
+    rb = oracle.row_bytes(ty, cols)
+    want = np.stack([oracle.dequant_row_ref(ty, src[r * rb:(r + 1) * rb], cols) for r in range(rows)])
+    assert np.abs(want).max() > 1e6 and (want == 0).mean() > 0.2  # the recipe's extremes are present
+    got = dequant(ctx, dev, src, ty, rows, cols, out_dtype)
+    assert np.abs(got[np.isfinite(got)]).max() > 0, "all zeros: the kernel did not run"
+    if out_dtype == F32:
+        synth.assert_bits_equal(got, want, "adversarial rows")
+    else:
+        # the exact f32 value rounded once (overflow to inf included)
+        with np.errstate(over="ignore"):
+            synth.assert_bits_equal(got, synth.round_to(want, out_dtype), "adversarial rows, 16-bit out")
+    # the same rows gathered in scrambled order with repeats
+    ids = np.array([2, 0, 1, 1, 2, 0, 0], np.uint32)
+    g = gather(ctx, dev, src, ty, rows, cols, ids, F32)
+    synth.assert_bits_equal(g, want[ids], "gather of adversarial rows")
+
+
+def test_negative_control_scale_unpack_bug_is_seen(ctx, dev, oracle):
+    # The reference plants q[j+4] for q[j] in the Q4_K min unpack and requires its gate to fail
+    # (src/lowmem/pool.rs:597-599). Same here, with the bug planted in a copy of the expected values.
+    nb, rows = 8, 3
+    src = oracle.adversarial_rows(Q4_K, nb, rows)
+    got = dequant(ctx, dev, src, Q4_K, rows, nb * 256)
+
+    def buggy_row(row):
+        out = np.empty(nb * 256, np.float32)
+        for b in range(nb):
+            blk = row[b * 144:(b + 1) * 144]
+            d = np.float32(blk[0:2].view(np.float16)[0])
+            dmin = np.float32(blk[2:4].view(np.float16)[0])
+            s = blk[4:16].astype(np.uint32)
+            for j in range(8):
+                if j < 4:
+                    sc, mn = s[j] & 63, s[j + 4] & 63
+                else:
+                    sc = (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4)
+                    mn = (s[j + 4] >> 4) | ((s[j + 4] >> 6) << 4)  # bug: q[j+4] where q[j] belongs
+                q = blk[16 + (j // 2) * 32:16 + (j // 2) * 32 + 32]
+                q = (q >> 4) if j & 1 else (q & 0xF)
+                with np.errstate(over="ignore", invalid="ignore"):
+                    out[b * 256 + j * 32:b * 256 + j * 32 + 32] = (d * np.float32(sc)) * q.astype(np.float32) - dmin * np.float32(mn)
+        return out
+    rb = nb * 144
+    wrong = np.stack([buggy_row(src[r * rb:(r + 1) * rb]) for r in range(rows)])
+    with pytest.raises(AssertionError):
+        synth.assert_bits_equal(got, wrong, "planted bug")
+
+
+@pytest.mark.parametrize("ty,dim", [(Q8_0, 896), (Q8_0, 32), (Q8_0, 2048), (Q4_K, 1024), (Q4_K, 768), (Q4_K, 256)])
+@pytest.mark.parametrize("out_dtype", [F32, F16])
+def test_random_tables(ctx, dev, oracle, ty, dim, out_dtype):
+    vocab = 1531
+    table = (synth.q8_0_table if ty == Q8_0 else synth.q4_k_table)(vocab, dim, seed=dim + ty)
+    ids = np.concatenate([synth.token_ids_zipf(vocab, 3000, seed=7), [vocab - 1, 0, vocab - 1, 1, vocab - 2]]).astype(np.uint32)
+    want = oracle.embed_gather(table, ty, vocab, dim, ids)
+    got = gather(ctx, dev, table, ty, vocab, dim, ids, out_dtype)
+    if out_dtype == F32:
+        synth.assert_bits_equal(got, want, "gather")
+    else:
+        synth.assert_bits_equal(got, synth.round_to(want, out_dtype), "gather, f16 out")
+
+
+@pytest.mark.parametrize("ty", [F32, F16, BF16])
+@pytest.mark.parametrize("out_dtype", [F32, F16, BF16])
+@pytest.mark.parametrize("dim", [576, 50])
+def test_float_tables(ctx, dev, oracle, ty, out_dtype, dim):
+    vocab = 700
+    t32 = synth.round_to(synth.f32_table(vocab, dim, seed=3, std=0.02), ty)
+    raw = t32 if ty == F32 else dev.bits16(dev.put(t32, ty))
+    ids = synth.token_ids_uniform(vocab, 500, seed=4)
+    want = oracle.embed_gather(np.ascontiguousarray(raw).view(np.uint8).reshape(-1), ty, vocab, dim, ids)
+    synth.assert_bits_equal(want, t32[ids], "oracle widening is exact")
+    dt = dev.put(t32, ty)
+    out = dev.empty((500, dim), out_dtype, fill=0.0)
+    ctx.embed_gather(dt, dev.put(ids), out, ggml_type=ty, vocab=vocab, dim=dim, n=500, out_dtype=out_dtype)
+    ctx.stream_sync()
+    synth.assert_bits_equal(dev.get(out), synth.round_to(want, out_dtype), "float table gather")
+
+
+def test_out_of_range_id_is_reported_and_zero_filled(ctx, dev, oracle):
+    import lokal_b200 as L
+    vocab, dim = 64, 128
+    table = synth.q8_0_table(vocab, dim, seed=1)
+    ids = np.array([3, 64, 5, 4000000000], np.uint32)
+    with pytest.raises(IndexError):
+        oracle.embed_gather(table, Q8_0, vocab, dim, ids)  # the reference returns Err (src/lowmem/mod.rs:662-664)
+    dt, di = dev.put(table), dev.put(ids)
+    out = dev.empty((4, dim), F32, fill=9.0)
+    ctx.embed_gather(dt, di, out, ggml_type=Q8_0, vocab=vocab, dim=dim, n=4)
+    with pytest.raises(L.LokalCudaError) as e:
+        ctx.stream_sync()
+    assert e.value.status == L.capi.ERR_ID_RANGE
+    got = dev.get(out)
+    want = oracle.embed_gather(table, Q8_0, vocab, dim, ids[[0, 2]])
+    synth.assert_bits_equal(got[[0, 2]], want, "valid rows")
+    assert (got[[1, 3]] == 0).all()
+    ctx.stream_sync()  # the error word was cleared; the context stays usable
+    for ty, tab in ((F32, np.zeros((vocab, dim), np.float32)),):
+        ctx.embed_gather(dev.put(tab), di, out, ggml_type=ty, vocab=vocab, dim=dim, n=4)
+        with pytest.raises(L.LokalCudaError):
+            ctx.stream_sync()
+
+
+def test_refusals(ctx, dev):
+    import lokal_b200 as L
+    t = dev.put(np.zeros(34 * 4, np.uint8))
+    ids = dev.put(np.zeros(2, np.uint32))
+    out = dev.empty((2, 64), F32)
+    for kw, status in [
+        (dict(ggml_type=14, dim=256), L.capi.ERR_UNSUPPORTED),   # Q6_K: not on this path yet, refused by name
+        (dict(ggml_type=Q8_0, dim=48), L.capi.ERR_BAD_ARG),      # not whole blocks (src/gguf/container.rs:220-226)
+        (dict(ggml_type=Q4_K, dim=896), L.capi.ERR_BAD_ARG),     # 3.5 super-blocks cannot exist
+        (dict(ggml_type=Q8_0, dim=64, out_dtype=Q8_0), L.capi.ERR_UNSUPPORTED),
+    ]:
+        with pytest.raises(L.LokalCudaError) as e:
+            ctx.embed_gather(t, ids, out, vocab=2, n=2, **kw)
+        assert e.value.status == status, kw
+    with pytest.raises(L.LokalCudaError):
+        ctx.embed_gather(t, None, out, ggml_type=Q8_0, vocab=2, dim=64, n=2)
+    ctx.embed_gather(t, ids, out, ggml_type=Q8_0, vocab=2, dim=64, n=0)
+
+
+def test_full_size_zipf_gather_q8_0(ctx, dev, oracle):
+    # 151936 x 896 Q8_0 table, 65536 ids from Zipf(1.1): bit-exact in f32 and f16
+    vocab, dim, n = synth.C4_VOCAB, synth.C4_DIM_Q8, synth.C4_IDS
+    table = synth.q8_0_table(vocab, dim, synth.C4_SEED)
+    ids = synth.token_ids_zipf(vocab, n, synth.C4_SEED)
+    want = oracle.embed_gather(table, Q8_0, vocab, dim, ids, threads=8)
+    dt, di = dev.put(table), dev.put(ids)
+    out = dev.empty((n, dim), F32, fill=1.0)
+    ctx.embed_gather(dt, di, out, ggml_type=Q8_0, vocab=vocab, dim=dim, n=n)
+    ctx.stream_sync()
+    synth.assert_bits_equal(dev.get(out), want, "full-size Q8_0 gather")
+    out16 = dev.empty((n, dim), F16, fill=1.0)
+    ctx.embed_gather(dt, di, out16, ggml_type=Q8_0, vocab=vocab, dim=dim, n=n, out_dtype=F16)
+    ctx.stream_sync()
+    synth.assert_bits_equal(dev.get(out16), synth.round_to(want, F16), "full-size Q8_0 gather, f16 out")
+
+
+def test_full_size_zipf_gather_q4_k(ctx, dev, oracle):
+    # Q4_K super-blocks hold 256 elements, so the 896-wide table of the benchmark cannot exist
+    # (the reference refuses it at open); the table is 151936 x 1024 instead.
+    vocab, dim, n = synth.C4_VOCAB, synth.C4_DIM_Q4K, synth.C4_IDS
+    table = synth.q4_k_table(vocab, dim, synth.C4_SEED + 1)
+    ids = synth.token_ids_zipf(vocab, n, synth.C4_SEED + 1)
+    want = oracle.embed_gather(table, Q4_K, vocab, dim, ids, threads=8)
+    dt, di = dev.put(table), dev.put(ids)
+    out = dev.empty((n, dim), F32, fill=1.0)
+    ctx.embed_gather(dt, di, out, ggml_type=Q4_K, vocab=vocab, dim=dim, n=n)
+    ctx.stream_sync()
+    synth.assert_bits_equal(dev.get(out), want, "full-size Q4_K gather")
