@@ -1,0 +1,464 @@
+#!/usr/bin/env python
+"""Benchmark of the fused per-token layer ops on B200 (one process per GPU).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c2|c1|c3] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+A step is one pass of the hot path over one batch of token rows: embedding gather (Q8_0 table), the rope table, and
+for each layer qk-norm/bias + RoPE, two residual-add + RMSNorm, and SwiGLU (lokal_cuda_pass_*). The projections and
+attention between them are out of scope, so their outputs are synthetic tensors, distinct per layer, resident in HBM
+(several GB per step, far larger than L2). `value` times the step with inputs resident on the device (one CUDA graph
+per step); `e2e` times the same step through lokal_cuda_pass_run_host with all inputs in pinned host memory and the
+result copied back. Rows are sharded over GPUs with no collective on the path (weak scaling: every GPU gets a full
+batch). Rank 0 prints ONE JSON line.
+
+--impl reference times the reference's own CPU algorithm for the same step (the C++ restatement in oracle/, all host
+threads, f32 as the reference computes) on a bounded sample of the rows.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import synth  # noqa: E402  (workload shapes and seeded generators)
+
+METRIC = "fused per-token layer ops (embed gather + per layer: qk-norm/bias+RoPE, 2x residual-add+RMSNorm, SwiGLU), tokens/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def embed_dim_ok(cfg):
+    return cfg.hidden % 32 == 0
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, cuda_index: int):
+        super().__init__(daemon=True)
+        self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            props = torch.cuda.get_device_properties(cuda_index)
+            h = None
+            try:
+                bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+                h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+            self.h = h
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                try:
+                    bits = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    bits = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for b, name in self.REASONS.items():
+                    if bits & b:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def finish(self):
+        self._stop.set()
+        if self.is_alive():
+            self.join(2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU algorithm (oracle port) on the host cores
+# ------------------------------------------------------------------------------------------------
+
+def cpu_inputs(cfg, rows, period, seed):
+    """f32 host inputs for `rows` token rows and `period` layers of distinct data (the reference computes in f32)."""
+    rng = np.random.default_rng(seed)
+    f = lambda *s, sc=1.0: rng.standard_normal(s, dtype=np.float32) * np.float32(sc)
+    L = cfg.layers
+    return dict(
+        norm_w=1 + f(L, 2, cfg.hidden, sc=0.1), final_w=1 + f(cfg.hidden, sc=0.1),
+        q_bias=f(L, cfg.q_dim, sc=0.1), k_bias=f(L, cfg.kv_dim, sc=0.1),
+        q_norm_w=1 + f(L, cfg.head_dim, sc=0.1), k_norm_w=1 + f(L, cfg.head_dim, sc=0.1),
+        delta_att=f(period, rows, cfg.hidden), delta_mlp=f(period, rows, cfg.hidden),
+        q=f(period, rows, cfg.q_dim), k=f(period, rows, cfg.kv_dim),
+        gate=f(period, rows, cfg.inter, sc=2.0), up=f(period, rows, cfg.inter, sc=2.0))
+
+
+def cpu_step_fn(cfg, rows, table, vocab, seed=1):
+    """Returns (run(threads) -> seconds, description) for one CPU step over `rows` rows."""
+    from oracle import lokal_oracle as O
+    period = 2
+    a = cpu_inputs(cfg, rows, period, seed)
+    ids = synth.token_ids_zipf(vocab, rows, seed)
+    pos = (np.random.default_rng(seed).integers(0, cfg.decode_positions, rows, dtype=np.int32)
+           if cfg.decode_positions else None)
+    out = np.zeros((rows, cfg.hidden), np.float32)
+    sink = np.zeros(1, np.float32)
+    args = O.LayerPassArgs(rows=rows, layers=cfg.layers, hidden=cfg.hidden, inter=cfg.inter, n_q_heads=cfg.n_q_heads,
+                           n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, eps=cfg.eps, theta=cfg.theta,
+                           has_bias=int(cfg.qk_bias), has_qk_norm=int(cfg.qk_norm),
+                           positions=None if pos is None else pos.ctypes.data, pos0=0,
+                           embed_table=table.ctypes.data, embed_type=O.Q8_0, vocab=vocab, ids=ids.ctypes.data,
+                           layer_period=period, out=out.ctypes.data, sink=sink.ctypes.data,
+                           **{k: v.ctypes.data for k, v in a.items()})
+    keep = (a, ids, pos, out, sink, table)
+
+    def run(threads):
+        t0 = time.perf_counter()
+        O.layer_pass(args, threads)
+        _ = keep
+        return time.perf_counter() - t0
+    return run
+
+
+def reference_arm(args, cfg, rank, world):
+    if rank != 0:
+        return
+    from oracle import lokal_oracle as O
+    O.build()
+    threads = O.hardware_threads()
+    vocab = min(cfg.vocab, 32768)  # the table only feeds one row per token; a smaller table keeps set-up short
+    table = synth.q8_0_table(vocab, cfg.hidden, cfg.seed)
+    # calibrate on a small probe, then size the per-step sample for about 2 s of wall time
+    probe_rows = min(cfg.rows, 4 * threads)
+    probe = cpu_step_fn(cfg, probe_rows, table, vocab)
+    probe(threads)
+    dt = probe(threads)
+    rows = int(min(cfg.rows, max(threads, probe_rows * 2.0 / max(dt, 1e-6))))
+    rows = max(threads, rows // threads * threads)
+    step = cpu_step_fn(cfg, rows, table, vocab)
+    for _ in range(args.warmup):
+        step(threads)
+    times = [step(threads) for _ in range(args.steps)]
+    total = float(sum(times))
+    value = rows * args.steps / total
+    sample = (f"{rows} of {cfg.rows} token rows per step, all {cfg.layers} layers, f32, {threads} threads "
+              f"(token-parallel; per-layer inputs cycle over 2 distinct layers of data)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, cfg.rows, args),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, rows_per_gpu, args):
+    return {"workload": cfg.name, "rows_per_gpu": rows_per_gpu, "layers": cfg.layers, "hidden": cfg.hidden,
+            "intermediate": cfg.inter, "q_heads": cfg.n_q_heads, "kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
+            "qk_norm": cfg.qk_norm, "qk_bias": cfg.qk_bias, "embed_table": f"Q8_0 {cfg.vocab}x{cfg.hidden}",
+            "sharding": f"token rows over {args.gpus} GPU(s), no collective on the path",
+            "l2": "per-layer inputs and outputs are distinct buffers, several GB per step, far larger than the 126 MB L2"}
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+
+def ours(args, cfg, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import lokal_b200 as L
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = L.Context(local_rank)
+    tdt = {L.F32: torch.float32, L.F16: torch.float16, L.BF16: torch.bfloat16}[cfg.dtype]
+    es = 2 if cfg.dtype != L.F32 else 4
+    T, H, I, QD, KD, NL = cfg.rows, cfg.hidden, cfg.inter, cfg.q_dim, cfg.kv_dim, cfg.layers
+    if args.scaling == "strong":
+        r0, T = L.shard_rows(cfg.rows, world, rank)
+    else:
+        r0 = rank * T  # weak scaling: rank r owns rows [r*T, (r+1)*T) of a world*T-row job
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(cfg.seed + rank)
+    rn = lambda *shape, s=1.0: (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * s).to(tdt)
+
+    # weights (host, uploaded once by the pass)
+    wrng = np.random.default_rng(cfg.seed)
+    wnp = lambda *shape, s=0.1, one=True: synth.round_to((1.0 if one else 0.0) + wrng.standard_normal(shape, dtype=np.float32) * np.float32(s), cfg.dtype)
+    as_bits = lambda a: (torch.from_numpy(a).to(tdt).contiguous())
+    vocab = cfg.vocab
+    table = synth.q8_0_table(vocab, H, cfg.seed)
+    weights = dict(norm_w=as_bits(wnp(NL, 2, H)), final_w=as_bits(wnp(H)))
+    if cfg.qk_bias:
+        weights.update(q_bias=as_bits(wnp(NL, QD, one=False)), k_bias=as_bits(wnp(NL, KD, one=False)))
+    if cfg.qk_norm:
+        weights.update(q_norm_w=as_bits(wnp(NL, cfg.head_dim)), k_norm_w=as_bits(wnp(NL, cfg.head_dim)))
+    common = dict(max_rows=T, layers=NL, hidden=H, inter=I, n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads,
+                  head_dim=cfg.head_dim, eps=cfg.eps, theta=cfg.theta, dtype=cfg.dtype, w_dtype=cfg.dtype,
+                  embed_type=L.Q8_0, vocab=vocab, embed_table=table, **weights)
+    pass_dev = L.LayerPass(ctx, slots=NL, **common)    # every layer's outputs go to their own buffers
+
+    # device-resident synthetic activations, distinct per layer
+    q = rn(NL, T, QD)
+    k = rn(NL, T, KD)
+    da = rn(NL, T, H)
+    dm = rn(NL, T, H)
+    g = rn(NL, T, I, s=2.0)
+    u = rn(NL, T, I, s=2.0)
+    ids_np = synth.token_ids_zipf(vocab, T, cfg.seed + rank)
+    ids = torch.from_numpy(ids_np.astype(np.int64)).to(dev).to(torch.int32)  # same bits as u32 for ids < 2^31
+    pos = None
+    if cfg.decode_positions:
+        pos = torch.randint(0, cfg.decode_positions, (T,), generator=gen, device=dev, dtype=torch.int32)
+    out = torch.empty(T, H, dtype=tdt, device=dev)
+    inp = L.LayerPass.inputs(ids=ids, rows=T, q=q, k=k, delta_att=da, delta_mlp=dm, gate=g, up=u, positions=pos, pos0=r0,
+                             q_layer_stride=T * QD, k_layer_stride=T * KD, delta_layer_stride=T * H, mlp_layer_stride=T * I)
+    torch.cuda.synchronize()
+
+    stream = ctx.stream_create()
+    tstream = torch.cuda.ExternalStream(stream, device=dev)
+    # one CUDA graph per step ("encode everything, submit once")
+    ctx.graph_begin(stream)
+    pass_dev.run_device(inp, out, stream=stream)
+    graph = ctx.graph_end(stream)
+    launches_per_step = pass_dev.launches
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        ctx.graph_launch(graph, stream)
+    ctx.stream_sync(stream)
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(tstream)
+    for _ in range(args.steps):
+        ctx.graph_launch(graph, stream)
+    e1.record(tstream)
+    ctx.stream_sync(stream)
+    barrier()
+    clocks = sampler.finish() if sampler else None
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    total_rows = T * world
+    value = total_rows / (ms_step * 1e-3)
+
+    # ---- per-kernel timing on this GPU (rank 0 reports): L launches over distinct per-layer buffers ----
+    rb = L.row_bytes(L.Q8_0, H)
+    uniq = int(np.unique(ids_np).size)
+    alg = {
+        "add_rmsnorm": 4 * H * es * T,
+        "qk_rope": (2 * (QD + KD) * es + cfg.head_dim * 4) * T,
+        "swiglu": 3 * I * es * T,
+        "embed_gather": T * (4 + H * es) + uniq * rb,
+    }
+    per_token_layer = 2 * 4 * H * es + (2 * (QD + KD) * es + cfg.head_dim * 4) + 3 * I * es
+    step_bytes = NL * per_token_layer * T + alg["embed_gather"] + 2 * H * es * T + cfg.head_dim * 4 * T
+    kern = {}
+    if rank == 0:
+        xs = rn(NL, T, H)
+        xn = torch.empty(NL, T, H, dtype=tdt, device=dev)
+        inner = torch.empty(NL, T, I, dtype=tdt, device=dev)
+        table_dev = torch.from_numpy(table).to(dev)
+        tab = torch.empty(T, cfg.head_dim, dtype=torch.float32, device=dev)
+        ctx.rope_table(tab, theta=cfg.theta, rot_dim=cfg.head_dim, rows=T, positions=pos, pos0=r0, stream=stream)
+        wn = weights["norm_w"].to(dev)
+        qb = weights["q_bias"].to(dev) if cfg.qk_bias else None
+        kb = weights["k_bias"].to(dev) if cfg.qk_bias else None
+        qn = weights["q_norm_w"].to(dev) if cfg.qk_norm else None
+        kn = weights["k_norm_w"].to(dev) if cfg.qk_norm else None
+        gout = torch.empty(NL if NL < 8 else 8, T, H, dtype=tdt, device=dev)
+
+        def k_norm(l):
+            ctx.add_rmsnorm(xs[l], da[l], wn[l, 1], xn[l], rows=T, dim=H, eps=cfg.eps, dtype=cfg.dtype, w_dtype=cfg.dtype, stream=stream)
+
+        def k_rope(l):
+            p = ctx.qk_rope_params(q=q[l], k=k[l], q_bias=None if qb is None else qb[l], k_bias=None if kb is None else kb[l],
+                                   q_norm_w=None if qn is None else qn[l], k_norm_w=None if kn is None else kn[l], cos_sin=tab,
+                                   rows=T, n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
+                                   eps=cfg.eps, q_dtype=cfg.dtype, w_dtype=cfg.dtype)
+            ctx.qk_rope(p, stream=stream)
+
+        def k_swiglu(l):
+            ctx.swiglu(g[l], u[l], inner[l], n=T * I, dtype=cfg.dtype, stream=stream)
+
+        def k_gather(l):
+            ctx.embed_gather(table_dev, ids, gout[l % gout.shape[0]], ggml_type=L.Q8_0, vocab=vocab, dim=H, n=T, out_dtype=cfg.dtype, stream=stream)
+
+        for name, fn in (("add_rmsnorm", k_norm), ("qk_rope", k_rope), ("swiglu", k_swiglu), ("embed_gather", k_gather)):
+            best = None
+            for rep in range(4):
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record(tstream)
+                for l in range(NL):
+                    fn(l)
+                a1.record(tstream)
+                ctx.stream_sync(stream)
+                if rep:  # first repetition is warm-up
+                    ms = a0.elapsed_time(a1) / NL
+                    best = ms if best is None else min(best, ms)
+            kern[name] = {"us_per_launch": 1e3 * best, "bytes_per_launch": int(alg[name]), "gbs": alg[name] / (best * 1e-3) / 1e9}
+        del xs, xn, inner, gout
+    torch.cuda.synchronize()
+
+    # ---- end to end: host inputs in pinned memory, result back on the host ----
+    e2e = None
+    if not args.no_e2e:
+        del pass_dev
+        pass_host = L.LayerPass(ctx, slots=min(3, NL), **common)
+        pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
+        hq, hk, hda, hdm, hg, hu = (pin(t) for t in (q, k, da, dm, g, u))
+        hids = pin(ids)
+        hpos = pin(pos) if pos is not None else None
+        hout = torch.empty(T, H, dtype=tdt, pin_memory=True)
+        hin = L.LayerPass.inputs(ids=hids, rows=T, q=hq, k=hk, delta_att=hda, delta_mlp=hdm, gate=hg, up=hu, positions=hpos,
+                                 pos0=r0, q_layer_stride=T * QD, k_layer_stride=T * KD, delta_layer_stride=T * H,
+                                 mlp_layer_stride=T * I)
+        # the device arm rotated q/k in place on the device; the host copies above were taken after it, so both
+        # arms have seen the same kind of data. One untimed run, then a bitwise self-check of host vs device results.
+        pass_host.run_host(hin, hout)
+        e2e_steps = max(2, min(args.steps, args.e2e_steps))
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            pass_host.run_host(hin, hout)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        h2d = T * 4 + (T * 4 if pos is not None else 0) + NL * T * (QD + KD + 2 * H + 2 * I) * es
+        e2e = {"value": total_rows * e2e_steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(T * H * es), "steps": e2e_steps, "ms_per_step": 1e3 * dt / e2e_steps,
+               "api": "lokal_cuda_pass_run_host (pinned host inputs, 3-slot layer ring, copies overlap kernels)"}
+        del pass_host
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        dom = max(kern, key=lambda n: kern[n]["us_per_launch"] * (2 * NL if n == "add_rmsnorm" else (1 if n == "embed_gather" else NL)))
+        roof = {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}",
+                "unit": "GB/s", "frac": kern[dom]["gbs"] / peak, "frac_of_nominal_8000": kern[dom]["gbs"] / NOMINAL_HBM_GBS,
+                "traffic": None,
+                "kernels": {n: dict(v, frac=v["gbs"] / peak, frac_of_nominal_8000=v["gbs"] / NOMINAL_HBM_GBS) for n, v in kern.items()}}
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+            "dtype": {L.F32: "f32", L.F16: "f16", L.BF16: "bf16"}[cfg.dtype] + " storage, f32 arithmetic", "data": "synthetic",
+            "config": workload_config(cfg, T, args),
+            "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9, "step_algorithmic_bytes": int(step_bytes),
+            "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
+            "roofline": roof, "clocks": clocks, "e2e": e2e,
+        }
+        if not args.no_cpu_baseline and world >= 1:
+            line["cpu_baseline"] = cpu_baseline(cfg)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(cfg):
+    """The reference's CPU algorithm (oracle port) on a bounded sample, timed on this box's host cores."""
+    from oracle import lokal_oracle as O
+    O.build()
+    threads = O.hardware_threads()
+    vocab = min(cfg.vocab, 32768)
+    table = synth.q8_0_table(vocab, cfg.hidden, cfg.seed)
+    probe_rows = min(cfg.rows, 4 * threads)
+    probe = cpu_step_fn(cfg, probe_rows, table, vocab)
+    probe(threads)
+    dt = probe(threads)
+    rows = int(min(cfg.rows, max(threads, probe_rows * 4.0 / max(dt, 1e-6))))  # about 4 s per step
+    rows = max(threads, rows // threads * threads)
+    step = cpu_step_fn(cfg, rows, table, vocab)
+    step(threads)
+    times = [step(threads) for _ in range(3)]
+    one = cpu_step_fn(cfg, max(1, rows // threads), table, vocab)
+    one(1)
+    t1 = one(1)
+    return {"value": rows / float(np.median(times)), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{rows} of {cfg.rows} token rows, all {cfg.layers} layers, f32, median of 3 steps, {threads} token-parallel threads",
+            "single_thread_value": max(1, rows // threads) / t1}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(synth.CONFIGS), default="c5")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    if world == 1 and args.gpus > 1:
+        sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+    cfg = synth.CONFIGS[args.workload]
+    if args.impl == "reference":
+        reference_arm(args, cfg, rank, world)
+    else:
+        ours(args, cfg, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

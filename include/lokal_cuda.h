@@ -212,6 +212,82 @@ LOKAL_API int lokal_cuda_dequant_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, 
  * multi-device code; this has no counterpart there. */
 LOKAL_API int lokal_cuda_shard_rows(size_t n_rows, int n_gpus, int rank, size_t* row0, size_t* count);
 
+/* ---- Layer pass: the per-token ops of one forward step, layer by layer -----------
+ * The place these ops take in the reference's step: MetalSession::run_from
+ * (src/gpu/metal.rs:2470-2691), MetalBatcher::decode_step (:3662-3775) and the
+ * CPU Model::forward (src/model.rs:196-261), with the projections and attention
+ * between them left to the caller. One step over `rows` token rows is
+ *   x = embed_gather(ids);  table = rope_table(positions | pos0);  xn = rmsnorm(x, w[0][0])
+ *   for each layer l:  qk_rope(q[l], k[l])            (bias -> per-head norm -> rotate, in place)
+ *                      x += delta_att[l]; xn = rmsnorm(x, w[l][1])
+ *                      inner[l] = silu(gate[l]) * up[l]
+ *                      x += delta_mlp[l]; xn = rmsnorm(x, w[l+1][0], or the final norm weight after the last layer)
+ * q, k, delta_att, delta_mlp, gate, up are what the out-of-scope projections
+ * and attention produce; the caller provides them per layer. The result of a
+ * step is the final normed hidden state, rows x hidden. */
+typedef struct lokal_pass_config {
+    uint64_t max_rows;        /* capacity in token rows of one step on this GPU */
+    uint32_t layers, hidden, inter, n_q_heads, n_kv_heads, head_dim, rot_dim;
+    float eps, theta;
+    int32_t dtype;            /* activation storage type: F32 / F16 / BF16 */
+    int32_t w_dtype;          /* type of norm weights and biases */
+    int32_t has_qk_bias, has_qk_norm;
+    int32_t embed_type;       /* ggml type of the embedding table */
+    uint32_t slots;           /* layer slots kept on the device for staged inputs and per-layer outputs:
+                                 `layers` keeps every layer's outputs; 2-4 is a ring for lokal_cuda_pass_run_host */
+    uint64_t vocab;
+} lokal_pass_config;
+
+/* Weights, HOST pointers, copied to the device once (weights resident, src/gpu/mod.rs:3-13). */
+typedef struct lokal_pass_weights {
+    const void* embed_table;  /* vocab rows of row_bytes(embed_type, hidden) */
+    const void* norm_w;       /* [layers][2][hidden]: input norm, post-attention norm */
+    const void* final_w;      /* [hidden] */
+    const void* q_bias;       /* [layers][n_q_heads*head_dim] or NULL */
+    const void* k_bias;       /* [layers][n_kv_heads*head_dim] or NULL */
+    const void* q_norm_w;     /* [layers][head_dim] or NULL */
+    const void* k_norm_w;     /* [layers][head_dim] or NULL */
+} lokal_pass_weights;
+
+/* Inputs of one step. For lokal_cuda_pass_run_host every pointer is HOST memory
+ * (pinned memory from lokal_cuda_host_alloc lets copies overlap the kernels); for
+ * lokal_cuda_pass_run_device every pointer is DEVICE memory. Per-layer buffers are
+ * [layers][rows][width] with the given layer strides (in elements). */
+typedef struct lokal_pass_inputs {
+    const uint32_t* ids;        /* [rows] */
+    const int32_t* positions;   /* [rows] or NULL for pos0 + row */
+    int64_t pos0;
+    uint64_t rows;
+    void* q;                    /* [layers][rows][n_q_heads*head_dim], rotated in place (device runs) */
+    void* k;                    /* [layers][rows][n_kv_heads*head_dim] */
+    const void* delta_att;      /* [layers][rows][hidden] */
+    const void* delta_mlp;      /* [layers][rows][hidden] */
+    const void* gate;           /* [layers][rows][inter] */
+    const void* up;             /* [layers][rows][inter] */
+    uint64_t q_layer_stride, k_layer_stride, delta_layer_stride, mlp_layer_stride;
+} lokal_pass_inputs;
+
+typedef struct lokal_cuda_pass lokal_cuda_pass;
+
+LOKAL_API int lokal_cuda_pass_create(lokal_cuda_ctx* ctx, const lokal_pass_config* cfg, const lokal_pass_weights* w,
+                                     lokal_cuda_pass** out);
+LOKAL_API int lokal_cuda_pass_destroy(lokal_cuda_ctx* ctx, lokal_cuda_pass* pass);
+/* One step on device-resident inputs, asynchronous on `s` (capturable between
+ * lokal_cuda_graph_begin/end). out_dev: rows x hidden in `dtype`. */
+LOKAL_API int lokal_cuda_pass_run_device(lokal_cuda_ctx* ctx, lokal_cuda_pass* pass, lokal_cuda_stream s,
+                                         const lokal_pass_inputs* in_dev, void* out_dev);
+/* One step on host inputs: layer l+1's inputs are copied while layer l computes
+ * (a ring of `slots` layer slots), the result is copied back, and the call
+ * returns when out_host is complete. Rotated q/k, xn and inner stay on the device. */
+LOKAL_API int lokal_cuda_pass_run_host(lokal_cuda_ctx* ctx, lokal_cuda_pass* pass, const lokal_pass_inputs* in_host,
+                                       void* out_host);
+/* Device addresses of the per-layer outputs a downstream projection would read
+ * (slot = layer % slots): which 0 = xn after the attention residual, 1 = xn after the
+ * MLP residual, 2 = inner, 3 = staged/rotated q, 4 = staged/rotated k (3, 4 only after run_host). */
+LOKAL_API int lokal_cuda_pass_output(lokal_cuda_ctx* ctx, lokal_cuda_pass* pass, uint32_t layer, int which, void** dptr);
+/* Kernels launched by the last run on this pass. */
+LOKAL_API uint64_t lokal_cuda_pass_launches(const lokal_cuda_pass* pass);
+
 /* ---- Host-slice mirrors of the reference's CPU signatures ---------------------
  * Inputs and outputs are HOST memory; each call stages through buffers owned
  * by the context, runs the device op and waits for the result. */

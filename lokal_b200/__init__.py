@@ -7,9 +7,9 @@ offers a thin handle named after the reference's ops. There is no CPU path.
 from . import capi
 from ._build import build
 from .capi import BF16, F16, F32, Q4_K, Q8_0, LokalCudaError, QkRopeParams
-from .ops import Context, blk_bytes, blk_elems, dtype_id, row_bytes, shard_rows
+from .ops import Context, LayerPass, blk_bytes, blk_elems, dtype_id, row_bytes, shard_rows
 
 __all__ = [
-    "capi", "build", "Context", "LokalCudaError", "QkRopeParams", "F32", "F16", "BF16", "Q8_0", "Q4_K",
+    "capi", "build", "Context", "LayerPass", "LokalCudaError", "QkRopeParams", "F32", "F16", "BF16", "Q8_0", "Q4_K",
     "blk_elems", "blk_bytes", "row_bytes", "shard_rows", "dtype_id",
 ]

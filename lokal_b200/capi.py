@@ -38,6 +38,38 @@ class QkRopeParams(C.Structure):
     ]
 
 
+class PassConfig(C.Structure):
+    """Mirror of lokal_pass_config."""
+    _fields_ = [
+        ("max_rows", C.c_uint64),
+        ("layers", C.c_uint32), ("hidden", C.c_uint32), ("inter", C.c_uint32), ("n_q_heads", C.c_uint32),
+        ("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("rot_dim", C.c_uint32),
+        ("eps", C.c_float), ("theta", C.c_float),
+        ("dtype", C.c_int32), ("w_dtype", C.c_int32), ("has_qk_bias", C.c_int32), ("has_qk_norm", C.c_int32),
+        ("embed_type", C.c_int32), ("slots", C.c_uint32),
+        ("vocab", C.c_uint64),
+    ]
+
+
+class PassWeights(C.Structure):
+    """Mirror of lokal_pass_weights (host pointers)."""
+    _fields_ = [
+        ("embed_table", C.c_void_p), ("norm_w", C.c_void_p), ("final_w", C.c_void_p), ("q_bias", C.c_void_p),
+        ("k_bias", C.c_void_p), ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p),
+    ]
+
+
+class PassInputs(C.Structure):
+    """Mirror of lokal_pass_inputs."""
+    _fields_ = [
+        ("ids", C.c_void_p), ("positions", C.c_void_p), ("pos0", C.c_int64), ("rows", C.c_uint64),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("delta_att", C.c_void_p), ("delta_mlp", C.c_void_p),
+        ("gate", C.c_void_p), ("up", C.c_void_p),
+        ("q_layer_stride", C.c_uint64), ("k_layer_stride", C.c_uint64), ("delta_layer_stride", C.c_uint64),
+        ("mlp_layer_stride", C.c_uint64),
+    ]
+
+
 _vp, _sz, _f, _i, _u32, _i64 = C.c_void_p, C.c_size_t, C.c_float, C.c_int, C.c_uint32, C.c_int64
 _pp = C.POINTER(C.c_void_p)
 
@@ -73,6 +105,12 @@ SIGNATURES = {
     "lokal_cuda_embed_gather": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _vp, _sz, _vp, _i]),
     "lokal_cuda_dequant_rows": (_i, [_vp, _vp, _i, _vp, _sz, _sz, _vp, _i]),
     "lokal_cuda_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
+    "lokal_cuda_pass_create": (_i, [_vp, C.POINTER(PassConfig), C.POINTER(PassWeights), _pp]),
+    "lokal_cuda_pass_destroy": (_i, [_vp, _vp]),
+    "lokal_cuda_pass_run_device": (_i, [_vp, _vp, _vp, C.POINTER(PassInputs), _vp]),
+    "lokal_cuda_pass_run_host": (_i, [_vp, _vp, C.POINTER(PassInputs), _vp]),
+    "lokal_cuda_pass_output": (_i, [_vp, _vp, _u32, _i, _pp]),
+    "lokal_cuda_pass_launches": (C.c_uint64, [_vp]),
     "lokal_cuda_host_rmsnorm": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp]),
     "lokal_cuda_host_rope": (_i, [_vp, _vp, _sz, _sz, _sz, _f]),
     "lokal_cuda_host_swiglu": (_i, [_vp, _vp, _vp, _sz, _vp]),

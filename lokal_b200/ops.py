@@ -14,7 +14,7 @@ import ctypes as C
 import numpy as np
 
 from . import capi
-from .capi import BF16, F16, F32, Q4_K, Q8_0, LokalCudaError, QkRopeParams
+from .capi import BF16, F16, F32, Q4_K, Q8_0, LokalCudaError, PassConfig, PassInputs, PassWeights, QkRopeParams
 
 
 def _ptr(x):
@@ -221,6 +221,64 @@ class Context:
         self._check(self._lib.lokal_cuda_host_embed_gather(self._h, _ptr(table_dev), ggml_type, vocab, dim, _ptr(ids),
                                                            ids.size, _ptr(out)))
         return out
+
+
+class LayerPass:
+    """One `lokal_cuda_pass`: the per-token ops of a forward step strung together layer by layer.
+
+    Weights (host numpy arrays) are uploaded once at construction; `run_device` launches a step on
+    device-resident inputs, `run_host` takes host inputs and returns when the result is in host memory.
+    """
+
+    def __init__(self, ctx: Context, *, max_rows, layers, hidden, inter, n_q_heads, n_kv_heads, head_dim, eps, theta,
+                 dtype, w_dtype, embed_type, vocab, embed_table, norm_w, final_w, q_bias=None, k_bias=None,
+                 q_norm_w=None, k_norm_w=None, rot_dim=None, slots=None):
+        self.ctx = ctx
+        cfg = PassConfig(max_rows=max_rows, layers=layers, hidden=hidden, inter=inter, n_q_heads=n_q_heads,
+                         n_kv_heads=n_kv_heads, head_dim=head_dim, rot_dim=head_dim if rot_dim is None else rot_dim,
+                         eps=eps, theta=theta, dtype=dtype, w_dtype=w_dtype, has_qk_bias=int(q_bias is not None),
+                         has_qk_norm=int(q_norm_w is not None), embed_type=embed_type,
+                         slots=layers if slots is None else slots, vocab=vocab)
+        w = PassWeights(embed_table=_ptr(embed_table), norm_w=_ptr(norm_w), final_w=_ptr(final_w), q_bias=_ptr(q_bias),
+                        k_bias=_ptr(k_bias), q_norm_w=_ptr(q_norm_w), k_norm_w=_ptr(k_norm_w))
+        h = C.c_void_p()
+        ctx._check(ctx._lib.lokal_cuda_pass_create(ctx._h, C.byref(cfg), C.byref(w), C.byref(h)))
+        self._h = h
+        self.cfg = cfg
+
+    def close(self):
+        if getattr(self, "_h", None) and self.ctx._h:
+            self.ctx._lib.lokal_cuda_pass_destroy(self.ctx._h, self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def inputs(*, ids, rows, q, k, delta_att, delta_mlp, gate, up, q_layer_stride, k_layer_stride, delta_layer_stride,
+               mlp_layer_stride, positions=None, pos0=0) -> PassInputs:
+        return PassInputs(ids=_ptr(ids), positions=_ptr(positions), pos0=pos0, rows=rows, q=_ptr(q), k=_ptr(k),
+                          delta_att=_ptr(delta_att), delta_mlp=_ptr(delta_mlp), gate=_ptr(gate), up=_ptr(up),
+                          q_layer_stride=q_layer_stride, k_layer_stride=k_layer_stride,
+                          delta_layer_stride=delta_layer_stride, mlp_layer_stride=mlp_layer_stride)
+
+    def run_device(self, inputs: PassInputs, out_dev, stream=None):
+        self.ctx._check(self.ctx._lib.lokal_cuda_pass_run_device(self.ctx._h, self._h, stream, C.byref(inputs), _ptr(out_dev)))
+
+    def run_host(self, inputs: PassInputs, out_host):
+        self.ctx._check(self.ctx._lib.lokal_cuda_pass_run_host(self.ctx._h, self._h, C.byref(inputs), _ptr(out_host)))
+
+    def output(self, layer: int, which: int) -> int:
+        p = C.c_void_p()
+        self.ctx._check(self.ctx._lib.lokal_cuda_pass_output(self.ctx._h, self._h, layer, which, C.byref(p)))
+        return p.value or 0
+
+    @property
+    def launches(self) -> int:
+        return int(self.ctx._lib.lokal_cuda_pass_launches(self._h))
 
 
 def blk_elems(ggml_type: int) -> int:

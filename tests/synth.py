@@ -144,7 +144,13 @@ def f32_table(vocab: int, dim: int, seed: int, std: float = 0.02) -> np.ndarray:
 # ---- tolerances the path is held to ----------------------------------------
 
 F32_MAX_ABS = 1e-5        # norm / rope / swiglu on f32 rows
-HALF_REL = 2e-3           # f16 / bf16 rows: |got - ref| <= HALF_REL * |ref| + atol
+# 16-bit rows: |got - ref| <= rtol * |ref| + atol against the UNROUNDED f32 oracle.
+# f16 keeps 11 significant bits, so a correctly rounded result is within 2^-11 = 4.9e-4 and the 2e-3 bar applies as
+# stated. bf16 keeps 8 significant bits: rounding ALONE costs up to 2^-8 = 3.9e-3 relative, above the stated 2e-3,
+# so no bf16-stored result can meet 2e-3 against an f32 reference. For bf16 the bar is therefore "the nearest-even
+# bf16 rounding of a value that agrees with the oracle to f32 accuracy": half a bf16 ulp plus 1e-5 of slack for a
+# rounding-direction flip caused by the last f32 bits.
+HALF_RTOL = {F16: 2e-3, BF16: 2.0 ** -8 + 1e-5}
 
 
 def check_f32(got: np.ndarray, ref: np.ndarray, what: str, atol: float = F32_MAX_ABS) -> float:
@@ -157,8 +163,9 @@ def check_f32(got: np.ndarray, ref: np.ndarray, what: str, atol: float = F32_MAX
     return err
 
 
-def check_half(got: np.ndarray, ref: np.ndarray, what: str, atol: float = 6e-8, rtol: float = HALF_REL) -> float:
+def check_half(got: np.ndarray, ref: np.ndarray, what: str, dtype: int, atol: float = 6e-8) -> float:
     """got: values read back from f16/bf16 storage (as f32); ref: the UNROUNDED f32 oracle on the same rounded inputs."""
+    rtol = HALF_RTOL[dtype]
     got = np.asarray(got, np.float64)
     ref = np.asarray(ref, np.float64)
     assert got.shape == ref.shape, f"{what}: shape {got.shape} vs {ref.shape}"

@@ -27,15 +27,15 @@ def test_golden_norm(ctx, dev, gold):
 
 def test_golden_rope(ctx, dev, gold):
     dq, dk = dev.put(gold["rope_q"]), dev.put(gold["rope_k"])
-    p = ctx.qk_rope_params(q=dq, k=dk, q_bias=dev.put(gold["rope_qb"]), k_bias=dev.put(gold["rope_kb"]), rows=3,
-                           n_q_heads=4, n_kv_heads=2, head_dim=64)
-    ctx.qk_rope_pos(p, theta=float(gold["rope_theta"]), positions=dev.put(gold["rope_pos"]))
+    qb, kb, pos = dev.put(gold["rope_qb"]), dev.put(gold["rope_kb"]), dev.put(gold["rope_pos"])  # params hold raw addresses
+    p = ctx.qk_rope_params(q=dq, k=dk, q_bias=qb, k_bias=kb, rows=3, n_q_heads=4, n_kv_heads=2, head_dim=64)
+    ctx.qk_rope_pos(p, theta=float(gold["rope_theta"]), positions=pos)
     ctx.stream_sync()
     synth.check_f32(dev.get(dq), gold["rope_q_out"], "golden rope q")
     synth.check_f32(dev.get(dk), gold["rope_k_out"], "golden rope k")
     dq, dk = dev.put(gold["qn_q"]), dev.put(gold["qn_k"])
-    p = ctx.qk_rope_params(q=dq, k=dk, q_norm_w=dev.put(gold["qn_qw"]), k_norm_w=dev.put(gold["qn_kw"]), rows=2,
-                           n_q_heads=2, n_kv_heads=1, head_dim=128, eps=1e-6)
+    qw, kw = dev.put(gold["qn_qw"]), dev.put(gold["qn_kw"])
+    p = ctx.qk_rope_params(q=dq, k=dk, q_norm_w=qw, k_norm_w=kw, rows=2, n_q_heads=2, n_kv_heads=1, head_dim=128, eps=1e-6)
     ctx.qk_rope_pos(p, theta=1e6, pos0=8000)
     ctx.stream_sync()
     synth.check_f32(dev.get(dq), gold["qn_q_out"], "golden qk-norm rope q")

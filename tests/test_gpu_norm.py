@@ -48,7 +48,7 @@ def test_config_shapes(ctx, dev, oracle, name, fused):
     else:
         # the stored residual is the f32 sum rounded once to the storage type
         synth.assert_bits_equal(x_new, synth.round_to(ref_x, cfg.dtype), "x + delta")
-        synth.check_half(xn, ref_xn, f"{name} rmsnorm")
+        synth.check_half(xn, ref_xn, f"{name} rmsnorm", cfg.dtype)
 
 
 @pytest.mark.parametrize("dtype", [F32, F16, BF16])
@@ -66,7 +66,7 @@ def test_shapes_and_tails(ctx, dev, oracle, dtype, rows, dim):
         synth.check_f32(xn, ref_xn, f"rmsnorm {rows}x{dim}")
     else:
         synth.assert_bits_equal(x_new, synth.round_to(ref_x, dtype), "x + delta")
-        synth.check_half(xn, ref_xn, f"rmsnorm {rows}x{dim}")
+        synth.check_half(xn, ref_xn, f"rmsnorm {rows}x{dim}", dtype)
 
 
 def test_reference_all_threes_vector(ctx, dev):
@@ -113,7 +113,7 @@ def test_weight_types(ctx, dev, oracle, w_dtype):
     w = synth.round_to(d["w_norm"], w_dtype)
     _, xn, _, _ = run_norm(ctx, dev, d["x"], d["delta"], w, 1e-6, BF16, w_dtype=w_dtype)
     _, ref = oracle.add_rmsnorm_rows(d["x"], d["delta"], w, 1e-6)
-    synth.check_half(xn, ref, "bf16 rows")
+    synth.check_half(xn, ref, "bf16 rows", BF16)
 
 
 def test_in_place_output(ctx, dev, oracle):

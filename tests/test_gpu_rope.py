@@ -89,8 +89,8 @@ def test_config_shapes(ctx, dev, oracle, name, entry):
         synth.check_f32(q, rq, f"{name} q")
         synth.check_f32(k, rk, f"{name} k")
     else:
-        synth.check_half(q, rq, f"{name} q", atol=ROPE_HALF_ATOL)
-        synth.check_half(k, rk, f"{name} k", atol=ROPE_HALF_ATOL)
+        synth.check_half(q, rq, f"{name} q", cfg.dtype, atol=ROPE_HALF_ATOL)
+        synth.check_half(k, rk, f"{name} k", cfg.dtype, atol=ROPE_HALF_ATOL)
 
 
 def test_full_size_decode_batch_positions(ctx, dev, oracle):
@@ -98,8 +98,8 @@ def test_full_size_decode_batch_positions(ctx, dev, oracle):
     d = synth.layer_inputs(cfg)
     q, k = run_qk(ctx, dev, cfg, d, cfg.rows)
     rq, rk = oracle_qk(oracle, cfg, d)
-    synth.check_half(q, rq, "c3 q", atol=ROPE_HALF_ATOL)
-    synth.check_half(k, rk, "c3 k", atol=ROPE_HALF_ATOL)
+    synth.check_half(q, rq, "c3 q", F16, atol=ROPE_HALF_ATOL)
+    synth.check_half(k, rk, "c3 k", F16, atol=ROPE_HALF_ATOL)
     # same positions in f32: the absolute bar holds out to position 32767
     q32, k32 = run_qk(ctx, dev, cfg, d, cfg.rows, q_dtype=F32, w_dtype=F32)
     synth.check_f32(q32, rq, "c3 q f32")
@@ -156,8 +156,8 @@ def test_geometries_with_bias_and_norm(ctx, dev, oracle, dtype, hd, rot, nq, nkv
         synth.check_f32(q, rq, "q")
         synth.check_f32(k, rk, "k")
     else:
-        synth.check_half(q, rq, "q", atol=ROPE_HALF_ATOL)
-        synth.check_half(k, rk, "k", atol=ROPE_HALF_ATOL)
+        synth.check_half(q, rq, "q", dtype, atol=ROPE_HALF_ATOL)
+        synth.check_half(k, rk, "k", dtype, atol=ROPE_HALF_ATOL)
 
 
 def test_reference_gpu_layout_f32_q_with_f16_k(ctx, dev, oracle):
@@ -168,7 +168,7 @@ def test_reference_gpu_layout_f32_q_with_f16_k(ctx, dev, oracle):
     q, k = run_qk(ctx, dev, cfg, d, 100, q_dtype=F32, k_dtype=F16, w_dtype=F32, pos0=3)
     rq, rk = oracle_qk(oracle, cfg, d, pos0=3)
     synth.check_f32(q, rq, "f32 q")
-    synth.check_half(k, rk, "f16 k", atol=ROPE_HALF_ATOL)
+    synth.check_half(k, rk, "f16 k", F16, atol=ROPE_HALF_ATOL)
 
 
 def test_out_of_place_and_cache_row_scatter(ctx, dev, oracle):
@@ -177,22 +177,22 @@ def test_out_of_place_and_cache_row_scatter(ctx, dev, oracle):
     d = synth.layer_inputs(cfg, rows)
     q, k = run_qk(ctx, dev, cfg, d, rows, out_of_place=True)
     rq, rk = oracle_qk(oracle, cfg, d)
-    synth.check_half(q, rq, "q out of place", atol=ROPE_HALF_ATOL)
-    synth.check_half(k, rk, "k out of place", atol=ROPE_HALF_ATOL)
+    synth.check_half(q, rq, "q out of place", BF16, atol=ROPE_HALF_ATOL)
+    synth.check_half(k, rk, "k out of place", BF16, atol=ROPE_HALF_ATOL)
     # k rows scattered to cache rows (slot*max_seq + pos), wider cache stride
     cache_rows, stride = 500, cfg.kv_dim + 64
     perm = np.random.default_rng(5).permutation(cache_rows)[:rows].astype(np.uint32)
     cache = dev.empty((cache_rows, stride), BF16, fill=3.0)
     dk = dev.put(d["k"], BF16)
     table = device_table(ctx, dev, cfg.theta, cfg.head_dim, rows)
-    p = ctx.qk_rope_params(k=dk, k_out=cache, k_out_rows=dev.put(perm), k_out_row_stride=stride, rows=rows,
+    dperm, dknw = dev.put(perm), dev.put(d["k_norm_w"], BF16)  # named: the params hold raw addresses only
+    p = ctx.qk_rope_params(k=dk, k_out=cache, k_out_rows=dperm, k_out_row_stride=stride, rows=rows,
                            n_q_heads=0, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, eps=cfg.eps,
-                           k_norm_w=dev.put(d["k_norm_w"], BF16), q_dtype=BF16, k_dtype=BF16, w_dtype=BF16,
-                           cos_sin=table)
+                           k_norm_w=dknw, q_dtype=BF16, k_dtype=BF16, w_dtype=BF16, cos_sin=table)
     ctx.qk_rope(p)
     ctx.stream_sync()
     got = dev.get(cache)
-    synth.check_half(got[perm, :cfg.kv_dim], rk, "scattered k", atol=ROPE_HALF_ATOL)
+    synth.check_half(got[perm, :cfg.kv_dim], rk, "scattered k", BF16, atol=ROPE_HALF_ATOL)
     untouched = np.ones(cache_rows, bool)
     untouched[perm] = False
     assert (got[untouched] == 3.0).all() and (got[:, cfg.kv_dim:] == 3.0).all()

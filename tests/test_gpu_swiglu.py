@@ -36,7 +36,7 @@ def test_config_shapes(ctx, dev, oracle, name):
     if cfg.dtype == F32:
         synth.check_f32(got, ref, name)
     else:
-        synth.check_half(got, ref, name)
+        synth.check_half(got, ref, name, cfg.dtype)
 
 
 def test_f32_error_by_magnitude(ctx, dev, oracle):
@@ -50,7 +50,10 @@ def test_f32_error_by_magnitude(ctx, dev, oracle):
     top = np.argsort(-np.abs(ref))[:1000]
     assert np.abs(ref[top]).min() > 20
     ulp = np.spacing(np.abs(ref[top]))
-    assert (np.abs(got[top] - ref[top]) <= ulp).all(), "a large output is more than one ulp off"
+    # a last-bit difference between the device's expf and libm's can move the quotient by one ulp, which the
+    # multiply by u can turn into two ulps of the product; more than that would mean a different expression
+    assert (np.abs(got[top] - ref[top]) <= 2 * ulp).all(), "a large output is more than two ulps off"
+    assert (np.abs(got[top] - ref[top]) <= ulp).mean() > 0.9
 
 
 @pytest.mark.parametrize("dtype", [F32, F16, BF16])
@@ -61,7 +64,7 @@ def test_tails_and_alignment(ctx, dev, oracle, dtype, n):
     u = synth.round_to(rng.standard_normal(n, dtype=np.float32) * 2, dtype)
     got, _ = run(ctx, dev, g, u, dtype)
     ref = oracle.swiglu(g, u)
-    (synth.check_f32 if dtype == F32 else synth.check_half)(got, ref, f"n={n}")
+    synth.check_f32(got, ref, f"n={n}") if dtype == F32 else synth.check_half(got, ref, f"n={n}", dtype)
 
 
 def test_special_values(ctx, dev, oracle):
@@ -72,7 +75,7 @@ def test_special_values(ctx, dev, oracle):
     for dt in (F16, BF16):
         gg, uu = synth.round_to(g, dt), synth.round_to(u, dt)
         got, _ = run(ctx, dev, gg, uu, dt)
-        synth.check_half(got, oracle.swiglu(gg, uu), "special values 16-bit")
+        synth.check_half(got, oracle.swiglu(gg, uu), "special values 16-bit", dt)
 
 
 def test_in_place_and_half_copy(ctx, dev, oracle):
