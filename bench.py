@@ -68,7 +68,7 @@ class ClockSampler(threading.Thread):
     def __init__(self, cuda_index: int):
         super().__init__(daemon=True)
         self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
-        self._stop = threading.Event()
+        self._halt = threading.Event()
         try:
             import pynvml
             import torch
@@ -90,7 +90,7 @@ class ClockSampler(threading.Thread):
     def run(self):
         if not self.ok:
             return
-        while not self._stop.is_set():
+        while not self._halt.is_set():
             try:
                 self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
                 try:
@@ -102,10 +102,10 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._halt.wait(0.05)
 
     def finish(self):
-        self._stop.set()
+        self._halt.set()
         if self.is_alive():
             self.join(2)
         if not self.samples:

@@ -35,6 +35,7 @@ struct lokal_cuda_pass {
     uint32_t* ids = nullptr;   // staged ids (run_host)
     int32_t* positions = nullptr;
     void* out_dev = nullptr;   // final normed hidden (run_host)
+    void* last_out = nullptr;  // where the last run put its result (the caller's buffer for run_device)
     // per-slot outputs and staged inputs
     void* xn0 = nullptr;    // [slots][max_rows][hidden]
     void* xn_att = nullptr; // [slots][max_rows][hidden]
@@ -248,6 +249,7 @@ int lokal_cuda_pass_run_device(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, lokal_cu
                        at(in->gate, l * in->mlp_layer_stride * P->es), at(in->up, l * in->mlp_layer_stride * P->es));
     }
     P->out_dev = saved_out;
+    P->last_out = out_dev;
     return rc;
 }
 
@@ -272,6 +274,7 @@ int lokal_cuda_pass_run_host(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, const loka
     }
     cudaStream_t cs = P->copy_stream, ks = P->compute_stream;
     P->launches = 0;
+    P->last_out = P->out_dev;
     // ids / positions, then the head of the step
     LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(P->ids, in->ids, rows * 4, cudaMemcpyHostToDevice, ks));
     if (in->positions) LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(P->positions, in->positions, rows * 4, cudaMemcpyHostToDevice, ks));
@@ -320,7 +323,7 @@ int lokal_cuda_pass_output(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, uint32_t lay
     const size_t slot = layer % c.slots, R = c.max_rows;
     switch (which) {
         case 0: *dptr = at(P->xn_att, slot * R * c.hidden * P->es); break;
-        case 1: *dptr = (layer + 1 < c.layers) ? at(P->xn_mlp, slot * R * c.hidden * P->es) : P->out_dev; break;
+        case 1: *dptr = (layer + 1 < c.layers) ? at(P->xn_mlp, slot * R * c.hidden * P->es) : P->last_out; break;
         case 2: *dptr = at(P->inner, slot * R * c.inter * P->es); break;
         case 3: *dptr = P->sq ? at(P->sq, slot * R * P->q_dim * P->es) : nullptr; break;
         case 4: *dptr = P->sk ? at(P->sk, slot * R * P->kv_dim * P->es) : nullptr; break;
