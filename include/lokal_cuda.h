@@ -175,6 +175,35 @@ LOKAL_API int lokal_cuda_qk_rope(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const
 LOKAL_API int lokal_cuda_qk_rope_pos(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_qk_rope_params* p,
                                      float theta, const int32_t* positions, int64_t pos0);
 
+/* lokal_cuda_qk_rope_pos for callers that must not allocate. (No counterpart
+ * in the reference: its GPU backends run on unified memory and size every
+ * buffer when a session is created.)
+ *
+ * Who needs it: a serving loop that may not stall -- cudaMalloc and cudaFree
+ * synchronise the whole device and take driver-wide locks, so one call from a
+ * decode step holds up every request in flight -- and an engine that has
+ * handed all remaining HBM to its KV-cache pool at start-up, where a later
+ * allocation can simply fail. lokal_cuda_qk_rope_pos grows a scratch block on
+ * demand; this variant never calls cudaMalloc, cudaFree or any allocating
+ * routine. Its (cos, sin) table lives in a fixed array inside the library
+ * image, LOKAL_NOALLOC_TABLE_BYTES per GPU, which every GPU that loads the
+ * library carries until the process exits.
+ *
+ * Limit: p->rows * p->rot_dim * 4 bytes must fit in LOKAL_NOALLOC_TABLE_BYTES
+ * (e.g. 2048 rows at rot_dim 128, 4096 rows at 64); anything larger is refused
+ * with LOKAL_ERR_BAD_ARG and a message naming the limit. Everything else,
+ * inputs, outputs and results, is as in lokal_cuda_qk_rope_pos.
+ *
+ * The first call on each GPU looks up the array's device address (a one-time
+ * host-side query); make that first call outside any stream capture. The
+ * array is shared by every call on that GPU and keeps the last call's table:
+ * each call first rewrites the rows it is about to read, so nothing has to
+ * start at zero, but two calls that overlap on the device (different streams,
+ * or different contexts on the same GPU) race on it. Serialise them. */
+#define LOKAL_NOALLOC_TABLE_BYTES (1u << 20)
+LOKAL_API int lokal_cuda_qk_rope_pos_noalloc(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_qk_rope_params* p,
+                                             float theta, const int32_t* positions, int64_t pos0);
+
 /* ---- SwiGLU ---------------------------------------------------------------
  * inner_i = (g_i / (1 + exp(-g_i))) * u_i (src/math.rs:68-70, src/model.rs:245-248;
  * GPU twins silu_mul / silu_mul_hf src/gpu/kernels.metal:3533, 3548; host

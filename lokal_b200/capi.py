@@ -101,6 +101,7 @@ SIGNATURES = {
     "lokal_cuda_rope_table": (_i, [_vp, _vp, _f, _u32, _vp, _i64, _sz, _vp]),
     "lokal_cuda_qk_rope": (_i, [_vp, _vp, C.POINTER(QkRopeParams)]),
     "lokal_cuda_qk_rope_pos": (_i, [_vp, _vp, C.POINTER(QkRopeParams), _f, _vp, _i64]),
+    "lokal_cuda_qk_rope_pos_noalloc": (_i, [_vp, _vp, C.POINTER(QkRopeParams), _f, _vp, _i64]),
     "lokal_cuda_swiglu": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i]),
     "lokal_cuda_embed_gather": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _vp, _sz, _vp, _i]),
     "lokal_cuda_dequant_rows": (_i, [_vp, _vp, _i, _vp, _sz, _sz, _vp, _i]),

@@ -406,3 +406,70 @@ int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_para
 }
 
 }  // namespace lokal
+
+// ---------------------------------------------------------------------------
+// qk_rope with positions, for callers that must not allocate
+// ---------------------------------------------------------------------------
+//
+// Some callers cannot afford a cudaMalloc on this path: a decode loop that
+// must not stall (an allocation synchronises the whole device and takes
+// driver-wide locks), or an engine that gave the rest of HBM to its KV-cache
+// pool at start-up, where a later allocation may fail. For them the cos/sin
+// table lives here, in a fixed array that is part of the library image: every
+// GPU that loads the library carries these LOKAL_NOALLOC_TABLE_BYTES until the
+// process exits, and nothing is ever allocated or freed by the entry point
+// below.
+//
+// In host code the array's name is only a stand-in; the address a kernel can
+// use comes from cudaGetSymbolAddress, looked up once per GPU with that GPU
+// current and kept in g_noalloc_table_addr.
+//
+// The array is shared by every call on a GPU and keeps whatever the last call
+// left in it. A call first rewrites the rows it is going to read, so no part
+// of it has to start at zero; calls that overlap on the device race on it.
+
+static __device__ __align__(256) float g_noalloc_rope_table[LOKAL_NOALLOC_TABLE_BYTES / sizeof(float)];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_table_addr[kNoallocMaxDevices] = {};
+}  // namespace
+
+extern "C" int lokal_cuda_qk_rope_pos_noalloc(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_qk_rope_params* p,
+                                              float theta, const int32_t* positions, int64_t pos0) {
+    if (!ctx) return LOKAL_ERR_BAD_ARG;
+    lokal::DeviceGuard guard(ctx->device);
+    if (!guard.ok) return ctx->fail(LOKAL_ERR_CUDA, "cannot select device %d", ctx->device);
+    if (!p) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope_pos_noalloc: params are null");
+    if (p->rot_dim == 0) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope_pos_noalloc: rot_dim is zero");
+    const unsigned long long limit_floats = LOKAL_NOALLOC_TABLE_BYTES / sizeof(float);
+    if (p->rows > limit_floats / p->rot_dim)
+        return ctx->fail(LOKAL_ERR_BAD_ARG,
+                         "qk_rope_pos_noalloc: %llu rows x rot_dim %u needs %llu bytes of table, the built-in table holds %u "
+                         "(use lokal_cuda_qk_rope_pos, or fewer rows per call)",
+                         (unsigned long long)p->rows, p->rot_dim, (unsigned long long)p->rows * p->rot_dim * 4ull,
+                         (unsigned)LOKAL_NOALLOC_TABLE_BYTES);
+    if (ctx->device < 0 || ctx->device >= kNoallocMaxDevices)
+        return ctx->fail(LOKAL_ERR_UNSUPPORTED, "qk_rope_pos_noalloc: device index %d is beyond %d", ctx->device, kNoallocMaxDevices);
+    float* table = nullptr;
+    {
+        // one-time set-up per GPU, with that GPU current (the guard above): the device address of the array
+        std::lock_guard<std::mutex> g(g_noalloc_mu);
+        table = g_noalloc_table_addr[ctx->device];
+        if (!table) {
+            void* addr = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&addr, g_noalloc_rope_table);
+            if (e != cudaSuccess || !addr)
+                return ctx->fail(LOKAL_ERR_CUDA, "qk_rope_pos_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            table = static_cast<float*>(addr);
+            g_noalloc_table_addr[ctx->device] = table;
+        }
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(s);
+    int rc = lokal::launch_rope_table(ctx, stream, theta, p->rot_dim, positions, pos0, p->rows, table);
+    if (rc != LOKAL_OK) return rc;
+    lokal_qk_rope_params q = *p;
+    q.cos_sin = table;
+    return lokal::launch_qk_rope(ctx, stream, q);
+}

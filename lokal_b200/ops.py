@@ -169,6 +169,14 @@ class Context:
     def qk_rope_pos(self, params: QkRopeParams, *, theta, positions=None, pos0=0, stream=None):
         self._check(self._lib.lokal_cuda_qk_rope_pos(self._h, stream, C.byref(params), theta, _ptr(positions), pos0))
 
+    def qk_rope_pos_noalloc(self, params: QkRopeParams, *, theta, positions=None, pos0=0, stream=None):
+        """qk_rope_pos for callers that must not allocate on this path (a decode loop that cannot stall on
+        cudaMalloc, an engine whose KV pool already owns the rest of HBM). The cos/sin table sits in a fixed
+        LOKAL_NOALLOC_TABLE_BYTES array inside the library, so rows * rot_dim * 4 must fit in it; calls that
+        overlap on one GPU share (and race on) that array. Make the first call on a GPU outside stream capture."""
+        self._check(self._lib.lokal_cuda_qk_rope_pos_noalloc(self._h, stream, C.byref(params), theta, _ptr(positions),
+                                                             pos0))
+
     def swiglu(self, gate, up, out, *, n, dtype, out_h=None, h_dtype=F16, stream=None):
         self._check(self._lib.lokal_cuda_swiglu(self._h, stream, _ptr(gate), _ptr(up), _ptr(out), _ptr(out_h), n,
                                                 dtype, h_dtype))
