@@ -342,18 +342,24 @@ def ours(args, cfg, rank, world, local_rank):
             ctx.embed_gather(table_dev, ids, gout[l % gout.shape[0]], ggml_type=L.Q8_0, vocab=vocab, dim=H, n=T, out_dtype=cfg.dtype, stream=stream)
 
         for name, fn in (("add_rmsnorm", k_norm), ("qk_rope", k_rope), ("swiglu", k_swiglu), ("embed_gather", k_gather)):
-            best = None
-            for rep in range(4):
+            # the NL launches go into one graph so host launch overhead stays out of the device time
+            ctx.graph_begin(stream)
+            for l in range(NL):
+                fn(l)
+            kg = ctx.graph_end(stream)
+            times = []
+            for rep in range(6):
                 a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a0.record(tstream)
-                for l in range(NL):
-                    fn(l)
+                ctx.graph_launch(kg, stream)
                 a1.record(tstream)
                 ctx.stream_sync(stream)
                 if rep:  # first repetition is warm-up
-                    ms = a0.elapsed_time(a1) / NL
-                    best = ms if best is None else min(best, ms)
-            kern[name] = {"us_per_launch": 1e3 * best, "bytes_per_launch": int(alg[name]), "gbs": alg[name] / (best * 1e-3) / 1e9}
+                    times.append(a0.elapsed_time(a1) / NL)
+            ctx.graph_destroy(kg)
+            avg = float(np.mean(times))
+            kern[name] = {"us_per_launch": 1e3 * avg, "us_best": 1e3 * min(times), "launches_timed": NL * len(times),
+                          "bytes_per_launch": int(alg[name]), "gbs": alg[name] / (avg * 1e-3) / 1e9}
         del xs, xn, inner, gout
     torch.cuda.synchronize()
 
@@ -447,6 +453,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(synth.CONFIGS), default="c5")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures under a profiler)")
+    ap.add_argument("--rows", type=int, default=0, help="override the token rows per GPU")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -454,6 +462,10 @@ def main():
     if world == 1 and args.gpus > 1:
         sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
     cfg = synth.CONFIGS[args.workload]
+    if args.layers or args.rows:  # reduced sizes for profiler captures; the default is the full workload
+        import dataclasses
+        cfg = dataclasses.replace(cfg, layers=args.layers or cfg.layers, rows=args.rows or cfg.rows,
+                                  name=cfg.name + f"[layers={args.layers or cfg.layers},rows={args.rows or cfg.rows}]")
     if args.impl == "reference":
         reference_arm(args, cfg, rank, world)
     else:

@@ -27,6 +27,7 @@ struct NormArgs {
     unsigned dim;
     unsigned nvec;
     float eps;
+    float inv_dim;
     int w_dtype;
     int h_dtype;
     int w_vec_ok;
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const 
                 *reinterpret_cast<uint4*>(xo + static_cast<size_t>(idx) * N) = pack16<T>(v[j]);
             }
 #pragma unroll
-            for (int e = 0; e < N; e++) acc += v[j][e] * v[j][e];
+            for (int e = 0; e < N; e++) acc = sq_acc<T>(acc, v[j][e]);
         }
     }
 
@@ -107,8 +108,7 @@ __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const 
         for (unsigned wv = 0; wv < nwarps; wv++) total += partial[wv];
         acc = total;
     }
-    const float mean_sq = acc / static_cast<float>(a.dim);
-    const float scale = 1.0f / sqrtf(mean_sq + a.eps);
+    const float scale = inv_rms<T>(acc, static_cast<float>(a.dim), a.inv_dim, a.eps);
 
     T* yr = reinterpret_cast<T*>(a.xn) + row * a.dim;
 #pragma unroll
@@ -198,14 +198,14 @@ int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, NormArgs a, bool ptrs_alig
         return LOKAL_OK;
     }
     a.nvec = a.dim / N;
-    // Threads per row: a warp while rows alone fill the machine; otherwise split
-    // each row over more threads so small batches still cover all SMs.
-    const size_t target_threads = static_cast<size_t>(ctx->sm_count) * 1024;
-    unsigned tpr = 32;
-    while (tpr < 1024 && tpr < a.nvec && a.rows * tpr < target_threads) tpr *= 2;
-    if (tpr == 32 && a.nvec > 32u * 8u) tpr = 64;
-    // A CTA of up to 1024 threads has 64 registers per thread: keep its share of the row small.
-    while (tpr > 32 && tpr < 1024 && (a.nvec + tpr - 1) / tpr > 2) tpr *= 2;
+    // Threads per row. One 16-byte vector per thread (a CTA per row, shared-memory combine) keeps every CTA small and
+    // short-lived, so the machine drains evenly at the end of the kernel; rows wider than 1024 vectors give each
+    // thread several vectors, and rows of at most 32 vectors take one warp each, eight rows to a CTA.
+    unsigned tpr = ((a.nvec + 31u) / 32u) * 32u;
+    if (tpr > 1024) tpr = 1024;
+    const long forced = tune_env("LOKAL_CUDA_NORM_TPR", 0);
+    if (forced >= 32 && forced <= 1024 && forced % 32 == 0) tpr = static_cast<unsigned>(forced);
+    while (tpr < 1024 && (a.nvec + tpr - 1) / tpr > 8) tpr *= 2;
     unsigned vpt = (a.nvec + tpr - 1) / tpr;
     if (vpt == 7) vpt = 8;
     cudaError_t e = tpr == 32 ? launch_vec<T, false>(a, tpr, vpt, s) : launch_vec<T, true>(a, tpr, vpt, s);
@@ -244,6 +244,7 @@ int launch_norm(lokal_cuda_ctx* ctx, cudaStream_t s, void* x, const void* delta,
     a.rows = rows;
     a.dim = static_cast<unsigned>(dim);
     a.eps = eps;
+    a.inv_dim = 1.0f / static_cast<float>(dim);
     a.w_dtype = w_dtype;
     a.h_dtype = h_dtype;
     a.w_vec_ok = aligned_to(w, 16);

@@ -72,8 +72,12 @@ struct QkArgs {
 
 // Fast path: rot_dim == head_dim == HD, 16-byte aligned rows. A group of LPH
 // lanes owns one head: each lane holds N elements of the first half and the N
-// partner elements of the second half.
-template <typename T, int HD>
+// partner elements of the second half, so a warp covers HPW heads per pass.
+// One warp walks the q and k heads of one row two passes at a time (the four
+// 16-byte loads of both passes are issued before either is consumed). The
+// row's cos/sin live in registers; the per-head norm weights are staged once
+// per CTA in shared memory as f32.
+template <typename T, int HD, bool NORM, bool BIAS>
 __global__ void __launch_bounds__(256) qk_rope_kernel(const QkArgs a) {
     constexpr int N = VecOf<T>::N;
     constexpr int HALF = HD / 2;
@@ -81,10 +85,20 @@ __global__ void __launch_bounds__(256) qk_rope_kernel(const QkArgs a) {
     constexpr int HPW = 32 / LPH;   // heads per warp pass
     static_assert(LPH >= 1 && LPH <= 32 && (LPH & (LPH - 1)) == 0, "head must map onto a power-of-two lane group");
 
+    __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];  // [q norm weights | k norm weights]
+    if (NORM) {
+        for (unsigned i = threadIdx.x; i < 2u * HD; i += blockDim.x) {
+            const void* src = i < HD ? a.q_norm_w : a.k_norm_w;
+            w_s[i] = src ? load_as_f32(src, a.w_dtype, i < HD ? i : i - HD) : 1.0f;
+        }
+        __syncthreads();
+    }
+
     const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const unsigned long long row = warp / a.wpr;
     if (row >= a.rows) return;
     const unsigned first_chunk = static_cast<unsigned>(warp % a.wpr) * a.cpw;
+    const unsigned end_chunk = min(first_chunk + a.cpw, a.chunks);
     const unsigned lane = threadIdx.x & 31u;
     const unsigned sub = lane % LPH;
     const unsigned hsel = lane / LPH;
@@ -104,57 +118,64 @@ __global__ void __launch_bounds__(256) qk_rope_kernel(const QkArgs a) {
             for (int e = 0; e < 4; e++) sn[4 * j + e] = t[e];
         }
     }
+    const T* q_row = reinterpret_cast<const T*>(a.q) + row * a.q_stride + sub * N;
+    const T* k_row = reinterpret_cast<const T*>(a.k) + row * a.k_stride + sub * N;
+    T* q_dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride + sub * N;
+    T* k_dst = nullptr;
+    if (a.n_kv) {
+        const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
+        k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + sub * N;
+    }
 
-    for (unsigned c = first_chunk; c < first_chunk + a.cpw && c < a.chunks; c++) {
+    // one pass: the head this lane group owns in chunk c
+    auto finish = [&](unsigned c, const uint4& lo, const uint4& hi) {
         const unsigned slot = c * HPW + hsel;
-        const bool live = slot < slots;
+        const bool live = c < end_chunk && slot < slots;
         const bool is_q = slot < a.n_q;
         const unsigned head = is_q ? slot : slot - a.n_q;
-        const T* src = is_q ? reinterpret_cast<const T*>(a.q) + row * a.q_stride
-                            : reinterpret_cast<const T*>(a.k) + row * a.k_stride;
-        src += static_cast<size_t>(head) * HD + sub * N;
         float va[N], vb[N];
         if (live) {
-            const uint4 lo = ld_stream(src), hi = ld_stream(src + HALF);
             unpack16<T>(lo, va);
             unpack16<T>(hi, vb);
         } else {
 #pragma unroll
             for (int e = 0; e < N; e++) va[e] = vb[e] = 0.0f;
         }
-        const void* bias = is_q ? a.q_bias : a.k_bias;
-        if (bias && live) {
-            float ba[N], bb[N];
-            load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + sub * N, a.w_vec_ok, ba);
-            load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + HALF + sub * N, a.w_vec_ok, bb);
-#pragma unroll
-            for (int e = 0; e < N; e++) {
-                va[e] = va[e] + ba[e];
-                vb[e] = vb[e] + bb[e];
-            }
-        }
-        // Uniform over the warp: the q and k norm weights are either both given or both absent per slot kind,
-        // and every lane takes part in the shuffles.
-        const bool any_norm = (a.q_norm_w != nullptr) || (a.k_norm_w != nullptr);
-        if (any_norm) {
-            float ss = 0.0f;
-#pragma unroll
-            for (int e = 0; e < N; e++) ss += va[e] * va[e];
-#pragma unroll
-            for (int e = 0; e < N; e++) ss += vb[e] * vb[e];
-#pragma unroll
-            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const void* nw = is_q ? a.q_norm_w : a.k_norm_w;
-            if (nw && live) {
-                const float mean_sq = ss / static_cast<float>(HD);
-                const float scale = 1.0f / sqrtf(mean_sq + a.eps);
-                float wa[N], wb[N];
-                load_w<N>(nw, a.w_dtype, sub * N, a.w_vec_ok, wa);
-                load_w<N>(nw, a.w_dtype, HALF + sub * N, a.w_vec_ok, wb);
+        if (BIAS) {
+            const void* bias = is_q ? a.q_bias : a.k_bias;
+            if (bias && live) {
+                float ba[N], bb[N];
+                load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + sub * N, a.w_vec_ok, ba);
+                load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + HALF + sub * N, a.w_vec_ok, bb);
 #pragma unroll
                 for (int e = 0; e < N; e++) {
-                    va[e] = (va[e] * scale) * wa[e];
-                    vb[e] = (vb[e] * scale) * wb[e];
+                    va[e] = va[e] + ba[e];
+                    vb[e] = vb[e] + bb[e];
+                }
+            }
+        }
+        if (NORM) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < N; e++) ss = sq_acc<T>(ss, va[e]);
+#pragma unroll
+            for (int e = 0; e < N; e++) ss = sq_acc<T>(ss, vb[e]);
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // every lane takes part
+            const bool has = is_q ? (a.q_norm_w != nullptr) : (a.k_norm_w != nullptr);
+            if (has && live) {
+                const float scale = inv_rms<T>(ss, static_cast<float>(HD), 1.0f / static_cast<float>(HD), a.eps);
+                const float* w = w_s + (is_q ? 0 : HD) + sub * N;
+#pragma unroll
+                for (int j = 0; j < N / 4; j++) {
+                    const float4 wa = *reinterpret_cast<const float4*>(w + 4 * j);
+                    const float4 wb = *reinterpret_cast<const float4*>(w + HALF + 4 * j);
+                    const float wav[4] = {wa.x, wa.y, wa.z, wa.w}, wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        va[4 * j + e] = (va[4 * j + e] * scale) * wav[e];
+                        vb[4 * j + e] = (vb[4 * j + e] * scale) * wbv[e];
+                    }
                 }
             }
         }
@@ -162,20 +183,36 @@ __global__ void __launch_bounds__(256) qk_rope_kernel(const QkArgs a) {
             float oa[N], ob[N];
 #pragma unroll
             for (int e = 0; e < N; e++) {
-                oa[e] = va[e] * cs[e] - vb[e] * sn[e];
-                ob[e] = va[e] * sn[e] + vb[e] * cs[e];
+                if (sizeof(T) == 2) {
+                    // the result is rounded to 16 bits on store: one product of each pair may ride in an FMA
+                    oa[e] = fmaf(va[e], cs[e], -(vb[e] * sn[e]));
+                    ob[e] = fmaf(va[e], sn[e], vb[e] * cs[e]);
+                } else {
+                    oa[e] = va[e] * cs[e] - vb[e] * sn[e];
+                    ob[e] = va[e] * sn[e] + vb[e] * cs[e];
+                }
             }
-            T* dst;
-            if (is_q) {
-                dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride;
-            } else {
-                const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
-                dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride;
-            }
-            dst += static_cast<size_t>(head) * HD + sub * N;
+            T* dst = (is_q ? q_dst : k_dst) + static_cast<size_t>(head) * HD;
             *reinterpret_cast<uint4*>(dst) = pack16<T>(oa);
             *reinterpret_cast<uint4*>(dst + HALF) = pack16<T>(ob);
         }
+    };
+    auto fetch = [&](unsigned c, uint4& lo, uint4& hi) {
+        const unsigned slot = c * HPW + hsel;
+        if (c < end_chunk && slot < slots) {
+            const bool is_q = slot < a.n_q;
+            const T* src = (is_q ? q_row : k_row) + static_cast<size_t>(is_q ? slot : slot - a.n_q) * HD;
+            lo = ld_stream(src);
+            hi = ld_stream(src + HALF);
+        }
+    };
+
+    for (unsigned c = first_chunk; c < end_chunk; c += 2) {
+        uint4 lo0, hi0, lo1, hi1;
+        fetch(c, lo0, hi0);
+        fetch(c + 1, lo1, hi1);
+        finish(c, lo0, hi0);
+        if (c + 1 < end_chunk) finish(c + 1, lo1, hi1);
     }
 }
 
@@ -254,24 +291,36 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     }
     const unsigned lph = (a.head_dim / 2) / N, hpw = 32 / lph;
     a.chunks = (slots + hpw - 1) / hpw;
-    // One warp per row while rows alone fill the machine; otherwise split a row's heads over several warps.
-    const unsigned long long want_warps = static_cast<unsigned long long>(ctx->sm_count) * 16;
+    // Warps per row: one warp walks all head groups of a row (the row's cos/sin are read once). Measured on B200
+    // this beat splitting a row over several warps even for 8192-row batches; few rows spread over more warps.
     unsigned wpr = 1;
+    const unsigned long long want_warps = static_cast<unsigned long long>(ctx->sm_count) * 16;
     if (a.rows < want_warps) {
         wpr = static_cast<unsigned>((want_warps + a.rows - 1) / a.rows);
         if (wpr > a.chunks) wpr = a.chunks;
     }
+    const long forced = tune_env("LOKAL_CUDA_ROPE_WPR", 0);
+    if (forced >= 1 && forced <= static_cast<long>(a.chunks)) wpr = static_cast<unsigned>(forced);
     a.cpw = (a.chunks + wpr - 1) / wpr;
     a.wpr = (a.chunks + a.cpw - 1) / a.cpw;
     const unsigned long long warps = a.rows * a.wpr;
     const unsigned long long blocks = (warps + 7) / 8;
     if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many rows for one launch");
     const unsigned grid = static_cast<unsigned>(blocks);
+    const bool norm = a.q_norm_w || a.k_norm_w, bias = a.q_bias || a.k_bias;
+#define LOKAL_ROPE_LAUNCH(HD_)                                                               \
+    do {                                                                                     \
+        if (norm && bias) qk_rope_kernel<T, HD_, true, true><<<grid, 256, 0, s>>>(a);        \
+        else if (norm) qk_rope_kernel<T, HD_, true, false><<<grid, 256, 0, s>>>(a);          \
+        else if (bias) qk_rope_kernel<T, HD_, false, true><<<grid, 256, 0, s>>>(a);          \
+        else qk_rope_kernel<T, HD_, false, false><<<grid, 256, 0, s>>>(a);                   \
+    } while (0)
     switch (a.head_dim) {
-        case 64: qk_rope_kernel<T, 64><<<grid, 256, 0, s>>>(a); break;
-        case 128: qk_rope_kernel<T, 128><<<grid, 256, 0, s>>>(a); break;
-        default: qk_rope_kernel<T, 256><<<grid, 256, 0, s>>>(a); break;
+        case 64: LOKAL_ROPE_LAUNCH(64); break;
+        case 128: LOKAL_ROPE_LAUNCH(128); break;
+        default: LOKAL_ROPE_LAUNCH(256); break;
     }
+#undef LOKAL_ROPE_LAUNCH
     LOKAL_CHECK_LAUNCH(ctx, "qk_rope_kernel");
     return LOKAL_OK;
 }

@@ -37,46 +37,61 @@ struct SwigluArgs {
 constexpr int kSwigluUnroll = 4;
 
 template <typename T>
-__global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
+__device__ __forceinline__ void swiglu_store(const SwigluArgs& a, uint4* o, unsigned long long v, const uint4& gv, const uint4& uv) {
     constexpr int N = VecOf<T>::N;
-    const T* g = reinterpret_cast<const T*>(a.gate);
-    const T* u = reinterpret_cast<const T*>(a.up);
-    T* o = reinterpret_cast<T*>(a.out);
-    // Each CTA owns a contiguous tile of kSwigluUnroll * blockDim vectors; a thread's
-    // vectors are blockDim apart so every load instruction of a warp is one 512-byte run.
-    const unsigned long long base = static_cast<unsigned long long>(blockIdx.x) * (blockDim.x * kSwigluUnroll) + threadIdx.x;
-    uint4 gv[kSwigluUnroll], uv[kSwigluUnroll];
+    float gf[N], uf[N], y[N];
+    unpack16<T>(gv, gf);
+    unpack16<T>(uv, uf);
 #pragma unroll
-    for (int j = 0; j < kSwigluUnroll; j++) {
-        const unsigned long long v = base + static_cast<unsigned long long>(j) * blockDim.x;
-        if (v < a.nvec) {
-            gv[j] = ld_stream(g + v * N);
-            uv[j] = ld_stream(u + v * N);
+    for (int e = 0; e < N; e++) y[e] = silu_mul<T>(gf[e], uf[e]);
+    *o = pack16<T>(y);
+    if (sizeof(T) == 4 && a.out_h) {
+        unsigned w[2];
+        if (a.h_dtype == LOKAL_F16) {
+            __half2 h0 = __floats2half2_rn(y[0], y[1]), h1 = __floats2half2_rn(y[2], y[3]);
+            w[0] = *reinterpret_cast<unsigned*>(&h0);
+            w[1] = *reinterpret_cast<unsigned*>(&h1);
+        } else {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(y[0], y[1]), h1 = __floats2bfloat162_rn(y[2], y[3]);
+            w[0] = *reinterpret_cast<unsigned*>(&h0);
+            w[1] = *reinterpret_cast<unsigned*>(&h1);
         }
+        *reinterpret_cast<uint2*>(reinterpret_cast<unsigned short*>(a.out_h) + v * N) = make_uint2(w[0], w[1]);
     }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
+    // Each CTA owns a contiguous tile of kSwigluUnroll * 256 vectors (16 KB per stream); a thread's vectors are
+    // 256 apart, so every load instruction of a warp is one 512-byte run. Many small CTAs: the machine drains
+    // evenly at the end of the kernel. All 64-bit address arithmetic is done once per CTA.
+    constexpr unsigned kTile = 256u * kSwigluUnroll;
+    const unsigned long long tile0 = static_cast<unsigned long long>(blockIdx.x) * kTile;
+    const uint4* g = reinterpret_cast<const uint4*>(a.gate) + tile0 + threadIdx.x;
+    const uint4* u = reinterpret_cast<const uint4*>(a.up) + tile0 + threadIdx.x;
+    uint4* o = reinterpret_cast<uint4*>(a.out) + tile0 + threadIdx.x;
+    const unsigned long long left = a.nvec - tile0;
+    uint4 gv[kSwigluUnroll], uv[kSwigluUnroll];
+    if (left >= kTile) {
 #pragma unroll
-    for (int j = 0; j < kSwigluUnroll; j++) {
-        const unsigned long long v = base + static_cast<unsigned long long>(j) * blockDim.x;
-        if (v < a.nvec) {
-            float gf[N], uf[N], y[N];
-            unpack16<T>(gv[j], gf);
-            unpack16<T>(uv[j], uf);
+        for (int j = 0; j < kSwigluUnroll; j++) {
+            gv[j] = ld_stream(g + j * 256);
+            uv[j] = ld_stream(u + j * 256);
+        }
 #pragma unroll
-            for (int e = 0; e < N; e++) y[e] = silu_mul<T>(gf[e], uf[e]);
-            *reinterpret_cast<uint4*>(o + v * N) = pack16<T>(y);
-            if (sizeof(T) == 4 && a.out_h) {
-                unsigned w[2];
-                if (a.h_dtype == LOKAL_F16) {
-                    __half2 h0 = __floats2half2_rn(y[0], y[1]), h1 = __floats2half2_rn(y[2], y[3]);
-                    w[0] = *reinterpret_cast<unsigned*>(&h0);
-                    w[1] = *reinterpret_cast<unsigned*>(&h1);
-                } else {
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(y[0], y[1]), h1 = __floats2bfloat162_rn(y[2], y[3]);
-                    w[0] = *reinterpret_cast<unsigned*>(&h0);
-                    w[1] = *reinterpret_cast<unsigned*>(&h1);
-                }
-                *reinterpret_cast<uint2*>(reinterpret_cast<unsigned short*>(a.out_h) + v * N) = make_uint2(w[0], w[1]);
+        for (int j = 0; j < kSwigluUnroll; j++) swiglu_store<T>(a, o + j * 256, tile0 + threadIdx.x + j * 256, gv[j], uv[j]);
+    } else {
+        const unsigned n = static_cast<unsigned>(left);
+#pragma unroll
+        for (int j = 0; j < kSwigluUnroll; j++) {
+            if (threadIdx.x + j * 256 < n) {
+                gv[j] = ld_stream(g + j * 256);
+                uv[j] = ld_stream(u + j * 256);
             }
+        }
+#pragma unroll
+        for (int j = 0; j < kSwigluUnroll; j++) {
+            if (threadIdx.x + j * 256 < n) swiglu_store<T>(a, o + j * 256, tile0 + threadIdx.x + j * 256, gv[j], uv[j]);
         }
     }
 }
