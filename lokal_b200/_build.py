@@ -45,7 +45,8 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return SO
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+    extra = os.environ.get("LOKAL_B200_NVCC_EXTRA", "").split()  # e.g. -DLOKAL_ROPE_MIN_CTAS=3 for experiments
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + \
           [os.path.join(CSRC, s) for s in SOURCES] + ["-o", SO]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:

@@ -283,6 +283,78 @@ __device__ __forceinline__ float inv_rms(float sum_sq, float n, float inv_n, flo
     return 1.0f / sqrtf(sum_sq / n + eps);
 }
 
+// ---------------------------------------------------------------------------
+// Packed f32 arithmetic (Blackwell: two IEEE round-to-nearest f32 operations per
+// lane in one instruction). mul2 / add2 give exactly the bits of two scalar
+// multiplies / adds, so the reference's separately rounded products and sums
+// are kept while the kernels issue half as many floating-point instructions.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
+}
+
+// 16 bytes <-> N/2 pairs of f32
+template <typename T>
+__device__ __forceinline__ void unpack16p(const uint4& v, float2 (&p)[VecOf<T>::N / 2]);
+template <>
+__device__ __forceinline__ void unpack16p<float>(const uint4& v, float2 (&p)[2]) {
+    p[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+    p[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
+}
+template <>
+__device__ __forceinline__ void unpack16p<__half>(const uint4& v, float2 (&p)[4]) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) p[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+}
+template <>
+__device__ __forceinline__ void unpack16p<__nv_bfloat16>(const uint4& v, float2 (&p)[4]) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) p[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack16p(const float2 (&p)[VecOf<T>::N / 2]);
+template <>
+__device__ __forceinline__ uint4 pack16p<float>(const float2 (&p)[2]) {
+    return make_uint4(__float_as_uint(p[0].x), __float_as_uint(p[0].y), __float_as_uint(p[1].x), __float_as_uint(p[1].y));
+}
+template <>
+__device__ __forceinline__ uint4 pack16p<__half>(const float2 (&p)[4]) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __half2 h = __floats2half2_rn(p[i].x, p[i].y);
+        w[i] = *reinterpret_cast<unsigned*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ uint4 pack16p<__nv_bfloat16>(const float2 (&p)[4]) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(p[i].x, p[i].y);
+        w[i] = *reinterpret_cast<unsigned*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 }  // namespace lokal
 
 // Launchers implemented in the per-op translation units.

@@ -25,6 +25,15 @@ namespace {
 
 constexpr unsigned kMaxRot = 1024;
 
+#ifndef LOKAL_ROPE_IN_FLIGHT
+#define LOKAL_ROPE_IN_FLIGHT 3  // head-group passes whose loads are issued together
+#endif
+constexpr int kRopeInFlight = LOKAL_ROPE_IN_FLIGHT;
+
+#ifndef LOKAL_ROPE_MIN_CTAS
+#define LOKAL_ROPE_MIN_CTAS 3  // resident 256-thread CTAs per SM the fast kernel is compiled for (caps registers at 80)
+#endif
+
 struct TableArgs {
     float inv_freq[kMaxRot / 2];
     const int32_t* positions;
@@ -76,20 +85,28 @@ struct QkArgs {
 // One warp walks the q and k heads of one row two passes at a time (the four
 // 16-byte loads of both passes are issued before either is consumed). The
 // row's cos/sin live in registers; the per-head norm weights are staged once
-// per CTA in shared memory as f32.
+// per CTA in shared memory as f32, laid out so that the lanes of a group read
+// consecutive 16-byte words. All arithmetic is packed f32x2: for f32 rows the
+// products and sums are rounded exactly as the reference's scalar code rounds
+// them; 16-bit rows, which are rounded again on store, let one product of each
+// rotated pair ride in a fused multiply-add.
 template <typename T, int HD, bool NORM, bool BIAS>
-__global__ void __launch_bounds__(256) qk_rope_kernel(const QkArgs a) {
+__global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const QkArgs a) {
     constexpr int N = VecOf<T>::N;
+    constexpr int P = N / 2;        // f32 pairs per 16-byte vector
     constexpr int HALF = HD / 2;
     constexpr int LPH = HALF / N;   // lanes per head
     constexpr int HPW = 32 / LPH;   // heads per warp pass
     static_assert(LPH >= 1 && LPH <= 32 && (LPH & (LPH - 1)) == 0, "head must map onto a power-of-two lane group");
 
-    __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];  // [q norm weights | k norm weights]
+    // [q first half | q second half | k first half | k second half], each half permuted to (j, lane, e) order
+    __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
     if (NORM) {
         for (unsigned i = threadIdx.x; i < 2u * HD; i += blockDim.x) {
-            const void* src = i < HD ? a.q_norm_w : a.k_norm_w;
-            w_s[i] = src ? load_as_f32(src, a.w_dtype, i < HD ? i : i - HD) : 1.0f;
+            const unsigned kind = i / HD, d = i % HD, half = d / HALF, r = d % HALF;
+            const unsigned lane_of = r / N, j = (r % N) / 4, e = r % 4;
+            const void* src = kind ? a.k_norm_w : a.q_norm_w;
+            w_s[kind * HD + half * HALF + (j * LPH + lane_of) * 4 + e] = src ? load_as_f32(src, a.w_dtype, d) : 1.0f;
         }
         __syncthreads();
     }
@@ -104,115 +121,128 @@ __global__ void __launch_bounds__(256) qk_rope_kernel(const QkArgs a) {
     const unsigned hsel = lane / LPH;
     const unsigned slots = a.n_q + a.n_kv;
 
-    float cs[N], sn[N];
+    float2 cs[P], sn[P], nsn[P];
     {
-        const float* tr = a.cos_sin + row * HD;
+        const float* tr = a.cos_sin + row * HD + sub * N;
 #pragma unroll
         for (int j = 0; j < N / 4; j++) {
-            float t[4];
-            unpack16<float>(ld_keep(tr + sub * N + 4 * j), t);
-#pragma unroll
-            for (int e = 0; e < 4; e++) cs[4 * j + e] = t[e];
-            unpack16<float>(ld_keep(tr + HALF + sub * N + 4 * j), t);
-#pragma unroll
-            for (int e = 0; e < 4; e++) sn[4 * j + e] = t[e];
+            float2 t[2];
+            unpack16p<float>(ld_keep(tr + 4 * j), t);
+            cs[2 * j] = t[0];
+            cs[2 * j + 1] = t[1];
+            unpack16p<float>(ld_keep(tr + HALF + 4 * j), t);
+            sn[2 * j] = t[0];
+            sn[2 * j + 1] = t[1];
         }
+#pragma unroll
+        for (int i = 0; i < P; i++) nsn[i] = make_float2(-sn[i].x, -sn[i].y);
     }
-    const T* q_row = reinterpret_cast<const T*>(a.q) + row * a.q_stride + sub * N;
-    const T* k_row = reinterpret_cast<const T*>(a.k) + row * a.k_stride + sub * N;
+    // Head slot s of the row lives at q_row + s*HD for s < n_q and at k_row + (s - n_q)*HD otherwise; the second
+    // base is pre-shifted by n_q heads so both cases are "base + s*HD".
+    const long long k_shift = static_cast<long long>(a.n_q) * HD;
+    const T* q_src = reinterpret_cast<const T*>(a.q) + row * a.q_stride + sub * N;
+    const T* k_src = reinterpret_cast<const T*>(a.k) + row * a.k_stride + sub * N - k_shift;
     T* q_dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride + sub * N;
     T* k_dst = nullptr;
     if (a.n_kv) {
         const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
-        k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + sub * N;
+        k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + sub * N - k_shift;
     }
 
-    // one pass: the head this lane group owns in chunk c
+    auto fetch = [&](unsigned c, uint4& lo, uint4& hi) {
+        const unsigned slot = c * HPW + hsel;
+        if (c < end_chunk && slot < slots) {
+            const T* src = (slot < a.n_q ? q_src : k_src) + static_cast<size_t>(slot) * HD;
+            lo = ld_stream(src);
+            hi = ld_stream(src + HALF);
+        }
+    };
     auto finish = [&](unsigned c, const uint4& lo, const uint4& hi) {
         const unsigned slot = c * HPW + hsel;
         const bool live = c < end_chunk && slot < slots;
         const bool is_q = slot < a.n_q;
-        const unsigned head = is_q ? slot : slot - a.n_q;
-        float va[N], vb[N];
+        float2 va[P], vb[P];
         if (live) {
-            unpack16<T>(lo, va);
-            unpack16<T>(hi, vb);
+            unpack16p<T>(lo, va);
+            unpack16p<T>(hi, vb);
         } else {
 #pragma unroll
-            for (int e = 0; e < N; e++) va[e] = vb[e] = 0.0f;
+            for (int i = 0; i < P; i++) va[i] = vb[i] = make_float2(0.0f, 0.0f);
         }
         if (BIAS) {
             const void* bias = is_q ? a.q_bias : a.k_bias;
             if (bias && live) {
+                const size_t boff = static_cast<size_t>(is_q ? slot : slot - a.n_q) * HD + sub * N;
                 float ba[N], bb[N];
-                load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + sub * N, a.w_vec_ok, ba);
-                load_w<N>(bias, a.w_dtype, static_cast<size_t>(head) * HD + HALF + sub * N, a.w_vec_ok, bb);
+                load_w<N>(bias, a.w_dtype, boff, a.w_vec_ok, ba);
+                load_w<N>(bias, a.w_dtype, boff + HALF, a.w_vec_ok, bb);
 #pragma unroll
-                for (int e = 0; e < N; e++) {
-                    va[e] = va[e] + ba[e];
-                    vb[e] = vb[e] + bb[e];
+                for (int i = 0; i < P; i++) {
+                    va[i] = add2(va[i], make_float2(ba[2 * i], ba[2 * i + 1]));
+                    vb[i] = add2(vb[i], make_float2(bb[2 * i], bb[2 * i + 1]));
                 }
             }
         }
         if (NORM) {
-            float ss = 0.0f;
+            float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int e = 0; e < N; e++) ss = sq_acc<T>(ss, va[e]);
-#pragma unroll
-            for (int e = 0; e < N; e++) ss = sq_acc<T>(ss, vb[e]);
+            for (int i = 0; i < P; i++) {
+                if (sizeof(T) == 2) {
+                    acc = fma2(va[i], va[i], acc);
+                    acc = fma2(vb[i], vb[i], acc);
+                } else {
+                    acc = add2(acc, mul2(va[i], va[i]));
+                    acc = add2(acc, mul2(vb[i], vb[i]));
+                }
+            }
+            float ss = acc.x + acc.y;
 #pragma unroll
             for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // every lane takes part
             const bool has = is_q ? (a.q_norm_w != nullptr) : (a.k_norm_w != nullptr);
             if (has && live) {
                 const float scale = inv_rms<T>(ss, static_cast<float>(HD), 1.0f / static_cast<float>(HD), a.eps);
-                const float* w = w_s + (is_q ? 0 : HD) + sub * N;
+                const float2 s2 = make_float2(scale, scale);
+                const float* w = w_s + (is_q ? 0 : HD) + sub * 4;
 #pragma unroll
                 for (int j = 0; j < N / 4; j++) {
-                    const float4 wa = *reinterpret_cast<const float4*>(w + 4 * j);
-                    const float4 wb = *reinterpret_cast<const float4*>(w + HALF + 4 * j);
-                    const float wav[4] = {wa.x, wa.y, wa.z, wa.w}, wbv[4] = {wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        va[4 * j + e] = (va[4 * j + e] * scale) * wav[e];
-                        vb[4 * j + e] = (vb[4 * j + e] * scale) * wbv[e];
-                    }
+                    const float4 wa = *reinterpret_cast<const float4*>(w + j * LPH * 4);
+                    const float4 wb = *reinterpret_cast<const float4*>(w + HALF + j * LPH * 4);
+                    va[2 * j] = mul2(mul2(va[2 * j], s2), make_float2(wa.x, wa.y));
+                    va[2 * j + 1] = mul2(mul2(va[2 * j + 1], s2), make_float2(wa.z, wa.w));
+                    vb[2 * j] = mul2(mul2(vb[2 * j], s2), make_float2(wb.x, wb.y));
+                    vb[2 * j + 1] = mul2(mul2(vb[2 * j + 1], s2), make_float2(wb.z, wb.w));
                 }
             }
         }
         if (live) {
-            float oa[N], ob[N];
+            float2 oa[P], ob[P];
 #pragma unroll
-            for (int e = 0; e < N; e++) {
+            for (int i = 0; i < P; i++) {
+                // a*cos - b*sin as a*cos + b*(-sin): the same bits, and it leaves the pair free to be fused or not
                 if (sizeof(T) == 2) {
-                    // the result is rounded to 16 bits on store: one product of each pair may ride in an FMA
-                    oa[e] = fmaf(va[e], cs[e], -(vb[e] * sn[e]));
-                    ob[e] = fmaf(va[e], sn[e], vb[e] * cs[e]);
+                    oa[i] = fma2(va[i], cs[i], mul2(vb[i], nsn[i]));
+                    ob[i] = fma2(va[i], sn[i], mul2(vb[i], cs[i]));
                 } else {
-                    oa[e] = va[e] * cs[e] - vb[e] * sn[e];
-                    ob[e] = va[e] * sn[e] + vb[e] * cs[e];
+                    oa[i] = add2(mul2(va[i], cs[i]), mul2(vb[i], nsn[i]));
+                    ob[i] = add2(mul2(va[i], sn[i]), mul2(vb[i], cs[i]));
                 }
             }
-            T* dst = (is_q ? q_dst : k_dst) + static_cast<size_t>(head) * HD;
-            *reinterpret_cast<uint4*>(dst) = pack16<T>(oa);
-            *reinterpret_cast<uint4*>(dst + HALF) = pack16<T>(ob);
-        }
-    };
-    auto fetch = [&](unsigned c, uint4& lo, uint4& hi) {
-        const unsigned slot = c * HPW + hsel;
-        if (c < end_chunk && slot < slots) {
-            const bool is_q = slot < a.n_q;
-            const T* src = (is_q ? q_row : k_row) + static_cast<size_t>(is_q ? slot : slot - a.n_q) * HD;
-            lo = ld_stream(src);
-            hi = ld_stream(src + HALF);
+            T* dst = (is_q ? q_dst : k_dst) + static_cast<size_t>(slot) * HD;
+            *reinterpret_cast<uint4*>(dst) = pack16p<T>(oa);
+            *reinterpret_cast<uint4*>(dst + HALF) = pack16p<T>(ob);
         }
     };
 
-    for (unsigned c = first_chunk; c < end_chunk; c += 2) {
-        uint4 lo0, hi0, lo1, hi1;
-        fetch(c, lo0, hi0);
-        fetch(c + 1, lo1, hi1);
-        finish(c, lo0, hi0);
-        if (c + 1 < end_chunk) finish(c + 1, lo1, hi1);
+    // kRopeInFlight passes are loaded before the first is consumed: bytes in flight per warp, not warps per SM,
+    // are what keep HBM busy here (the per-lane state of a pass is too large for high occupancy).
+    for (unsigned c = first_chunk; c < end_chunk; c += kRopeInFlight) {
+        uint4 lo[kRopeInFlight], hi[kRopeInFlight];
+#pragma unroll
+        for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);
+#pragma unroll
+        for (int i = 0; i < kRopeInFlight; i++) {
+            if (i == 0 || c + i < end_chunk) finish(c + i, lo[i], hi[i]);
+        }
     }
 }
 
@@ -304,16 +334,20 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     a.cpw = (a.chunks + wpr - 1) / wpr;
     a.wpr = (a.chunks + a.cpw - 1) / a.cpw;
     const unsigned long long warps = a.rows * a.wpr;
-    const unsigned long long blocks = (warps + 7) / 8;
+    unsigned cta = 256;
+    const long forced_cta = tune_env("LOKAL_CUDA_ROPE_CTA", 0);
+    if (forced_cta == 32 || forced_cta == 64 || forced_cta == 128) cta = static_cast<unsigned>(forced_cta);
+    const unsigned wpc = cta / 32;
+    const unsigned long long blocks = (warps + wpc - 1) / wpc;
     if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many rows for one launch");
     const unsigned grid = static_cast<unsigned>(blocks);
     const bool norm = a.q_norm_w || a.k_norm_w, bias = a.q_bias || a.k_bias;
 #define LOKAL_ROPE_LAUNCH(HD_)                                                               \
     do {                                                                                     \
-        if (norm && bias) qk_rope_kernel<T, HD_, true, true><<<grid, 256, 0, s>>>(a);        \
-        else if (norm) qk_rope_kernel<T, HD_, true, false><<<grid, 256, 0, s>>>(a);          \
-        else if (bias) qk_rope_kernel<T, HD_, false, true><<<grid, 256, 0, s>>>(a);          \
-        else qk_rope_kernel<T, HD_, false, false><<<grid, 256, 0, s>>>(a);                   \
+        if (norm && bias) qk_rope_kernel<T, HD_, true, true><<<grid, cta, 0, s>>>(a);        \
+        else if (norm) qk_rope_kernel<T, HD_, true, false><<<grid, cta, 0, s>>>(a);          \
+        else if (bias) qk_rope_kernel<T, HD_, false, true><<<grid, cta, 0, s>>>(a);          \
+        else qk_rope_kernel<T, HD_, false, false><<<grid, cta, 0, s>>>(a);                   \
     } while (0)
     switch (a.head_dim) {
         case 64: LOKAL_ROPE_LAUNCH(64); break;
