@@ -46,6 +46,18 @@ def env_int(name, default):
         return default
 
 
+def ncu_traffic(workload: str, kernel: str):
+    """DRAM bytes per launch of `kernel` from the committed ncu capture of this workload (profiles/), or None."""
+    p = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        t = json.load(open(p))
+        if t.get("workload") == workload:
+            return t["dram_bytes_per_launch"].get(kernel)
+    except Exception:
+        pass
+    return None
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -102,7 +114,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._halt.wait(0.05)
+            self._halt.wait(0.002)  # the timed region is tens of milliseconds: sample every ~2 ms
 
     def finish(self):
         self._halt.set()
@@ -401,7 +413,7 @@ def ours(args, cfg, rank, world, local_rank):
         dom = max(kern, key=lambda n: kern[n]["us_per_launch"] * (2 * NL if n == "add_rmsnorm" else (1 if n == "embed_gather" else NL)))
         roof = {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}",
                 "unit": "GB/s", "frac": kern[dom]["gbs"] / peak, "frac_of_nominal_8000": kern[dom]["gbs"] / NOMINAL_HBM_GBS,
-                "traffic": None,
+                "traffic": ncu_traffic(cfg.name, dom),
                 "kernels": {n: dict(v, frac=v["gbs"] / peak, frac_of_nominal_8000=v["gbs"] / NOMINAL_HBM_GBS) for n, v in kern.items()}}
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
