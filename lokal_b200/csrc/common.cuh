@@ -355,6 +355,38 @@ __device__ __forceinline__ uint4 pack16p<__nv_bfloat16>(const float2 (&p)[4]) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---------------------------------------------------------------------------
+// Kernel launch with programmatic dependent launch (PDL). Each kernel of this library begins with pdl_sync():
+// it lets the next kernel in the stream start its launch and block scheduling while this one drains, and it
+// waits until the kernel before it has completed (and its writes are visible) before touching global memory.
+// Stream order semantics are unchanged; what is hidden is launch latency between the short kernels of a step.
+// LOKAL_CUDA_PDL=0 turns the launch attribute off (the device-side calls then return at once).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_sync() {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+inline bool pdl_enabled() {
+    static const bool on = tune_env("LOKAL_CUDA_PDL", 1) != 0;
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace lokal
 
 // Launchers implemented in the per-op translation units.

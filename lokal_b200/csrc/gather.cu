@@ -145,6 +145,7 @@ __device__ __forceinline__ void store_out16(OutT* dst, const float (&y)[VecOf<Ou
 
 template <int QT, typename OutT>
 __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherArgs a) {
+    pdl_sync();
     constexpr int EPL = VecOf<OutT>::N;
     extern __shared__ __align__(128) unsigned char smem[];
     const unsigned warps_per_cta = blockDim.x >> 5;
@@ -272,6 +273,7 @@ __device__ __forceinline__ float dequant_elem_global(int qt, const unsigned char
 
 template <typename OutT>
 __global__ void __launch_bounds__(256) gather_quant_plain_kernel(const GatherArgs a, int qt) {
+    pdl_sync();
     const unsigned long long i = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (i >= a.n) return;
     const unsigned lane = threadIdx.x & 31u;
@@ -289,6 +291,7 @@ __global__ void __launch_bounds__(256) gather_quant_plain_kernel(const GatherArg
 // ---- float tables (F32 / F16 / BF16): copy or widen/narrow a row ----
 template <typename SrcT, typename OutT>
 __global__ void __launch_bounds__(256) gather_float_kernel(const GatherArgs a, int vec_ok) {
+    pdl_sync();
     constexpr int N = VecOf<SrcT>::N;  // elements per 16-byte source vector
     const unsigned long long i = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (i >= a.n) return;
@@ -339,9 +342,9 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
         const int vec_ok = aligned && (static_cast<size_t>(a.dim) * ses) % 16 == 0 &&
                            (static_cast<size_t>(a.dim) * sizeof(OutT)) % 16 == 0;
         const unsigned grid = static_cast<unsigned>(row_warps_blocks);
-        if (ggml_type == LOKAL_F32) gather_float_kernel<float, OutT><<<grid, 256, 0, s>>>(a, vec_ok);
-        else if (ggml_type == LOKAL_F16) gather_float_kernel<__half, OutT><<<grid, 256, 0, s>>>(a, vec_ok);
-        else gather_float_kernel<__nv_bfloat16, OutT><<<grid, 256, 0, s>>>(a, vec_ok);
+        if (ggml_type == LOKAL_F32) launch_k(gather_float_kernel<float, OutT>, grid, 256, 0, s, a, vec_ok);
+        else if (ggml_type == LOKAL_F16) launch_k(gather_float_kernel<__half, OutT>, grid, 256, 0, s, a, vec_ok);
+        else launch_k(gather_float_kernel<__nv_bfloat16, OutT>, grid, 256, 0, s, a, vec_ok);
         LOKAL_CHECK_LAUNCH(ctx, "gather_float_kernel");
         return LOKAL_OK;
     }
@@ -351,7 +354,7 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
     const size_t smem = ((warps * 2 * 8 + 127u) & ~127u) + static_cast<size_t>(warps) * 2 * a.stage_bytes;
     const bool staged = aligned && smem <= 200u * 1024u && (a.row_bytes % 2 == 0);
     if (!staged) {
-        gather_quant_plain_kernel<OutT><<<static_cast<unsigned>(row_warps_blocks), 256, 0, s>>>(a, ggml_type);
+        launch_k(gather_quant_plain_kernel<OutT>, static_cast<unsigned>(row_warps_blocks), 256, 0, s, a, ggml_type);
         LOKAL_CHECK_LAUNCH(ctx, "gather_quant_plain_kernel");
         return LOKAL_OK;
     }
@@ -366,7 +369,7 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
     if (per_sm < 1) per_sm = 1;
     unsigned long long grid = static_cast<unsigned long long>(ctx->sm_count) * per_sm;
     if (grid > row_warps_blocks) grid = row_warps_blocks;
-    kern<<<static_cast<unsigned>(grid), warps * 32, smem, s>>>(a);
+    launch_k(kern, static_cast<unsigned>(grid), warps * 32, smem, s, a);
     LOKAL_CHECK_LAUNCH(ctx, "gather_quant_staged_kernel");
     return LOKAL_OK;
 }

@@ -57,6 +57,7 @@ __device__ __forceinline__ void store_h_copy(void* base, int h_dtype, size_t ele
 
 template <typename T, int VPT, bool CTA_MODE>
 __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const NormArgs a) {
+    pdl_sync();
     constexpr int N = VecOf<T>::N;
     const unsigned tpr = CTA_MODE ? blockDim.x : 32u;
     const unsigned t = CTA_MODE ? threadIdx.x : (threadIdx.x & 31u);
@@ -130,6 +131,7 @@ __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const 
 // twice (the second read hits L1/L2).
 template <typename T>
 __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a) {
+    pdl_sync();
     const size_t row = blockIdx.x;
     const T* xr = reinterpret_cast<const T*>(a.x) + row * a.dim;
     const T* dr = a.delta ? reinterpret_cast<const T*>(a.delta) + row * a.dim : nullptr;
@@ -177,13 +179,13 @@ cudaError_t launch_vec(const NormArgs& a, unsigned tpr, unsigned vpt, cudaStream
         grid = dim3(ceil_div(a.rows, 8));
     }
     switch (vpt) {
-        case 1: norm_rows_kernel<T, 1, CTA_MODE><<<grid, block, 0, s>>>(a); break;
-        case 2: norm_rows_kernel<T, 2, CTA_MODE><<<grid, block, 0, s>>>(a); break;
-        case 3: norm_rows_kernel<T, 3, CTA_MODE><<<grid, block, 0, s>>>(a); break;
-        case 4: norm_rows_kernel<T, 4, CTA_MODE><<<grid, block, 0, s>>>(a); break;
-        case 5: norm_rows_kernel<T, 5, CTA_MODE><<<grid, block, 0, s>>>(a); break;
-        case 6: norm_rows_kernel<T, 6, CTA_MODE><<<grid, block, 0, s>>>(a); break;
-        default: norm_rows_kernel<T, 8, CTA_MODE><<<grid, block, 0, s>>>(a); break;
+        case 1: launch_k(norm_rows_kernel<T, 1, CTA_MODE>, grid, block, 0, s, a); break;
+        case 2: launch_k(norm_rows_kernel<T, 2, CTA_MODE>, grid, block, 0, s, a); break;
+        case 3: launch_k(norm_rows_kernel<T, 3, CTA_MODE>, grid, block, 0, s, a); break;
+        case 4: launch_k(norm_rows_kernel<T, 4, CTA_MODE>, grid, block, 0, s, a); break;
+        case 5: launch_k(norm_rows_kernel<T, 5, CTA_MODE>, grid, block, 0, s, a); break;
+        case 6: launch_k(norm_rows_kernel<T, 6, CTA_MODE>, grid, block, 0, s, a); break;
+        default: launch_k(norm_rows_kernel<T, 8, CTA_MODE>, grid, block, 0, s, a); break;
     }
     return cudaGetLastError();
 }
@@ -193,7 +195,7 @@ int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, NormArgs a, bool ptrs_alig
     constexpr unsigned N = VecOf<T>::N;
     const bool vec = ptrs_aligned && a.dim % N == 0 && a.dim / N <= 1024u * 8u;
     if (!vec) {
-        norm_rows_generic_kernel<T><<<static_cast<unsigned>(a.rows), 256, 0, s>>>(a);
+        launch_k(norm_rows_generic_kernel<T>, static_cast<unsigned>(a.rows), 256, 0, s, a);
         LOKAL_CHECK_LAUNCH(ctx, "norm_rows_generic_kernel");
         return LOKAL_OK;
     }

@@ -44,6 +44,7 @@ struct TableArgs {
 };
 
 __global__ void __launch_bounds__(256) rope_table_kernel(const __grid_constant__ TableArgs a) {
+    pdl_sync();
     const unsigned long long gid = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (gid >= a.rows * a.half) return;
     const unsigned long long row = gid / a.half;
@@ -92,6 +93,7 @@ struct QkArgs {
 // rotated pair ride in a fused multiply-add.
 template <typename T, int HD, bool NORM, bool BIAS>
 __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const QkArgs a) {
+    pdl_sync();
     constexpr int N = VecOf<T>::N;
     constexpr int P = N / 2;        // f32 pairs per 16-byte vector
     constexpr int HALF = HD / 2;
@@ -101,21 +103,12 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
 
     // [q first half | q second half | k first half | k second half], each half permuted to (j, lane, e) order
     __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
-    if (NORM) {
-        for (unsigned i = threadIdx.x; i < 2u * HD; i += blockDim.x) {
-            const unsigned kind = i / HD, d = i % HD, half = d / HALF, r = d % HALF;
-            const unsigned lane_of = r / N, j = (r % N) / 4, e = r % 4;
-            const void* src = kind ? a.k_norm_w : a.q_norm_w;
-            w_s[kind * HD + half * HALF + (j * LPH + lane_of) * 4 + e] = src ? load_as_f32(src, a.w_dtype, d) : 1.0f;
-        }
-        __syncthreads();
-    }
-
     const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const unsigned long long row = warp / a.wpr;
-    if (row >= a.rows) return;
+    // Warps past the last row stay for the shared-memory staging barrier below but are given an empty chunk range.
+    const bool valid = warp / a.wpr < a.rows;
+    const unsigned long long row = valid ? warp / a.wpr : a.rows - 1;
     const unsigned first_chunk = static_cast<unsigned>(warp % a.wpr) * a.cpw;
-    const unsigned end_chunk = min(first_chunk + a.cpw, a.chunks);
+    const unsigned end_chunk = valid ? min(first_chunk + a.cpw, a.chunks) : first_chunk;
     const unsigned lane = threadIdx.x & 31u;
     const unsigned sub = lane % LPH;
     const unsigned hsel = lane / LPH;
@@ -234,14 +227,30 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
     };
 
     // kRopeInFlight passes are loaded before the first is consumed: bytes in flight per warp, not warps per SM,
-    // are what keep HBM busy here (the per-lane state of a pass is too large for high occupancy).
-    for (unsigned c = first_chunk; c < end_chunk; c += kRopeInFlight) {
-        uint4 lo[kRopeInFlight], hi[kRopeInFlight];
+    // are what keep HBM busy here (the per-lane state of a pass is too large for high occupancy). The first loads
+    // are issued before the norm weights are staged, so the staging barrier does not delay them.
+    unsigned c = first_chunk;
+    uint4 lo[kRopeInFlight], hi[kRopeInFlight];
 #pragma unroll
-        for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);
+    for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);
+    if (NORM) {
+        for (unsigned i = threadIdx.x; i < 2u * HD; i += blockDim.x) {
+            const unsigned kind = i / HD, d = i % HD, half = d / HALF, r = d % HALF;
+            const unsigned lane_of = r / N, j = (r % N) / 4, e = r % 4;
+            const void* src = kind ? a.k_norm_w : a.q_norm_w;
+            w_s[kind * HD + half * HALF + (j * LPH + lane_of) * 4 + e] = src ? load_as_f32(src, a.w_dtype, d) : 1.0f;
+        }
+        __syncthreads();
+    }
+    while (c < end_chunk) {
 #pragma unroll
         for (int i = 0; i < kRopeInFlight; i++) {
             if (i == 0 || c + i < end_chunk) finish(c + i, lo[i], hi[i]);
+        }
+        c += kRopeInFlight;
+        if (c < end_chunk) {
+#pragma unroll
+            for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);
         }
     }
 }
@@ -252,6 +261,7 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
 // norm changed them or the output is a different buffer.
 template <typename T>
 __global__ void __launch_bounds__(256) qk_rope_generic_kernel(const QkArgs a) {
+    pdl_sync();
     const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const unsigned slots = a.n_q + a.n_kv;
     const unsigned long long row = warp / slots;
@@ -315,7 +325,7 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
         const unsigned long long warps = a.rows * slots;
         const unsigned long long blocks = (warps + 7) / 8;
         if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many head rows for one launch");
-        qk_rope_generic_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+        launch_k(qk_rope_generic_kernel<T>, static_cast<unsigned>(blocks), 256, 0, s, a);
         LOKAL_CHECK_LAUNCH(ctx, "qk_rope_generic_kernel");
         return LOKAL_OK;
     }
@@ -344,10 +354,10 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     const bool norm = a.q_norm_w || a.k_norm_w, bias = a.q_bias || a.k_bias;
 #define LOKAL_ROPE_LAUNCH(HD_)                                                               \
     do {                                                                                     \
-        if (norm && bias) qk_rope_kernel<T, HD_, true, true><<<grid, cta, 0, s>>>(a);        \
-        else if (norm) qk_rope_kernel<T, HD_, true, false><<<grid, cta, 0, s>>>(a);          \
-        else if (bias) qk_rope_kernel<T, HD_, false, true><<<grid, cta, 0, s>>>(a);          \
-        else qk_rope_kernel<T, HD_, false, false><<<grid, cta, 0, s>>>(a);                   \
+        if (norm && bias) launch_k(qk_rope_kernel<T, HD_, true, true>, grid, cta, 0, s, a);        \
+        else if (norm) launch_k(qk_rope_kernel<T, HD_, true, false>, grid, cta, 0, s, a);          \
+        else if (bias) launch_k(qk_rope_kernel<T, HD_, false, true>, grid, cta, 0, s, a);          \
+        else launch_k(qk_rope_kernel<T, HD_, false, false>, grid, cta, 0, s, a);                   \
     } while (0)
     switch (a.head_dim) {
         case 64: LOKAL_ROPE_LAUNCH(64); break;
@@ -391,7 +401,7 @@ int launch_rope_table(lokal_cuda_ctx* ctx, cudaStream_t s, float theta, uint32_t
     const unsigned long long total = static_cast<unsigned long long>(rows) * half;
     const unsigned long long blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "rope_table: too many rows for one launch");
-    rope_table_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+    launch_k(rope_table_kernel, static_cast<unsigned>(blocks), 256, 0, s, a);
     LOKAL_CHECK_LAUNCH(ctx, "rope_table_kernel");
     return LOKAL_OK;
 }

@@ -62,6 +62,7 @@ __device__ __forceinline__ void swiglu_store(const SwigluArgs& a, uint4* o, unsi
 
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
+    pdl_sync();
     // Each CTA owns a contiguous tile of kSwigluUnroll * 256 vectors (16 KB per stream); a thread's vectors are
     // 256 apart, so every load instruction of a warp is one 512-byte run. Many small CTAs: the machine drains
     // evenly at the end of the kernel. All 64-bit address arithmetic is done once per CTA.
@@ -99,6 +100,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
 // Elements [first, n): the ragged tail, or everything when pointers are not 16-byte aligned.
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_scalar_kernel(const SwigluArgs a, unsigned long long first) {
+    pdl_sync();
     const unsigned long long i = first + static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= a.n) return;
     const float g = to_f32<T>(reinterpret_cast<const T*>(a.gate)[i]);
@@ -119,14 +121,14 @@ int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, SwigluArgs a, bool aligned
         const unsigned long long per_cta = 256ull * kSwigluUnroll;
         const unsigned long long blocks = (a.nvec + per_cta - 1) / per_cta;
         if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "swiglu: too many elements for one launch");
-        swiglu_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+        launch_k(swiglu_kernel<T>, static_cast<unsigned>(blocks), 256, 0, s, a);
         LOKAL_CHECK_LAUNCH(ctx, "swiglu_kernel");
     }
     const unsigned long long first = a.nvec * N;
     if (first < a.n) {
         const unsigned long long blocks = (a.n - first + 255) / 256;
         if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "swiglu: too many elements for one launch");
-        swiglu_scalar_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a, first);
+        launch_k(swiglu_scalar_kernel<T>, static_cast<unsigned>(blocks), 256, 0, s, a, first);
         LOKAL_CHECK_LAUNCH(ctx, "swiglu_scalar_kernel");
     }
     return LOKAL_OK;
