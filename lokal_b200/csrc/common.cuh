@@ -17,6 +17,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <set>
+#include <utility>
 #include <string>
 
 #include "../../include/lokal_cuda.h"
@@ -115,9 +117,14 @@ struct VecOf<__nv_bfloat16> {
     static constexpr int N = 8;
 };
 
-// Loads/stores of the activation streams (touched once per kernel). Plain accesses: measured on B200, default-policy
-// 16-byte loads and stores ran a 2-read/1-write stream a few percent faster than the evict-first (.cs) forms.
-__device__ __forceinline__ uint4 ld_stream(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+// Loads/stores of the activation streams (touched once per kernel): 16-byte loads that do not allocate in L1 (each
+// byte is consumed once, by the thread that loaded it) and plain 16-byte stores. Chosen by measurement on B200 over
+// the default-policy and the evict-first (.cs) forms, on the time of a whole step.
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ void st_stream(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 __device__ __forceinline__ uint4 ld_keep(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
@@ -356,6 +363,47 @@ __device__ __forceinline__ uint4 pack16p<__nv_bfloat16>(const float2 (&p)[4]) {
 }
 
 // ---------------------------------------------------------------------------
+// Bulk asynchronous copies (TMA, untiled form) completing on an mbarrier. No cluster multicast is used anywhere:
+// the .shared::cluster qualifier below is only the address-space spelling of this CTA's own shared memory.
+// Every wait is bounded; a caller that sees `false` records kErrTimeout in the context's error word and leaves.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t mbar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+// Bulk copy global -> this CTA's shared memory; src, dst and bytes are multiples of 16.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, unsigned bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(mbar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(mbar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+constexpr unsigned kWaitLimit = 1u << 20;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, unsigned parity) {
+    for (unsigned spin = 0; spin < kWaitLimit; spin++) {
+        if (mbar_try_wait(mbar, parity)) return true;
+    }
+    return false;
+}
+
+// ---------------------------------------------------------------------------
 // Kernel launch with programmatic dependent launch (PDL). Each kernel of this library begins with pdl_sync():
 // it lets the next kernel in the stream start its launch and block scheduling while this one drains, and it
 // waits until the kernel before it has completed (and its writes are visible) before touching global memory.
@@ -384,6 +432,25 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    // Every kernel of the library asks for the same L1/shared-memory split. Two of them stage rows in shared memory,
+    // the others use next to none; left to the driver each would get its own split, and an SM has to drain before
+    // its split can change (measured: several microseconds between consecutive kernels of a step). 60 % shared
+    // memory gave the shortest step on B200; LOKAL_CUDA_CARVEOUT=<percent> overrides it, -1 leaves it to the driver.
+    {
+        static const long carve = tune_env("LOKAL_CUDA_CARVEOUT", 60);
+        if (carve >= 0 && carve <= 100) {
+            static std::mutex mu;
+            static std::set<std::pair<int, const void*>> done;
+            int dev = 0;
+            cudaGetDevice(&dev);
+            const std::pair<int, const void*> key(dev, reinterpret_cast<const void*>(kernel));
+            std::lock_guard<std::mutex> g(mu);
+            if (done.find(key) == done.end()) {
+                cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(carve));
+                done.insert(key);
+            }
+        }
+    }
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

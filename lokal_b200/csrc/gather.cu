@@ -27,42 +27,6 @@
 namespace lokal {
 namespace {
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t mbar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
-}
-// Bulk copy global -> this CTA's shared memory; src, dst and bytes are multiples of 16.
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, unsigned bytes, uint32_t mbar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(mbar)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(mbar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-constexpr unsigned kWaitLimit = 1u << 20;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, unsigned parity) {
-    for (unsigned spin = 0; spin < kWaitLimit; spin++) {
-        if (mbar_try_wait(mbar, parity)) return true;
-    }
-    return false;
-}
-
 struct GatherArgs {
     const unsigned char* table;
     const uint32_t* ids;  // null -> row i

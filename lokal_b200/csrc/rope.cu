@@ -78,44 +78,47 @@ struct QkArgs {
     unsigned chunks;   // head slots of a row, in groups of (32 / lanes-per-head)
     unsigned cpw;      // chunks handled by one warp
     unsigned wpr;      // warps per row
+    unsigned q_row_bytes, k_row_bytes;  // n_q*head_dim*sizeof(T), n_kv*head_dim*sizeof(T) (staged kernel)
+    unsigned stage_bytes;               // per-warp staging area, multiple of 128
+    unsigned* err_word;
 };
 
-// Fast path: rot_dim == head_dim == HD, 16-byte aligned rows. A group of LPH
-// lanes owns one head: each lane holds N elements of the first half and the N
-// partner elements of the second half, so a warp covers HPW heads per pass.
-// One warp walks the q and k heads of one row two passes at a time (the four
-// 16-byte loads of both passes are issued before either is consumed). The
-// row's cos/sin live in registers; the per-head norm weights are staged once
-// per CTA in shared memory as f32, laid out so that the lanes of a group read
-// consecutive 16-byte words. All arithmetic is packed f32x2: for f32 rows the
-// products and sums are rounded exactly as the reference's scalar code rounds
-// them; 16-bit rows, which are rounded again on store, let one product of each
-// rotated pair ride in a fused multiply-add.
+// ---------------------------------------------------------------------------
+// Fast path: rot_dim == head_dim == HD, 16-byte aligned rows.
+//
+// Lane mapping: a group of LPH lanes owns one head; each lane holds N elements
+// of the head's first half and the N partner elements of the second half, so a
+// warp covers HPW heads per pass and the q heads followed by the k heads of a
+// row are "head slots" 0 .. n_q+n_kv-1. The row's cos/sin live in registers;
+// the per-head norm weights are staged once per CTA in shared memory as f32,
+// permuted so that the lanes of a group read consecutive 16-byte words.
+// Arithmetic is packed f32x2. For f32 rows every product and sum is rounded
+// exactly as the reference's scalar code rounds it, in its order: bias, then
+// (v*scale)*w, then the rotation. 16-bit rows are rounded again on store, so
+// there the weights and the rotation, which do not depend on the scale, are
+// applied while the reduction's shuffles are still in flight, the scale is
+// multiplied in last, and one product of each rotated pair rides in an FMA.
+// ---------------------------------------------------------------------------
 template <typename T, int HD, bool NORM, bool BIAS>
-__global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const QkArgs a) {
-    pdl_sync();
-    constexpr int N = VecOf<T>::N;
-    constexpr int P = N / 2;        // f32 pairs per 16-byte vector
-    constexpr int HALF = HD / 2;
-    constexpr int LPH = HALF / N;   // lanes per head
-    constexpr int HPW = 32 / LPH;   // heads per warp pass
+struct RopeRow {
+    static constexpr int N = VecOf<T>::N;
+    static constexpr int P = N / 2;        // f32 pairs per 16-byte vector
+    static constexpr int HALF = HD / 2;
+    static constexpr int LPH = HALF / N;   // lanes per head
+    static constexpr int HPW = 32 / LPH;   // heads per warp pass
     static_assert(LPH >= 1 && LPH <= 32 && (LPH & (LPH - 1)) == 0, "head must map onto a power-of-two lane group");
 
-    // [q first half | q second half | k first half | k second half], each half permuted to (j, lane, e) order
-    __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
-    const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    // Warps past the last row stay for the shared-memory staging barrier below but are given an empty chunk range.
-    const bool valid = warp / a.wpr < a.rows;
-    const unsigned long long row = valid ? warp / a.wpr : a.rows - 1;
-    const unsigned first_chunk = static_cast<unsigned>(warp % a.wpr) * a.cpw;
-    const unsigned end_chunk = valid ? min(first_chunk + a.cpw, a.chunks) : first_chunk;
-    const unsigned lane = threadIdx.x & 31u;
-    const unsigned sub = lane % LPH;
-    const unsigned hsel = lane / LPH;
-    const unsigned slots = a.n_q + a.n_kv;
-
     float2 cs[P], sn[P], nsn[P];
-    {
+    T* q_dst;
+    T* k_dst;  // pre-shifted by -n_q heads so that both are indexed by the head slot
+    const float* w_s;
+    unsigned sub, hsel, slots;
+
+    __device__ __forceinline__ void init(const QkArgs& a, unsigned long long row, unsigned lane, const float* w_shared) {
+        sub = lane % LPH;
+        hsel = lane / LPH;
+        slots = a.n_q + a.n_kv;
+        w_s = w_shared;
         const float* tr = a.cos_sin + row * HD + sub * N;
 #pragma unroll
         for (int j = 0; j < N / 4; j++) {
@@ -129,30 +132,29 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
         }
 #pragma unroll
         for (int i = 0; i < P; i++) nsn[i] = make_float2(-sn[i].x, -sn[i].y);
-    }
-    // Head slot s of the row lives at q_row + s*HD for s < n_q and at k_row + (s - n_q)*HD otherwise; the second
-    // base is pre-shifted by n_q heads so both cases are "base + s*HD".
-    const long long k_shift = static_cast<long long>(a.n_q) * HD;
-    const T* q_src = reinterpret_cast<const T*>(a.q) + row * a.q_stride + sub * N;
-    const T* k_src = reinterpret_cast<const T*>(a.k) + row * a.k_stride + sub * N - k_shift;
-    T* q_dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride + sub * N;
-    T* k_dst = nullptr;
-    if (a.n_kv) {
-        const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
-        k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + sub * N - k_shift;
+        const long long k_shift = static_cast<long long>(a.n_q) * HD;
+        q_dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride + sub * N;
+        k_dst = nullptr;
+        if (a.n_kv) {
+            const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
+            k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + sub * N - k_shift;
+        }
     }
 
-    auto fetch = [&](unsigned c, uint4& lo, uint4& hi) {
-        const unsigned slot = c * HPW + hsel;
-        if (c < end_chunk && slot < slots) {
-            const T* src = (slot < a.n_q ? q_src : k_src) + static_cast<size_t>(slot) * HD;
-            lo = ld_stream(src);
-            hi = ld_stream(src + HALF);
+    // Norm weights into shared memory: [q first half | q second half | k first half | k second half], each half in
+    // (j, lane, e) order; a missing weight vector is staged as ones. Called by every thread of the CTA.
+    static __device__ __forceinline__ void stage_weights(const QkArgs& a, float* w_shared) {
+        for (unsigned i = threadIdx.x; i < 2u * HD; i += blockDim.x) {
+            const unsigned kind = i / HD, d = i % HD, half = d / HALF, r = d % HALF;
+            const unsigned lane_of = r / N, j = (r % N) / 4, e = r % 4;
+            const void* src = kind ? a.k_norm_w : a.q_norm_w;
+            w_shared[kind * HD + half * HALF + (j * LPH + lane_of) * 4 + e] = src ? load_as_f32(src, a.w_dtype, d) : 1.0f;
         }
-    };
-    auto finish = [&](unsigned c, const uint4& lo, const uint4& hi) {
-        const unsigned slot = c * HPW + hsel;
-        const bool live = c < end_chunk && slot < slots;
+    }
+
+    // One pass: the head in slot `slot` (this lane group's head), raw halves in lo / hi. Every lane of the warp
+    // must call this together (the reduction shuffles); lanes with live == false contribute zeros and store nothing.
+    __device__ __forceinline__ void pass(const QkArgs& a, unsigned slot, bool live, const uint4& lo, const uint4& hi) const {
         const bool is_q = slot < a.n_q;
         float2 va[P], vb[P];
         if (live) {
@@ -176,6 +178,7 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
                 }
             }
         }
+        float2 s2 = make_float2(1.0f, 1.0f);
         if (NORM) {
             float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
@@ -190,20 +193,27 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
             }
             float ss = acc.x + acc.y;
 #pragma unroll
-            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // every lane takes part
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const bool has = is_q ? (a.q_norm_w != nullptr) : (a.k_norm_w != nullptr);
-            if (has && live) {
-                const float scale = inv_rms<T>(ss, static_cast<float>(HD), 1.0f / static_cast<float>(HD), a.eps);
-                const float2 s2 = make_float2(scale, scale);
-                const float* w = w_s + (is_q ? 0 : HD) + sub * 4;
+            const float scale = has ? inv_rms<T>(ss, static_cast<float>(HD), 1.0f / static_cast<float>(HD), a.eps) : 1.0f;
+            s2 = make_float2(scale, scale);
+            const float* w = w_s + (is_q ? 0 : HD) + sub * 4;  // ones where a kind has no norm weights
 #pragma unroll
-                for (int j = 0; j < N / 4; j++) {
-                    const float4 wa = *reinterpret_cast<const float4*>(w + j * LPH * 4);
-                    const float4 wb = *reinterpret_cast<const float4*>(w + HALF + j * LPH * 4);
-                    va[2 * j] = mul2(mul2(va[2 * j], s2), make_float2(wa.x, wa.y));
-                    va[2 * j + 1] = mul2(mul2(va[2 * j + 1], s2), make_float2(wa.z, wa.w));
-                    vb[2 * j] = mul2(mul2(vb[2 * j], s2), make_float2(wb.x, wb.y));
-                    vb[2 * j + 1] = mul2(mul2(vb[2 * j + 1], s2), make_float2(wb.z, wb.w));
+            for (int j = 0; j < N / 4; j++) {
+                const float4 wa = *reinterpret_cast<const float4*>(w + j * LPH * 4);
+                const float4 wb = *reinterpret_cast<const float4*>(w + HALF + j * LPH * 4);
+                const float2 wa0 = make_float2(wa.x, wa.y), wa1 = make_float2(wa.z, wa.w);
+                const float2 wb0 = make_float2(wb.x, wb.y), wb1 = make_float2(wb.z, wb.w);
+                if (sizeof(T) == 2) {  // scale applied after the rotation
+                    va[2 * j] = mul2(va[2 * j], wa0);
+                    va[2 * j + 1] = mul2(va[2 * j + 1], wa1);
+                    vb[2 * j] = mul2(vb[2 * j], wb0);
+                    vb[2 * j + 1] = mul2(vb[2 * j + 1], wb1);
+                } else {  // the reference's (v * scale) * w
+                    va[2 * j] = mul2(mul2(va[2 * j], s2), wa0);
+                    va[2 * j + 1] = mul2(mul2(va[2 * j + 1], s2), wa1);
+                    vb[2 * j] = mul2(mul2(vb[2 * j], s2), wb0);
+                    vb[2 * j + 1] = mul2(mul2(vb[2 * j + 1], s2), wb1);
                 }
             }
         }
@@ -211,10 +221,14 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
             float2 oa[P], ob[P];
 #pragma unroll
             for (int i = 0; i < P; i++) {
-                // a*cos - b*sin as a*cos + b*(-sin): the same bits, and it leaves the pair free to be fused or not
+                // a*cos - b*sin written as a*cos + b*(-sin): the same bits
                 if (sizeof(T) == 2) {
                     oa[i] = fma2(va[i], cs[i], mul2(vb[i], nsn[i]));
                     ob[i] = fma2(va[i], sn[i], mul2(vb[i], cs[i]));
+                    if (NORM) {
+                        oa[i] = mul2(oa[i], s2);
+                        ob[i] = mul2(ob[i], s2);
+                    }
                 } else {
                     oa[i] = add2(mul2(va[i], cs[i]), mul2(vb[i], nsn[i]));
                     ob[i] = add2(mul2(va[i], sn[i]), mul2(vb[i], cs[i]));
@@ -224,34 +238,107 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
             *reinterpret_cast<uint4*>(dst) = pack16p<T>(oa);
             *reinterpret_cast<uint4*>(dst + HALF) = pack16p<T>(ob);
         }
-    };
+    }
+};
 
-    // kRopeInFlight passes are loaded before the first is consumed: bytes in flight per warp, not warps per SM,
-    // are what keep HBM busy here (the per-lane state of a pass is too large for high occupancy). The first loads
-    // are issued before the norm weights are staged, so the staging barrier does not delay them.
+// Register variant: one warp walks a range of head groups of one row; the loads of kRopeInFlight passes are issued
+// before the first is consumed. Used when a row is split over several warps (few rows) or is too large to stage.
+template <typename T, int HD, bool NORM, bool BIAS>
+__global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const QkArgs a) {
+    pdl_sync();
+    using R = RopeRow<T, HD, NORM, BIAS>;
+    constexpr int N = R::N, HALF = R::HALF, HPW = R::HPW;
+    __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
+
+    const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    // Warps past the last row stay for the staging barrier below but are given an empty chunk range.
+    const bool valid = warp / a.wpr < a.rows;
+    const unsigned long long row = valid ? warp / a.wpr : a.rows - 1;
+    const unsigned first_chunk = static_cast<unsigned>(warp % a.wpr) * a.cpw;
+    const unsigned end_chunk = valid ? min(first_chunk + a.cpw, a.chunks) : first_chunk;
+    R r;
+    r.init(a, row, threadIdx.x & 31u, w_s);
+    // slot s of the row is at q_row + s*HD for s < n_q, at k_row + (s - n_q)*HD otherwise (second base pre-shifted)
+    const T* q_src = reinterpret_cast<const T*>(a.q) + row * a.q_stride + r.sub * N;
+    const T* k_src = reinterpret_cast<const T*>(a.k) + row * a.k_stride + r.sub * N - static_cast<long long>(a.n_q) * HD;
+    auto fetch = [&](unsigned c, uint4& lo, uint4& hi) {
+        const unsigned slot = c * HPW + r.hsel;
+        if (c < end_chunk && slot < r.slots) {
+            const T* src = (slot < a.n_q ? q_src : k_src) + static_cast<size_t>(slot) * HD;
+            lo = ld_stream(src);
+            hi = ld_stream(src + HALF);
+        }
+    };
     unsigned c = first_chunk;
     uint4 lo[kRopeInFlight], hi[kRopeInFlight];
 #pragma unroll
-    for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);
+    for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);  // issued before the staging barrier
     if (NORM) {
-        for (unsigned i = threadIdx.x; i < 2u * HD; i += blockDim.x) {
-            const unsigned kind = i / HD, d = i % HD, half = d / HALF, r = d % HALF;
-            const unsigned lane_of = r / N, j = (r % N) / 4, e = r % 4;
-            const void* src = kind ? a.k_norm_w : a.q_norm_w;
-            w_s[kind * HD + half * HALF + (j * LPH + lane_of) * 4 + e] = src ? load_as_f32(src, a.w_dtype, d) : 1.0f;
-        }
+        R::stage_weights(a, w_s);
         __syncthreads();
     }
     while (c < end_chunk) {
 #pragma unroll
         for (int i = 0; i < kRopeInFlight; i++) {
-            if (i == 0 || c + i < end_chunk) finish(c + i, lo[i], hi[i]);
+            const unsigned slot = (c + i) * HPW + r.hsel;
+            if (i == 0 || c + i < end_chunk) r.pass(a, slot, c + i < end_chunk && slot < r.slots, lo[i], hi[i]);
         }
         c += kRopeInFlight;
         if (c < end_chunk) {
 #pragma unroll
             for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);
         }
+    }
+}
+
+// Staged variant: lane 0 of each warp brings the whole row (its q heads, then its k heads) into shared memory with
+// two bulk asynchronous copies that complete on an mbarrier, so all of the row's bytes are in flight at once without
+// holding registers; the warp then walks the head groups out of shared memory and stores results straight to
+// global memory. Same lane mapping, arithmetic and results as qk_rope_kernel.
+template <typename T, int HD, bool NORM, bool BIAS>
+__global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) {
+    pdl_sync();
+    using R = RopeRow<T, HD, NORM, BIAS>;
+    constexpr int N = R::N, HALF = R::HALF, HPW = R::HPW;
+    extern __shared__ __align__(128) unsigned char dyn_smem[];
+    __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
+    const unsigned warps_per_cta = blockDim.x >> 5, warp_in_cta = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(dyn_smem);
+    unsigned char* stage = dyn_smem + 128 + static_cast<size_t>(warp_in_cta) * a.stage_bytes;
+    const uint32_t bar = smem_addr(&bars[warp_in_cta]);
+    const unsigned long long warp = static_cast<unsigned long long>(blockIdx.x) * warps_per_cta + warp_in_cta;
+    const bool valid = warp < a.rows;
+    const unsigned long long row = valid ? warp : a.rows - 1;
+    if (lane == 0) {
+        mbar_init(bar, 1);
+        mbar_init_fence();
+        if (valid) {
+            mbar_expect_tx(bar, a.q_row_bytes + a.k_row_bytes);
+            if (a.q_row_bytes) bulk_copy_g2s(smem_addr(stage), reinterpret_cast<const T*>(a.q) + row * a.q_stride, a.q_row_bytes, bar);
+            if (a.k_row_bytes) bulk_copy_g2s(smem_addr(stage + a.q_row_bytes), reinterpret_cast<const T*>(a.k) + row * a.k_stride, a.k_row_bytes, bar);
+        }
+    }
+    R r;
+    r.init(a, row, lane, w_s);
+    if (NORM) R::stage_weights(a, w_s);
+    __syncthreads();  // norm weights staged; every warp's mbarrier initialised before anyone waits on it
+    if (!valid) return;
+    if (!mbar_wait_bounded(bar, 0)) {
+        if (lane == 0) atomicOr(a.err_word, kErrTimeout);
+        mbar_wait_bounded(bar, 0);  // one more bounded chance for the copies in flight to land before leaving
+        return;
+    }
+    const T* srow = reinterpret_cast<const T*>(stage) + r.sub * N;
+#pragma unroll 2
+    for (unsigned c = 0; c < a.chunks; c++) {
+        const unsigned slot = c * HPW + r.hsel;
+        const bool live = slot < r.slots;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (live) {
+            lo = *reinterpret_cast<const uint4*>(srow + static_cast<size_t>(slot) * HD);
+            hi = *reinterpret_cast<const uint4*>(srow + static_cast<size_t>(slot) * HD + HALF);
+        }
+        r.pass(a, slot, live, lo, hi);
     }
 }
 
@@ -352,6 +439,34 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many rows for one launch");
     const unsigned grid = static_cast<unsigned>(blocks);
     const bool norm = a.q_norm_w || a.k_norm_w, bias = a.q_bias || a.k_bias;
+    a.q_row_bytes = a.n_q * a.head_dim * static_cast<unsigned>(sizeof(T));
+    a.k_row_bytes = a.n_kv * a.head_dim * static_cast<unsigned>(sizeof(T));
+    a.stage_bytes = (a.q_row_bytes + a.k_row_bytes + 127u) & ~127u;
+    a.err_word = ctx->err_word;
+    // Staged kernel: whole rows through shared memory by bulk copy. Needs one warp per row, row starts that are
+    // 16-byte aligned (true on this path) and a row small enough that several warps' stages fit in shared memory.
+    const bool staged_ok = a.wpr == 1 && a.stage_bytes <= 24u * 1024u && tune_env("LOKAL_CUDA_ROPE_STAGED", 1) != 0;
+    if (staged_ok) {
+        unsigned swpc = 8;
+        while (swpc > 1 && 128u + swpc * a.stage_bytes > 48u * 1024u) swpc /= 2;
+        const unsigned sgrid = static_cast<unsigned>((a.rows + swpc - 1) / swpc);
+        const size_t smem = 128u + static_cast<size_t>(swpc) * a.stage_bytes;
+#define LOKAL_ROPE_LAUNCH_STAGED(HD_)                                                                      \
+    do {                                                                                                   \
+        if (norm && bias) launch_k(qk_rope_staged_kernel<T, HD_, true, true>, sgrid, swpc * 32, smem, s, a);   \
+        else if (norm) launch_k(qk_rope_staged_kernel<T, HD_, true, false>, sgrid, swpc * 32, smem, s, a);     \
+        else if (bias) launch_k(qk_rope_staged_kernel<T, HD_, false, true>, sgrid, swpc * 32, smem, s, a);     \
+        else launch_k(qk_rope_staged_kernel<T, HD_, false, false>, sgrid, swpc * 32, smem, s, a);              \
+    } while (0)
+        switch (a.head_dim) {
+            case 64: LOKAL_ROPE_LAUNCH_STAGED(64); break;
+            case 128: LOKAL_ROPE_LAUNCH_STAGED(128); break;
+            default: LOKAL_ROPE_LAUNCH_STAGED(256); break;
+        }
+#undef LOKAL_ROPE_LAUNCH_STAGED
+        LOKAL_CHECK_LAUNCH(ctx, "qk_rope_staged_kernel");
+        return LOKAL_OK;
+    }
 #define LOKAL_ROPE_LAUNCH(HD_)                                                               \
     do {                                                                                     \
         if (norm && bias) launch_k(qk_rope_kernel<T, HD_, true, true>, grid, cta, 0, s, a);        \

@@ -234,3 +234,30 @@ def test_refusals(ctx, dev):
         ctx.rope_table(t, theta=1e4, rot_dim=63, rows=2)
     with pytest.raises(L.LokalCudaError):
         ctx.rope_table(t, theta=1e4, rot_dim=64, rows=2, pos0=-1)
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c5"])
+def test_large_batches_staged_kernel_equals_register_kernel(ctx, dev, oracle, name, monkeypatch):
+    # With enough rows one warp walks a whole row and the row is staged through shared memory by bulk copies;
+    # LOKAL_CUDA_ROPE_STAGED=0 keeps the register kernel. Same arithmetic: the two must agree bit for bit,
+    # and both must meet the bar against the oracle.
+    import dataclasses
+    cfg = dataclasses.replace(synth.CONFIGS[name], decode_positions=0)
+    rows = 2600
+    d = synth.layer_inputs(cfg, rows)
+    d.pop("positions", None)
+    q1, k1 = run_qk(ctx, dev, cfg, d, rows, pos0=123)
+    monkeypatch.setenv("LOKAL_CUDA_ROPE_STAGED", "0")
+    q0, k0 = run_qk(ctx, dev, cfg, d, rows, pos0=123)
+    monkeypatch.delenv("LOKAL_CUDA_ROPE_STAGED")
+    synth.assert_bits_equal(q1, q0, "staged vs register kernel, q")
+    synth.assert_bits_equal(k1, k0, "staged vs register kernel, k")
+    rq, rk = oracle.qk_rope_rows(d["q"], d["k"], n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
+                                 theta=cfg.theta, eps=cfg.eps, q_bias=d.get("q_bias"), k_bias=d.get("k_bias"),
+                                 q_norm_w=d.get("q_norm_w"), k_norm_w=d.get("k_norm_w"), pos0=123, threads=8)
+    if cfg.dtype == F32:
+        synth.check_f32(q1, rq, f"{name} q")
+        synth.check_f32(k1, rk, f"{name} k")
+    else:
+        synth.check_half(q1, rq, f"{name} q", cfg.dtype, atol=ROPE_HALF_ATOL)
+        synth.check_half(k1, rk, f"{name} k", cfg.dtype, atol=ROPE_HALF_ATOL)
