@@ -453,7 +453,132 @@ def cpu_baseline(cfg):
     t1 = one(1)
     return {"value": rows / float(np.median(times)), "unit": "tokens/s", "cores": threads, "kind": "port",
             "sample": f"{rows} of {cfg.rows} token rows, all {cfg.layers} layers, f32, median of 3 steps, {threads} token-parallel threads",
-            "single_thread_value": max(1, rows // threads) / t1}
+            "single_thread_value": max(1, rows // threads) / t1, "ops": cpu_ops(cfg, threads)}
+
+
+def cpu_ops(cfg, threads, rows=None):
+    """Each op of the path on its own, one layer, f32: token rows per second with 1 thread and with all threads."""
+    from oracle import lokal_oracle as O
+    rows = min(cfg.rows, 2048) if rows is None else rows
+    d = synth.layer_inputs(cfg, rows)
+
+    def best(fn, reps=3):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return rows / min(ts)
+
+    kw = dict(n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, theta=cfg.theta, eps=cfg.eps,
+              q_bias=d.get("q_bias"), k_bias=d.get("k_bias"), q_norm_w=d.get("q_norm_w"), k_norm_w=d.get("k_norm_w"),
+              positions=d.get("positions"))
+    out = {}
+    for name, fn in (("add_rmsnorm", lambda t: O.add_rmsnorm_rows(d["x"], d["delta"], d["w_norm"], cfg.eps, threads=t)),
+                     ("qk_rope", lambda t: O.qk_rope_rows(d["q"], d["k"], threads=t, **kw)),
+                     ("swiglu", lambda t: O.swiglu(d["gate"], d["up"], threads=t))):
+        out[name] = {"rows_per_s_1_thread": best(lambda: fn(1)), f"rows_per_s_{threads}_threads": best(lambda: fn(threads))}
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# C4: embedding gather + GGUF row dequant on its own (65536 Zipf(1.1) ids over a 151936-row table)
+# ------------------------------------------------------------------------------------------------
+
+def gather_workload(args, rank, world, local_rank):
+    import torch
+
+    import lokal_b200 as L
+    from oracle import lokal_oracle as O
+
+    if rank != 0:
+        return
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = L.Context(local_rank)
+    vocab, n = synth.C4_VOCAB, synth.C4_IDS
+    ids_np = synth.token_ids_zipf(vocab, n, synth.C4_SEED)
+    uniq = int(np.unique(ids_np).size)
+    ids = torch.from_numpy(ids_np.view(np.int32)).to(dev)
+    stream = ctx.stream_create()
+    tstream = torch.cuda.ExternalStream(stream, device=dev)
+    tdt = {L.F32: torch.float32, L.F16: torch.float16}
+    peak, peak_kind = measured_peak()
+    variants = [("q8_0_f32", L.Q8_0, synth.C4_DIM_Q8, L.F32), ("q8_0_f16", L.Q8_0, synth.C4_DIM_Q8, L.F16),
+                ("q4_k_f32", L.Q4_K, synth.C4_DIM_Q4K, L.F32), ("q4_k_f16", L.Q4_K, synth.C4_DIM_Q4K, L.F16)]
+    tables, kern = {}, {}
+    O.build()
+    threads = O.hardware_threads()
+    for name, ty, dim, odt in variants:
+        if (ty, dim) not in tables:
+            host = (synth.q8_0_table if ty == L.Q8_0 else synth.q4_k_table)(vocab, dim, synth.C4_SEED + ty)
+            tables[(ty, dim)] = (host, torch.from_numpy(host).to(dev))
+        host, table = tables[(ty, dim)]
+        es = 4 if odt == L.F32 else 2
+        nbuf = 8  # rotating outputs: 8 x (up to 268 MB) between reuses, far beyond L2
+        outs = torch.empty(nbuf, n, dim, dtype=tdt[odt], device=dev)
+        reps_per_graph = 16
+        ctx.graph_begin(stream)
+        for r in range(reps_per_graph):
+            ctx.embed_gather(table, ids, outs[r % nbuf], ggml_type=ty, vocab=vocab, dim=dim, n=n, out_dtype=odt, stream=stream)
+        g = ctx.graph_end(stream)
+        times = []
+        for rep in range(max(args.warmup, 3) + max(3, min(args.steps, 10))):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(tstream)
+            ctx.graph_launch(g, stream)
+            a1.record(tstream)
+            ctx.stream_sync(stream)
+            if rep >= max(args.warmup, 3):
+                times.append(a0.elapsed_time(a1) / reps_per_graph)
+        ctx.graph_destroy(g)
+        rb = L.row_bytes(ty, dim)
+        alg = n * (4 + dim * es) + uniq * rb
+        ms = float(np.mean(times))
+        kern[name] = {"us_per_launch": 1e3 * ms, "tokens_per_s": n / (ms * 1e-3), "bytes_per_launch": int(alg),
+                      "bytes_not_deduplicated": int(n * (rb + 4 + dim * es)), "gbs": alg / (ms * 1e-3) / 1e9,
+                      "frac": alg / (ms * 1e-3) / 1e9 / peak, "frac_of_nominal_8000": alg / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS}
+        # bit-exact spot check against the oracle on the first 2048 ids, every run
+        want = O.embed_gather(host, ty, vocab, dim, ids_np[:2048], threads=threads)
+        got = outs[0][:2048].to(torch.float32).cpu().numpy()
+        ref = want if odt == L.F32 else synth.round_to(want, odt)
+        kern[name]["bit_exact_vs_oracle_first_2048_rows"] = bool(np.array_equal(got.view(np.uint32), ref.view(np.uint32)))
+        del outs
+    # end to end: host ids in, host f32 rows out (Q8_0 -> f32, the configuration's first variant)
+    host, table = tables[(L.Q8_0, synth.C4_DIM_Q8)]
+    ctx.host_embed_gather(table, L.Q8_0, vocab, synth.C4_DIM_Q8, ids_np)
+    t0 = time.perf_counter()
+    e2e_reps = 3
+    for _ in range(e2e_reps):
+        ctx.host_embed_gather(table, L.Q8_0, vocab, synth.C4_DIM_Q8, ids_np)
+    dt = (time.perf_counter() - t0) / e2e_reps
+    e2e = {"value": n / dt, "unit": "tokens/s", "h2d_bytes_per_step": n * 4, "d2h_bytes_per_step": n * synth.C4_DIM_Q8 * 4,
+           "ms_per_step": 1e3 * dt, "api": "lokal_cuda_host_embed_gather (host ids in, host f32 rows out, table resident)"}
+    # CPU: the reference's gather loop (one row at a time, dequant_row_ref), 1 thread and all threads
+    cpu = {}
+    for t in (1, threads):
+        O.embed_gather(host, L.Q8_0, vocab, synth.C4_DIM_Q8, ids_np, threads=t)
+        t0 = time.perf_counter()
+        O.embed_gather(host, L.Q8_0, vocab, synth.C4_DIM_Q8, ids_np, threads=t)
+        cpu[t] = n / (time.perf_counter() - t0)
+    first = kern["q8_0_f32"]
+    line = {
+        "metric": "embedding gather + GGUF row dequant, tokens/s", "value": first["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+        "steps": len(times) * reps_per_graph, "warmup": max(args.warmup, 3), "ms_per_step": first["us_per_launch"] * 1e-3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 blocks -> f32", "data": "synthetic",
+        "config": {"workload": "gguf-gather-zipf65536", "vocab": vocab, "ids": n, "unique_ids": uniq,
+                   "tables": "Q8_0 151936x896; Q4_K 151936x1024 (a 896-wide Q4_K row cannot exist: 256-element super-blocks)",
+                   "l2": "outputs rotate over 8 buffers (up to 2.1 GB) between reuses"},
+        "gpu_launches": len(times) * reps_per_graph,
+        "roofline": {"bound": "hbm", "kernel": "gather_quant_staged_kernel<Q8_0,f32>", "achieved": first["gbs"], "peak": peak,
+                     "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": first["frac"], "traffic": None, "kernels": kern},
+        "e2e": e2e,
+        "cpu_baseline": {"value": cpu[threads], "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"all {n} ids, Q8_0 896-wide rows to f32", "single_thread_value": cpu[1]},
+    }
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -462,7 +587,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(synth.CONFIGS), default="c5")
+    ap.add_argument("--workload", choices=sorted(synth.CONFIGS) + ["c4"], default="c5")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures under a profiler)")
@@ -473,6 +598,10 @@ def main():
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if world == 1 and args.gpus > 1:
         sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+    if args.workload == "c4":
+        if args.impl == "reference":
+            sys.exit("--impl reference is defined for the layer workloads; the c4 line carries its own cpu_baseline")
+        return gather_workload(args, rank, world, local_rank)
     cfg = synth.CONFIGS[args.workload]
     if args.layers or args.rows:  # reduced sizes for profiler captures; the default is the full workload
         import dataclasses
