@@ -159,3 +159,19 @@ def test_refusals(ctx, dev):
     assert e.value.status == L.capi.ERR_BAD_ARG
     ctx.rmsnorm(x, w, x, rows=0, dim=8, eps=1e-5, dtype=F32)  # empty batch is fine
     ctx.stream_sync()
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c5"])
+@pytest.mark.parametrize("fused", [False, True])
+def test_large_batches(ctx, dev, oracle, name, fused):
+    cfg = synth.CONFIGS[name]
+    rows = 2600
+    d = synth.layer_inputs(cfg, rows)
+    delta = d["delta"] if fused else None
+    x1, n1, _, _ = run_norm(ctx, dev, d["x"], delta, d["w_norm"], cfg.eps, cfg.dtype, w_dtype=cfg.dtype)
+    ref_x, ref_xn = oracle.add_rmsnorm_rows(d["x"], delta, d["w_norm"], cfg.eps, threads=8)
+    if cfg.dtype == F32:
+        synth.check_f32(n1, ref_xn, f"{name} rmsnorm")
+    else:
+        synth.check_half(n1, ref_xn, f"{name} rmsnorm", cfg.dtype)
+    synth.assert_bits_equal(x1, synth.round_to(ref_x, cfg.dtype), "x + delta")
