@@ -235,6 +235,45 @@ LOKAL_API int lokal_cuda_embed_gather(lokal_cuda_ctx* ctx, lokal_cuda_stream s, 
 LOKAL_API int lokal_cuda_dequant_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, int ggml_type, const void* src,
                                       size_t rows, size_t cols, void* out, int out_dtype);
 
+/* ---- K/V staging into the cache -----------------------------------------------------
+ * The step right after RoPE: fresh K and V rows are narrowed to the cache type and
+ * written to their cache rows. Reference: f32_to_f16 (src/gpu/kernels.metal:2118),
+ * batched-decode row addressing (slot*max_seq + pos)*kv_dim (src/gpu/kernels.metal:3310,
+ * 3411-3412; RowMeta{pos,slot}, src/gpu/metal.rs:79-82), and the sink + ring store of the
+ * windowed backends: WindowCfg / slot_of (src/lowmem/mod.rs:163-193), write_spans
+ * (src/lowmem/forward.rs:256-271; src/gpu/metal.rs:673-691).
+ *
+ * The reference splits a chunk into at most three host-computed spans; here the cache row
+ * of every token row is computed on the device into an index array, which both
+ * lokal_cuda_kv_stage and lokal_cuda_qk_rope (k_out_rows) consume. */
+typedef struct lokal_kv_layout {
+    uint64_t max_seq;   /* rows per slot in the linear layout; ignored when windowed */
+    uint64_t sink;      /* windowed store: positions 0..sink are pinned ... */
+    uint64_t sink_pad;  /* ... in a region padded to this many rows ... */
+    uint64_t ring;      /* ... followed by a ring of this many rows; ring == 0 selects the linear layout */
+} lokal_kv_layout;
+
+/* WindowCfg::new(w, sink) with the reference's prefill chunk of slack (512 in the reference,
+ * src/gpu/metal.rs:30): sink_pad and ring are rounded up to multiples of 128. Host only. */
+LOKAL_API int lokal_cuda_window_cfg(uint64_t window, uint64_t sink, uint64_t prefill_chunk, lokal_kv_layout* out);
+/* WindowCfg::slot_of: the store row (within one slot) that holds position p. Host only. */
+LOKAL_API uint64_t lokal_cuda_window_slot_of(const lokal_kv_layout* layout, uint64_t p);
+/* write_spans: destination spans (first chunk row, first store row, length) for positions
+ * [pos0, pos0+n); spans[] must hold 3 entries of 3 values. Returns the span count. Host only. */
+LOKAL_API int lokal_cuda_window_write_spans(const lokal_kv_layout* layout, uint64_t pos0, uint64_t n, uint64_t* spans);
+
+/* Cache row of every token row, on the device:
+ *   linear:   slot_r * max_seq + pos_r            windowed: slot_r * (sink_pad + ring) + slot_of(pos_r)
+ * positions / slots: device int32[rows] / uint32[rows], or NULL for pos0 + r / slot0. */
+LOKAL_API int lokal_cuda_kv_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_kv_layout* layout,
+                                 const int32_t* positions, int64_t pos0, const uint32_t* slots, uint32_t slot0,
+                                 size_t rows, uint32_t* rows_out);
+/* dst[dst_rows[r]] = narrow(src[r]) for `rows` rows of `width` elements (strides in elements;
+ * dst_rows NULL = row r). Types F32 / F16 / BF16; a narrowing conversion rounds to nearest even. */
+LOKAL_API int lokal_cuda_kv_stage(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* src, int src_dtype,
+                                  size_t src_row_stride, void* dst, int dst_dtype, size_t dst_row_stride,
+                                  const uint32_t* dst_rows, size_t rows, size_t width);
+
 /* ---- Token-row sharding over GPUs ---------------------------------------------
  * Rows are independent, so GPU `rank` of `n_gpus` owns the contiguous block
  * [row0, row0+count); no exchange happens on the path. The reference has no

@@ -38,6 +38,11 @@ class QkRopeParams(C.Structure):
     ]
 
 
+class KvLayout(C.Structure):
+    """Mirror of lokal_kv_layout."""
+    _fields_ = [("max_seq", C.c_uint64), ("sink", C.c_uint64), ("sink_pad", C.c_uint64), ("ring", C.c_uint64)]
+
+
 class PassConfig(C.Structure):
     """Mirror of lokal_pass_config."""
     _fields_ = [
@@ -105,6 +110,11 @@ SIGNATURES = {
     "lokal_cuda_swiglu": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i]),
     "lokal_cuda_embed_gather": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _vp, _sz, _vp, _i]),
     "lokal_cuda_dequant_rows": (_i, [_vp, _vp, _i, _vp, _sz, _sz, _vp, _i]),
+    "lokal_cuda_window_cfg": (_i, [C.c_uint64, C.c_uint64, C.c_uint64, C.POINTER(KvLayout)]),
+    "lokal_cuda_window_slot_of": (C.c_uint64, [C.POINTER(KvLayout), C.c_uint64]),
+    "lokal_cuda_window_write_spans": (_i, [C.POINTER(KvLayout), C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "lokal_cuda_kv_rows": (_i, [_vp, _vp, C.POINTER(KvLayout), _vp, _i64, _vp, _u32, _sz, _vp]),
+    "lokal_cuda_kv_stage": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _sz, _vp, _sz, _sz]),
     "lokal_cuda_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "lokal_cuda_pass_create": (_i, [_vp, C.POINTER(PassConfig), C.POINTER(PassWeights), _pp]),
     "lokal_cuda_pass_destroy": (_i, [_vp, _vp]),

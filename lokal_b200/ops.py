@@ -14,7 +14,7 @@ import ctypes as C
 import numpy as np
 
 from . import capi
-from .capi import BF16, F16, F32, Q4_K, Q8_0, LokalCudaError, PassConfig, PassInputs, PassWeights, QkRopeParams
+from .capi import BF16, F16, F32, Q4_K, Q8_0, KvLayout, LokalCudaError, PassConfig, PassInputs, PassWeights, QkRopeParams
 
 
 def _ptr(x):
@@ -189,6 +189,19 @@ class Context:
         self._check(self._lib.lokal_cuda_dequant_rows(self._h, stream, ggml_type, _ptr(src), rows, cols, _ptr(out),
                                                       out_dtype))
 
+    def kv_rows(self, rows_out, *, layout: KvLayout, rows, positions=None, pos0=0, slots=None, slot0=0, stream=None):
+        """Cache row of every token row (linear slot*max_seq+pos, or sink + ring) into a device uint32 array."""
+        self._check(self._lib.lokal_cuda_kv_rows(self._h, stream, C.byref(layout), _ptr(positions), pos0, _ptr(slots),
+                                                 slot0, rows, _ptr(rows_out)))
+
+    def kv_stage(self, src, dst, *, src_dtype, dst_dtype, rows, width, src_row_stride=None, dst_row_stride=None,
+                 dst_rows=None, stream=None):
+        """dst[dst_rows[r]] = narrow(src[r]): fresh K/V rows into their cache rows."""
+        self._check(self._lib.lokal_cuda_kv_stage(self._h, stream, _ptr(src), src_dtype,
+                                                  width if src_row_stride is None else src_row_stride, _ptr(dst),
+                                                  dst_dtype, width if dst_row_stride is None else dst_row_stride,
+                                                  _ptr(dst_rows), rows, width))
+
     # -- host-slice mirrors of the reference's CPU signatures ----------------------
     def host_rmsnorm(self, x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
         """math::rmsnorm(x, weight, eps) -> new vector; x may be [dim] or [rows, dim]."""
@@ -299,6 +312,27 @@ def blk_bytes(ggml_type: int) -> int:
 
 def row_bytes(ggml_type: int, n: int) -> int:
     return capi.load().lokal_cuda_row_bytes(ggml_type, n)
+
+
+def window_cfg(window: int, sink: int, prefill_chunk: int = 512) -> KvLayout:
+    """WindowCfg::new: sink region padded to 128 rows, ring = window + one prefill chunk, rounded up to 128."""
+    lay = KvLayout()
+    rc = capi.load().lokal_cuda_window_cfg(window, sink, prefill_chunk, C.byref(lay))
+    if rc != capi.OK:
+        raise LokalCudaError(rc, f"invalid window config: window {window}, sink {sink}")
+    return lay
+
+
+def window_slot_of(layout: KvLayout, p: int) -> int:
+    return int(capi.load().lokal_cuda_window_slot_of(C.byref(layout), p))
+
+
+def window_write_spans(layout: KvLayout, pos0: int, n: int) -> list[tuple[int, int, int]]:
+    buf = (C.c_uint64 * 9)()
+    cnt = capi.load().lokal_cuda_window_write_spans(C.byref(layout), pos0, n, buf)
+    if cnt < 0:
+        raise LokalCudaError(capi.ERR_BAD_ARG, "chunk does not fit three spans (longer than the ring) or layout is linear")
+    return [(int(buf[3 * i]), int(buf[3 * i + 1]), int(buf[3 * i + 2])) for i in range(cnt)]
 
 
 def shard_rows(n_rows: int, n_gpus: int, rank: int) -> tuple[int, int]:
