@@ -308,26 +308,41 @@ ORACLE_API void lokal_ref_swiglu(const float* gate, const float* up, size_t n, f
 // GGUF block formats (src/gguf/dequant.rs:21-41, 81-119)
 // ---------------------------------------------------------------------------
 
-enum : uint32_t { GGML_F32 = 0, GGML_F16 = 1, GGML_Q8_0 = 8, GGML_Q4_K = 12, GGML_BF16 = 30 };
+enum : uint32_t {
+    GGML_F32 = 0, GGML_F16 = 1, GGML_Q4_0 = 2, GGML_Q5_0 = 6, GGML_Q8_0 = 8, GGML_Q2_K = 10, GGML_Q3_K = 11,
+    GGML_Q4_K = 12, GGML_Q5_K = 13, GGML_Q6_K = 14, GGML_IQ4_NL = 20, GGML_IQ4_XS = 23, GGML_BF16 = 30
+};
 
 ORACLE_API size_t lokal_ref_blk_elems(uint32_t ty) {
     switch (ty) {
         case GGML_F32: case GGML_F16: case GGML_BF16: return 1;
-        case GGML_Q8_0: return 32;
-        case GGML_Q4_K: return 256;
+        case GGML_Q4_0: case GGML_Q5_0: case GGML_Q8_0: case GGML_IQ4_NL: return 32;
+        case GGML_Q2_K: case GGML_Q3_K: case GGML_Q4_K: case GGML_Q5_K: case GGML_Q6_K: case GGML_IQ4_XS: return 256;
         default: return 0;
     }
 }
 
+// sizeof(block_*) of ggml, as src/gguf/dequant.rs:94-114 lists them.
 ORACLE_API size_t lokal_ref_blk_bytes(uint32_t ty) {
     switch (ty) {
         case GGML_F32: return 4;
         case GGML_F16: case GGML_BF16: return 2;
+        case GGML_Q4_0: return 2 + 16;
+        case GGML_Q5_0: return 2 + 4 + 16;
         case GGML_Q8_0: return 2 + 32;
+        case GGML_IQ4_NL: return 2 + 16;
+        case GGML_IQ4_XS: return 2 + 2 + 4 + 128;
+        case GGML_Q2_K: return 16 + 64 + 2 + 2;
+        case GGML_Q3_K: return 32 + 64 + 12 + 2;
         case GGML_Q4_K: return 2 + 2 + 12 + 128;
+        case GGML_Q5_K: return 2 + 2 + 12 + 32 + 128;
+        case GGML_Q6_K: return 128 + 64 + 16 + 2;
         default: return 0;
     }
 }
+
+// The 16-entry codebook of the IQ4 types (kvalues_iq4nl of ggml; src/gguf/dequant.rs:165-166). Format data.
+static const int8_t kIq4nlValues[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
 // n / blk_elems * blk_bytes with integer division (src/gguf/dequant.rs:117-119).
 ORACLE_API size_t lokal_ref_row_bytes(uint32_t ty, size_t n) {
@@ -404,6 +419,163 @@ ORACLE_API int lokal_ref_dequant_row(uint32_t ty, const uint8_t* src, size_t src
                 }
             }
             return 0;
+        case GGML_Q4_0:  // src/gguf/dequant.rs:204-214: f16 d, 16 bytes of nibbles; (nibble - 8) * d
+            for (size_t b = 0; b < n / 32; b++) {
+                const uint8_t* blk = src + b * 18;
+                float d = f16_bits_at(blk, 0);
+                float* y = out + b * 32;
+                for (size_t j = 0; j < 16; j++) {
+                    uint8_t q = blk[2 + j];
+                    y[j] = (float)((int)(q & 0x0F) - 8) * d;
+                    y[j + 16] = (float)((int)(q >> 4) - 8) * d;
+                }
+            }
+            return 0;
+        case GGML_Q5_0:  // src/gguf/dequant.rs:215-230: Q4_0 plus a fifth bit per element in a u32; (value - 16) * d
+            for (size_t b = 0; b < n / 32; b++) {
+                const uint8_t* blk = src + b * 22;
+                float d = f16_bits_at(blk, 0);
+                uint32_t qh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24);
+                float* y = out + b * 32;
+                for (size_t j = 0; j < 16; j++) {
+                    uint8_t hi0 = (uint8_t)(((qh >> j) << 4) & 0x10);
+                    uint8_t hi1 = (uint8_t)((qh >> (j + 12)) & 0x10);
+                    uint8_t q = blk[6 + j];
+                    y[j] = (float)((int)((q & 0x0F) | hi0) - 16) * d;
+                    y[j + 16] = (float)((int)((q >> 4) | hi1) - 16) * d;
+                }
+            }
+            return 0;
+        case GGML_IQ4_NL:  // src/gguf/dequant.rs:405-415: f16 d, nibbles index the 16-entry codebook
+            for (size_t b = 0; b < n / 32; b++) {
+                const uint8_t* blk = src + b * 18;
+                float d = f16_bits_at(blk, 0);
+                float* y = out + b * 32;
+                for (size_t j = 0; j < 16; j++) {
+                    uint8_t q = blk[2 + j];
+                    y[j] = d * (float)kIq4nlValues[q & 0x0F];
+                    y[j + 16] = d * (float)kIq4nlValues[q >> 4];
+                }
+            }
+            return 0;
+        case GGML_IQ4_XS:  // src/gguf/dequant.rs:419-436: d | scales_h u16 | scales_l[4] | qs[128]; 6-bit scales biased by -32
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 136;
+                float d = f16_bits_at(blk, 0);
+                unsigned scales_h = (unsigned)blk[2] | ((unsigned)blk[3] << 8);
+                float* y = out + b * 256;
+                for (size_t ib = 0; ib < 8; ib++) {  // eight sub-blocks of 32
+                    int ls = (int)((blk[4 + ib / 2] >> (4 * (ib % 2))) & 0xF) | (int)(((scales_h >> (2 * ib)) & 3) << 4);
+                    float dl = d * (float)(ls - 32);
+                    const uint8_t* q = blk + 8 + ib * 16;
+                    for (size_t j = 0; j < 16; j++) {
+                        y[ib * 32 + j] = dl * (float)kIq4nlValues[q[j] & 0x0F];
+                        y[ib * 32 + 16 + j] = dl * (float)kIq4nlValues[q[j] >> 4];
+                    }
+                }
+            }
+            return 0;
+        case GGML_Q2_K:  // src/gguf/dequant.rs:437-451: scales[16] | qs[64] | d | dmin; (d*sc)*q - dmin*min
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 84;
+                float d = f16_bits_at(blk, 80), dmin = f16_bits_at(blk, 82);
+                float* y = out + b * 256;
+                for (size_t nh = 0; nh < 2; nh++) {          // halves of 128 elements share a 32-byte run of quants
+                    for (size_t j = 0; j < 4; j++) {         // 2-bit field j of each quant byte
+                        for (size_t half = 0; half < 2; half++) {
+                            uint8_t sc = blk[nh * 8 + j * 2 + half];
+                            float dl = d * (float)(sc & 0xF), ml = dmin * (float)(sc >> 4);
+                            const uint8_t* q = blk + 16 + nh * 32 + half * 16;
+                            for (size_t l = 0; l < 16; l++) {
+                                float t = dl * (float)((q[l] >> (2 * j)) & 3);
+                                y[nh * 128 + j * 32 + half * 16 + l] = t - ml;
+                            }
+                        }
+                    }
+                }
+            }
+            return 0;
+        case GGML_Q3_K:  // src/gguf/dequant.rs:457-473: hmask[32] | qs[64] | scales[12] | d; a CLEAR hmask bit subtracts 4
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 110;
+                float d_all = f16_bits_at(blk, 108);
+                const uint8_t* p = blk + 96;
+                int scales[16];
+                for (size_t s = 0; s < 16; s++) {
+                    // six-bit scale s: low nibble from bytes 0..7 (low nibbles first, then high nibbles), top two bits
+                    // from the 2-bit fields of bytes 8..11 -- ggml's aux shuffle written out per scale
+                    size_t byte = s % 4, grp = s / 4;
+                    unsigned lo = grp < 2 ? (unsigned)(p[(grp & 1) * 4 + byte] & 0xF) : (unsigned)(p[(grp & 1) * 4 + byte] >> 4);
+                    unsigned hi = ((unsigned)p[8 + byte] >> (2 * grp)) & 3u;
+                    scales[s] = (int)(lo | (hi << 4)) - 32;
+                }
+                float* y = out + b * 256;
+                for (size_t nh = 0; nh < 2; nh++) {
+                    for (size_t j = 0; j < 4; j++) {
+                        uint8_t mbit = (uint8_t)(1u << (nh * 4 + j));
+                        for (size_t half = 0; half < 2; half++) {
+                            float dl = d_all * (float)scales[nh * 8 + j * 2 + half];
+                            const uint8_t* q = blk + 32 + nh * 32 + half * 16;
+                            const uint8_t* hm = blk + half * 16;
+                            for (size_t l = 0; l < 16; l++) {
+                                int v = (int)((q[l] >> (2 * j)) & 3) - ((hm[l] & mbit) ? 0 : 4);
+                                y[nh * 128 + j * 32 + half * 16 + l] = dl * (float)v;
+                            }
+                        }
+                    }
+                }
+            }
+            return 0;
+        case GGML_Q5_K:  // src/gguf/dequant.rs:484-510: Q4_K plus one high bit per element in qh[32]
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 176;
+                float d = f16_bits_at(blk, 0), dmin = f16_bits_at(blk, 2);
+                const uint8_t* scales = blk + 4;
+                const uint8_t* qh = blk + 16;
+                const uint8_t* qs = blk + 48;
+                float* y = out + b * 256;
+                for (size_t g = 0; g < 4; g++) {  // groups of 64 elements
+                    const uint8_t* ql = qs + g * 32;
+                    uint8_t sc, m;
+                    scale_min_k4(2 * g, scales, &sc, &m);
+                    float d1 = d * (float)sc, m1 = dmin * (float)m;
+                    scale_min_k4(2 * g + 1, scales, &sc, &m);
+                    float d2 = d * (float)sc, m2 = dmin * (float)m;
+                    uint8_t u1 = (uint8_t)(1u << (2 * g)), u2 = (uint8_t)(2u << (2 * g));
+                    for (size_t l = 0; l < 32; l++) {
+                        int lo = (int)(ql[l] & 0x0F) + ((qh[l] & u1) ? 16 : 0);
+                        int hi = (int)(ql[l] >> 4) + ((qh[l] & u2) ? 16 : 0);
+                        float a = d1 * (float)lo, c = d2 * (float)hi;
+                        y[g * 64 + l] = a - m1;
+                        y[g * 64 + 32 + l] = c - m2;
+                    }
+                }
+            }
+            return 0;
+        case GGML_Q6_K:  // src/gguf/dequant.rs:511-533: ql[128] | qh[64] | int8 scales[16] | d; (d*sc)*(q - 32)
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 210;
+                float d = f16_bits_at(blk, 208);
+                float* y = out + b * 256;
+                for (size_t h = 0; h < 2; h++) {  // halves of 128 elements
+                    const uint8_t* ql = blk + h * 64;
+                    const uint8_t* qh = blk + 128 + h * 32;
+                    const int8_t* sc = (const int8_t*)(blk + 192 + h * 8);
+                    for (size_t l = 0; l < 32; l++) {
+                        size_t is = l / 16;
+                        int q1 = (int)(int8_t)((ql[l] & 0x0F) | (((qh[l] >> 0) & 3) << 4)) - 32;
+                        int q2 = (int)(int8_t)((ql[l + 32] & 0x0F) | (((qh[l] >> 2) & 3) << 4)) - 32;
+                        int q3 = (int)(int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+                        int q4 = (int)(int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+                        float s1 = d * (float)sc[is], s2 = d * (float)sc[is + 2], s3 = d * (float)sc[is + 4], s4 = d * (float)sc[is + 6];
+                        y[h * 128 + l] = s1 * (float)q1;
+                        y[h * 128 + l + 32] = s2 * (float)q2;
+                        y[h * 128 + l + 64] = s3 * (float)q3;
+                        y[h * 128 + l + 96] = s4 * (float)q4;
+                    }
+                }
+            }
+            return 0;
     }
     return -2;
 }
@@ -476,8 +648,17 @@ ORACLE_API int64_t lokal_ref_embed_gather(const uint8_t* table, uint32_t ty, siz
 // LCG bytes + negative subnormal scale, LCG bytes + max f16 scale with
 // max-magnitude quants}. `out` holds n_rows*n_blocks*blk_bytes bytes.
 ORACLE_API int lokal_ref_adversarial_rows(uint32_t ty, size_t n_blocks, size_t n_rows, uint8_t* out) {
-    if (ty != GGML_Q8_0 && ty != GGML_Q4_K) return -2;
     size_t bb = lokal_ref_blk_bytes(ty);
+    if (lokal_ref_blk_elems(ty) < 32) return -2;
+    // where the f16 scale d sits in a block, and dmin for the types that have one (-1 = none)
+    int d_off = 0, dmin_off = -1;
+    switch (ty) {
+        case GGML_Q4_K: case GGML_Q5_K: dmin_off = 2; break;
+        case GGML_Q2_K: d_off = 80; dmin_off = 82; break;   // at the END of the block
+        case GGML_Q3_K: d_off = 108; break;
+        case GGML_Q6_K: d_off = 208; break;
+        default: break;
+    }
     uint32_t lcg = 0x2545F491u;
     const uint8_t scale_bytes[4][2] = {{0x00, 0x00}, {0x01, 0x00}, {0xFF, 0x83}, {0xFF, 0x7B}};
     for (size_t row = 0; row < n_rows; row++) {
@@ -490,15 +671,32 @@ ORACLE_API int lokal_ref_adversarial_rows(uint32_t ty, size_t n_blocks, size_t n
                 lcg = lcg * 1664525u + 1013904223u;
                 b[i] = (uint8_t)(lcg >> 16);
             }
-            b[0] = scale_bytes[variant][0];
-            b[1] = scale_bytes[variant][1];
-            if (ty == GGML_Q4_K) {
-                b[2] = scale_bytes[3 - variant + 1][0];
-                b[3] = scale_bytes[3 - variant + 1][1];
+            b[d_off] = scale_bytes[variant][0];
+            b[d_off + 1] = scale_bytes[variant][1];
+            if (dmin_off >= 0) {
+                b[dmin_off] = scale_bytes[3 - variant + 1][0];
+                b[dmin_off + 1] = scale_bytes[3 - variant + 1][1];
             }
-            if (variant == 3) {
-                if (ty == GGML_Q8_0) std::memset(b + 2, 0x80, 32);
-                else std::memset(b + 4, 0xFF, 140);
+            if (variant != 3) continue;
+            switch (ty) {  // max-magnitude quants under the max scale (src/lowmem/pool.rs:1131-1189)
+                case GGML_Q8_0: std::memset(b + 2, 0x80, 32); break;
+                case GGML_Q4_0: std::memset(b + 2, 0x0F, 16); break;
+                case GGML_Q5_0: std::memset(b + 2, 0xFF, 20); break;          // qh and nibbles all set
+                case GGML_Q4_K: std::memset(b + 4, 0xFF, 140); break;         // all scale/min bits, all nibbles
+                case GGML_Q5_K: std::memset(b + 4, 0xFF, 172); break;         // scales, high bits, nibbles
+                case GGML_IQ4_NL: std::memset(b + 2, 0xFF, 16); break;        // codebook index 15 everywhere
+                case GGML_IQ4_XS: std::memset(b + 2, 0xFF, 134); break;       // ls = 63, every nibble 15
+                case GGML_Q2_K: std::memset(b, 0xFF, 80); break;              // every scale and min maxed, quants 3
+                case GGML_Q3_K:
+                    std::memset(b, 0x00, 32);        // hmask clear: the -4 path everywhere
+                    std::memset(b + 32, 0xFF, 64);   // quants all 3
+                    std::memset(b + 96, 0xFF, 12);   // scales all 63
+                    break;
+                case GGML_Q6_K:
+                    std::memset(b, 0xFF, 192);
+                    std::memset(b + 192, 0x80, 16);  // scales = -128
+                    break;
+                default: break;
             }
         }
     }

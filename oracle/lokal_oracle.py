@@ -17,6 +17,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "liblokal_oracle.so")
 
 F32, F16, Q8_0, Q4_K, BF16 = 0, 1, 8, 12, 30
+Q4_0, Q5_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 2, 6, 10, 11, 13, 14, 20, 23
+QUANT_TYPES = (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS)
 
 
 def build(force: bool = False) -> str:

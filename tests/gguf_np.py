@@ -1,0 +1,165 @@
+"""A second, independent reading of the GGUF block formats: vectorised numpy decoders written from the block
+layouts (sizeof and field order as src/gguf/dequant.rs:94-114 lists them), used to cross-check the C++ oracle
+before either judges the GPU. Every f32 multiply / subtract is a separate numpy f32 operation, so the rounding
+sequence is the one the reference's expressions have. Returns f32 arrays of shape [n_blocks * elems]."""
+import numpy as np
+
+F32 = np.float32
+KV = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int32)  # IQ4 codebook
+
+
+def _f16(b, off):
+    return np.ascontiguousarray(b[:, off:off + 2]).view(np.float16).astype(F32)[:, 0]
+
+
+def _blocks(raw, size):
+    raw = np.ascontiguousarray(raw, np.uint8)
+    assert raw.size % size == 0
+    return raw.reshape(-1, size)
+
+
+def _scale_min_k4(s):
+    """12 packed bytes -> (8 six-bit scales, 8 six-bit mins) per block."""
+    s = s.astype(np.uint32)
+    sc = np.empty((s.shape[0], 8), np.uint32)
+    mn = np.empty_like(sc)
+    sc[:, :4] = s[:, 0:4] & 63
+    mn[:, :4] = s[:, 4:8] & 63
+    sc[:, 4:] = (s[:, 8:12] & 0xF) | ((s[:, 0:4] >> 6) << 4)
+    mn[:, 4:] = (s[:, 8:12] >> 4) | ((s[:, 4:8] >> 6) << 4)
+    return sc, mn
+
+
+def q8_0(raw):
+    b = _blocks(raw, 34)
+    return (b[:, 2:].view(np.int8).astype(F32) * _f16(b, 0)[:, None]).reshape(-1)
+
+
+def q4_0(raw):
+    b = _blocks(raw, 18)
+    q = b[:, 2:].astype(np.int32)
+    v = np.concatenate([(q & 15) - 8, (q >> 4) - 8], axis=1).astype(F32)
+    return (v * _f16(b, 0)[:, None]).reshape(-1)
+
+
+def q5_0(raw):
+    b = _blocks(raw, 22)
+    qh = np.ascontiguousarray(b[:, 2:6]).view("<u4")[:, 0].astype(np.uint64)
+    j = np.arange(16, dtype=np.uint64)
+    hi_lo = ((qh[:, None] >> j) & 1).astype(np.int32) << 4
+    hi_hi = ((qh[:, None] >> (j + 16)) & 1).astype(np.int32) << 4
+    q = b[:, 6:].astype(np.int32)
+    v = np.concatenate([((q & 15) | hi_lo) - 16, ((q >> 4) | hi_hi) - 16], axis=1).astype(F32)
+    return (v * _f16(b, 0)[:, None]).reshape(-1)
+
+
+def iq4_nl(raw):
+    b = _blocks(raw, 18)
+    q = b[:, 2:].astype(np.int32)
+    v = np.concatenate([KV[q & 15], KV[q >> 4]], axis=1).astype(F32)
+    return (_f16(b, 0)[:, None] * v).reshape(-1)
+
+
+def iq4_xs(raw):
+    b = _blocks(raw, 136)
+    d = _f16(b, 0)
+    sh = np.ascontiguousarray(b[:, 2:4]).view("<u2")[:, 0].astype(np.int32)
+    sl = b[:, 4:8].astype(np.int32)
+    ib = np.arange(8)
+    ls = ((sl[:, ib // 2] >> (4 * (ib % 2))) & 15) | (((sh[:, None] >> (2 * ib)) & 3) << 4)
+    dl = d[:, None] * (ls - 32).astype(F32)                       # [nb, 8]
+    q = b[:, 8:].reshape(-1, 8, 16).astype(np.int32)
+    v = np.concatenate([KV[q & 15], KV[q >> 4]], axis=2).astype(F32)  # [nb, 8, 32]
+    return (dl[:, :, None] * v).reshape(-1)
+
+
+def q2_k(raw):
+    b = _blocks(raw, 84)
+    d, dmin = _f16(b, 80), _f16(b, 82)
+    sc = b[:, :16].astype(np.int32).reshape(-1, 2, 4, 2)           # [nb, half128, field j, half16]
+    qs = b[:, 16:80].astype(np.int32).reshape(-1, 2, 2, 16)        # [nb, half128, half16, l]
+    j = np.arange(4).reshape(1, 1, 4, 1, 1)
+    q = (qs[:, :, None, :, :] >> (2 * j)) & 3                      # [nb, 2, 4, 2, 16]
+    dl = d[:, None, None, None] * (sc & 15).astype(F32)
+    ml = dmin[:, None, None, None] * (sc >> 4).astype(F32)
+    y = (dl[..., None] * q.astype(F32)).astype(F32) - ml[..., None]
+    return y.astype(F32).reshape(-1)
+
+
+def q3_k(raw):
+    b = _blocks(raw, 110)
+    d = _f16(b, 108)
+    p = b[:, 96:108].astype(np.uint32)
+    w = lambda i: p[:, 4 * i] | (p[:, 4 * i + 1] << 8) | (p[:, 4 * i + 2] << 16) | (p[:, 4 * i + 3] << 24)
+    a0, a1, t = w(0), w(1), w(2)
+    k1, k2 = np.uint32(0x03030303), np.uint32(0x0f0f0f0f)
+    aux = [(a0 & k2) | (((t >> 0) & k1) << 4), (a1 & k2) | (((t >> 2) & k1) << 4),
+           ((a0 >> 4) & k2) | (((t >> 4) & k1) << 4), ((a1 >> 4) & k2) | (((t >> 6) & k1) << 4)]
+    scales = np.stack([(a >> (8 * k)) & 0xFF for a in aux for k in range(4)], axis=1).astype(np.int32) - 32  # [nb, 16]
+    sc = scales.reshape(-1, 2, 4, 2)
+    hm = b[:, :32].astype(np.int32).reshape(-1, 1, 1, 2, 16)
+    qs = b[:, 32:96].astype(np.int32).reshape(-1, 2, 1, 2, 16)
+    j = np.arange(4).reshape(1, 1, 4, 1, 1)
+    nh = np.arange(2).reshape(1, 2, 1, 1, 1)
+    q = (qs >> (2 * j)) & 3
+    hi = np.where((hm >> (nh * 4 + j)) & 1, 0, 4)
+    dl = d[:, None, None, None] * sc.astype(F32)
+    return (dl[..., None] * (q - hi).astype(F32)).astype(F32).reshape(-1)
+
+
+def q4_k(raw):
+    b = _blocks(raw, 144)
+    d, dmin = _f16(b, 0), _f16(b, 2)
+    sc, mn = _scale_min_k4(b[:, 4:16])
+    qs = b[:, 16:].astype(np.int32).reshape(-1, 4, 32)
+    q = np.stack([qs & 15, qs >> 4], axis=2).reshape(-1, 8, 32)   # group order: low nibbles, then high nibbles
+    dl = d[:, None] * sc.astype(F32)
+    ml = dmin[:, None] * mn.astype(F32)
+    return ((dl[:, :, None] * q.astype(F32)).astype(F32) - ml[:, :, None]).astype(F32).reshape(-1)
+
+
+def q5_k(raw):
+    b = _blocks(raw, 176)
+    d, dmin = _f16(b, 0), _f16(b, 2)
+    sc, mn = _scale_min_k4(b[:, 4:16])
+    qh = b[:, 16:48].astype(np.int32)
+    qs = b[:, 48:].astype(np.int32).reshape(-1, 4, 32)
+    g = np.arange(4).reshape(1, 4, 1)
+    lo = (qs & 15) + (((qh[:, None, :] >> (2 * g)) & 1) << 4)
+    hi = (qs >> 4) + (((qh[:, None, :] >> (2 * g + 1)) & 1) << 4)
+    q = np.stack([lo, hi], axis=2).reshape(-1, 8, 32)
+    dl = d[:, None] * sc.astype(F32)
+    ml = dmin[:, None] * mn.astype(F32)
+    return ((dl[:, :, None] * q.astype(F32)).astype(F32) - ml[:, :, None]).astype(F32).reshape(-1)
+
+
+def q6_k(raw):
+    b = _blocks(raw, 210)
+    d = _f16(b, 208)
+    ql = b[:, :128].astype(np.int32).reshape(-1, 2, 2, 32)         # [nb, half128, lo/hi 32 bytes, l]
+    qh = b[:, 128:192].astype(np.int32).reshape(-1, 2, 32)
+    sc = b[:, 192:208].view(np.int8).astype(np.int32).reshape(-1, 2, 8)
+    parts = []
+    for k in range(4):  # sub-rows l, l+32, l+64, l+96 of each 128-element half
+        nib = (ql[:, :, k & 1, :] & 15) if k < 2 else (ql[:, :, k & 1, :] >> 4)
+        q = (nib | (((qh >> (2 * k)) & 3) << 4)) - 32
+        s = np.repeat(sc[:, :, 2 * k:2 * k + 2], 16, axis=2)       # scale index is + 2k, is = l // 16
+        parts.append((d[:, None, None] * s.astype(F32)).astype(F32) * q.astype(F32))
+    return np.stack(parts, axis=2).astype(F32).reshape(-1)
+
+
+DECODERS = {2: q4_0, 6: q5_0, 8: q8_0, 10: q2_k, 11: q3_k, 12: q4_k, 13: q5_k, 14: q6_k, 20: iq4_nl, 23: iq4_xs}
+NAMES = {2: "Q4_0", 6: "Q5_0", 8: "Q8_0", 10: "Q2_K", 11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 20: "IQ4_NL", 23: "IQ4_XS"}
+
+
+def random_blocks(ty, n_blocks, seed, blk_bytes, scale_offsets):
+    """Uniform random bytes with finite, moderate f16 scales at the given offsets (no inf / nan scales)."""
+    rng = np.random.default_rng(seed)
+    b = rng.integers(0, 256, (n_blocks, blk_bytes), dtype=np.uint8)
+    for off in scale_offsets:
+        v = (rng.standard_normal(n_blocks) * 0.02).astype(np.float16)
+        b[:, off:off + 2] = v.view(np.uint8).reshape(n_blocks, 2)
+    return b.reshape(-1)
+
+
+SCALE_OFFSETS = {2: (0,), 6: (0,), 8: (0,), 10: (80, 82), 11: (108,), 12: (0, 2), 13: (0, 2), 14: (208,), 20: (0,), 23: (0,)}
