@@ -53,12 +53,24 @@ typedef enum lokal_status {
     LOKAL_ERR_NO_DEVICE = 7    /* no usable CUDA device */
 } lokal_status;
 
-/* GGUF tensor type ids (src/gguf/dequant.rs:21-41; BF16 = 30 per ggml.h). */
+/* GGUF tensor type ids (src/gguf/dequant.rs:21-41; BF16 = 30 per ggml.h).
+ * F32/F16/BF16 are the activation and weight-vector types of every op; all of
+ * them are table types of embed_gather / dequant_rows (block sizes
+ * src/gguf/dequant.rs:94-114). The codebook types (IQ1/IQ2/IQ3) and the
+ * activation-only Q8_1/Q8_K are not covered: LOKAL_ERR_UNSUPPORTED. */
 typedef enum lokal_type {
     LOKAL_F32 = 0,
     LOKAL_F16 = 1,
+    LOKAL_Q4_0 = 2,
+    LOKAL_Q5_0 = 6,
     LOKAL_Q8_0 = 8,
+    LOKAL_Q2_K = 10,
+    LOKAL_Q3_K = 11,
     LOKAL_Q4_K = 12,
+    LOKAL_Q5_K = 13,
+    LOKAL_Q6_K = 14,
+    LOKAL_IQ4_NL = 20,
+    LOKAL_IQ4_XS = 23,
     LOKAL_BF16 = 30
 } lokal_type;
 

@@ -13,6 +13,8 @@ from . import _build
 
 # lokal_type (GGUF tensor type ids)
 F32, F16, Q8_0, Q4_K, BF16 = 0, 1, 8, 12, 30
+Q4_0, Q5_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 2, 6, 10, 11, 13, 14, 20, 23
+QUANT_TYPES = (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS)
 
 # lokal_status
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_CUDA, ERR_ID_RANGE, ERR_TIMEOUT, ERR_NO_DEVICE = range(8)

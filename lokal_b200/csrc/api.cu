@@ -242,8 +242,8 @@ int lokal_cuda_graph_destroy(lokal_cuda_ctx* ctx, lokal_cuda_graph* g) {
 size_t lokal_cuda_blk_elems(int t) {
     switch (t) {
         case LOKAL_F32: case LOKAL_F16: case LOKAL_BF16: return 1;
-        case LOKAL_Q8_0: return 32;
-        case LOKAL_Q4_K: return 256;
+        case LOKAL_Q4_0: case LOKAL_Q5_0: case LOKAL_Q8_0: case LOKAL_IQ4_NL: return 32;
+        case LOKAL_Q2_K: case LOKAL_Q3_K: case LOKAL_Q4_K: case LOKAL_Q5_K: case LOKAL_Q6_K: case LOKAL_IQ4_XS: return 256;
         default: return 0;
     }
 }
@@ -252,8 +252,15 @@ size_t lokal_cuda_blk_bytes(int t) {
     switch (t) {
         case LOKAL_F32: return 4;
         case LOKAL_F16: case LOKAL_BF16: return 2;
+        case LOKAL_Q4_0: case LOKAL_IQ4_NL: return 18;
+        case LOKAL_Q5_0: return 22;
         case LOKAL_Q8_0: return 34;
+        case LOKAL_Q2_K: return 84;
+        case LOKAL_Q3_K: return 110;
         case LOKAL_Q4_K: return 144;
+        case LOKAL_Q5_K: return 176;
+        case LOKAL_Q6_K: return 210;
+        case LOKAL_IQ4_XS: return 136;
         default: return 0;
     }
 }

@@ -4,10 +4,13 @@
 // walks the ids, slices row id out of the table bytes (read_rows,
 // src/lowmem/mod.rs:654-668) and expands it with gguf::dequant_row_ref
 // (src/gguf/dequant.rs:191-239 F32/F16/Q8_0, :462-483 Q4_K, scale unpack
-// :141-150). Results here are bit-identical to that: int -> f32 and f16 -> f32
-// conversions are exact, and the Q4_K value d1*q - m1 is computed with
-// __fmul_rn / __fsub_rn so the two products and the subtraction are each
-// rounded once and never contracted into an FMA.
+// :141-150; :204-230 Q4_0/Q5_0, :396-425 IQ4_NL/IQ4_XS, :426-461 Q2_K/Q3_K,
+// :484-535 Q5_K/Q6_K). Results here are bit-identical to that: int -> f32 and
+// f16 -> f32 conversions are exact, and every product and difference of the
+// reference's expressions (d1*q - m1, (d*sc)*q ...) is computed with
+// __fmul_rn / __fsub_rn, so each is rounded once and never contracted into an
+// FMA. Q8_0 and Q4_K have vector decoders; the other block types decode one
+// element at a time from the staged row with the same arithmetic.
 //
 // Kernel shape (quantised tables): one warp per token row, persistent over a
 // grid-stride list of rows. Lane 0 stages the raw row into shared memory with
@@ -23,6 +26,8 @@
 // Every wait on an mbarrier is bounded: after the limit the warp records
 // kErrTimeout in the context's error word and leaves.
 #include "common.cuh"
+
+#include <type_traits>
 
 namespace lokal {
 namespace {
@@ -94,10 +99,146 @@ __device__ __forceinline__ void decode_q4_k(const unsigned char* row, unsigned e
     }
 }
 
+
+// ---- one element of any block type, bytes fetched through rd(offset) ----
+// The element-indexed form of the reference's sequential decoders; each arm
+// cites the loop it restates. All arithmetic on f32 is one rounded operation
+// per reference operation.
+struct SharedBytes {
+    const unsigned char* p;
+    __device__ __forceinline__ unsigned operator()(unsigned i) const { return p[i]; }
+};
+struct GlobalBytes {
+    const unsigned char* p;
+    __device__ __forceinline__ unsigned operator()(unsigned i) const { return __ldg(p + i); }
+};
+
+template <typename Rd>
+__device__ __forceinline__ float rd_f16(const Rd& rd, unsigned off) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(rd(off) | (rd(off + 1) << 8))));
+}
+
+// The 16-entry non-linear codebook of IQ4_NL / IQ4_XS (src/gguf/dequant.rs:161-166),
+// packed one signed byte per entry so the lookup is a shift, not a divergent memory access.
+__device__ __forceinline__ float iq4_value(unsigned q) {
+    // -127, -104, -83, -65, -49, -35, -22, -10 | 1, 13, 25, 38, 53, 69, 89, 113
+    const unsigned long long lo = 0xF6EADDCFBFAD9881ull, hi = 0x7159453526190D01ull;
+    const unsigned long long w = (q & 8u) ? hi : lo;
+    return static_cast<float>(static_cast<int>(static_cast<signed char>((w >> (8 * (q & 7u))) & 0xFF)));
+}
+
+// get_scale_min_k4 (src/gguf/dequant.rs:141-150): 6-bit scale and min of sub-block j from 12 packed bytes at sb.
+template <typename Rd>
+__device__ __forceinline__ void scale_min_k4(const Rd& rd, unsigned sb, unsigned j, unsigned& sc, unsigned& mn) {
+    if (j < 4) {
+        sc = rd(sb + j) & 63u;
+        mn = rd(sb + j + 4) & 63u;
+    } else {
+        sc = (rd(sb + j + 4) & 0x0Fu) | ((rd(sb + j - 4) >> 6) << 4);
+        mn = (rd(sb + j + 4) >> 4) | ((rd(sb + j) >> 6) << 4);
+    }
+}
+
+template <int QT, typename Rd>
+__device__ __forceinline__ float dequant_elem(const Rd& rd, unsigned col) {
+    if constexpr (QT == LOKAL_Q8_0) {  // src/gguf/dequant.rs:231-239
+        const unsigned b = (col >> 5) * 34;
+        const int q = static_cast<int>(static_cast<signed char>(rd(b + 2 + (col & 31))));
+        return __fmul_rn(static_cast<float>(q), rd_f16(rd, b));
+    } else if constexpr (QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL) {  // :204-214, :396-406
+        const unsigned b = (col >> 5) * 18, j = col & 31;
+        const unsigned byte = rd(b + 2 + (j & 15));
+        const unsigned q = (j & 16) ? (byte >> 4) : (byte & 15u);
+        const float d = rd_f16(rd, b);
+        if constexpr (QT == LOKAL_Q4_0) return __fmul_rn(static_cast<float>(static_cast<int>(q) - 8), d);
+        else return __fmul_rn(d, iq4_value(q));
+    } else if constexpr (QT == LOKAL_Q5_0) {  // :215-230: bit j (low half) or j+16 (high half) of qh is the 5th bit
+        const unsigned b = (col >> 5) * 22, j = col & 31;
+        const unsigned qh = rd(b + 2) | (rd(b + 3) << 8) | (rd(b + 4) << 16) | (rd(b + 5) << 24);
+        const unsigned byte = rd(b + 6 + (j & 15));
+        const unsigned nib = (j & 16) ? (byte >> 4) : (byte & 15u);
+        const int q = static_cast<int>(nib | (((qh >> j) & 1u) << 4)) - 16;
+        return __fmul_rn(static_cast<float>(q), rd_f16(rd, b));
+    } else if constexpr (QT == LOKAL_IQ4_XS) {  // :410-425: d, scales_h u16, scales_l[4], qs[128]
+        const unsigned b = (col >> 8) * 136, i = col & 255, ib = i >> 5, j = i & 31;
+        const unsigned sh = rd(b + 2) | (rd(b + 3) << 8);
+        const unsigned ls = ((rd(b + 4 + (ib >> 1)) >> (4 * (ib & 1))) & 15u) | (((sh >> (2 * ib)) & 3u) << 4);
+        const float dl = __fmul_rn(rd_f16(rd, b), static_cast<float>(static_cast<int>(ls) - 32));
+        const unsigned byte = rd(b + 8 + 16 * ib + (j & 15));
+        return __fmul_rn(dl, iq4_value((j & 16) ? (byte >> 4) : (byte & 15u)));
+    } else if constexpr (QT == LOKAL_Q2_K) {  // :426-440: scales[16], qs[64], d, dmin
+        const unsigned b = (col >> 8) * 84, i = col & 255;
+        const unsigned nh = i >> 7, j = (i >> 5) & 3, half = (i >> 4) & 1, l = i & 15;
+        const unsigned sc = rd(b + nh * 8 + j * 2 + half);
+        const unsigned q = (rd(b + 16 + nh * 32 + half * 16 + l) >> (2 * j)) & 3u;
+        const float dl = __fmul_rn(rd_f16(rd, b + 80), static_cast<float>(sc & 15u));
+        const float ml = __fmul_rn(rd_f16(rd, b + 82), static_cast<float>(sc >> 4));
+        return __fsub_rn(__fmul_rn(dl, static_cast<float>(q)), ml);
+    } else if constexpr (QT == LOKAL_Q3_K) {  // :445-461 and q3k_scales :171-189: hmask[32], qs[64], scales[12], d
+        const unsigned b = (col >> 8) * 110, i = col & 255;
+        const unsigned nh = i >> 7, j = (i >> 5) & 3, half = (i >> 4) & 1, l = i & 15;
+        // scale s = aux word a, byte k of the kmask shuffle: low nibble from byte (a&1)*4+k (high nibble of it
+        // for a >= 2), two more bits from byte 8+k at bit 2a; stored biased by 32
+        const unsigned s = nh * 8 + j * 2 + half, a = s >> 2, k = s & 3;
+        const unsigned pb = rd(b + 96 + (a & 1) * 4 + k);
+        const unsigned lo = (a < 2) ? (pb & 15u) : (pb >> 4);
+        const unsigned hi = (rd(b + 96 + 8 + k) >> (2 * a)) & 3u;
+        const float dl = __fmul_rn(rd_f16(rd, b + 108), static_cast<float>(static_cast<int>(lo | (hi << 4)) - 32));
+        const unsigned hbit = (rd(b + half * 16 + l) >> (nh * 4 + j)) & 1u;
+        const int q = static_cast<int>((rd(b + 32 + nh * 32 + half * 16 + l) >> (2 * j)) & 3u) - (hbit ? 0 : 4);
+        return __fmul_rn(dl, static_cast<float>(q));
+    } else if constexpr (QT == LOKAL_Q4_K) {  // :462-483
+        const unsigned b = (col >> 8) * 144, i = col & 255;
+        unsigned sc, mn;
+        scale_min_k4(rd, b + 4, i >> 5, sc, mn);
+        const float d1 = __fmul_rn(rd_f16(rd, b), static_cast<float>(sc));
+        const float m1 = __fmul_rn(rd_f16(rd, b + 2), static_cast<float>(mn));
+        const unsigned byte = rd(b + 16 + (i >> 6) * 32 + (i & 31));
+        const unsigned q = (i & 32) ? (byte >> 4) : (byte & 0xFu);
+        return __fsub_rn(__fmul_rn(d1, static_cast<float>(q)), m1);
+    } else if constexpr (QT == LOKAL_Q5_K) {  // :484-511: d, dmin, scales[12], qh[32], qs[128]
+        const unsigned b = (col >> 8) * 176, i = col & 255, sub = i >> 5, l = i & 31;
+        unsigned sc, mn;
+        scale_min_k4(rd, b + 4, sub, sc, mn);
+        const float d1 = __fmul_rn(rd_f16(rd, b), static_cast<float>(sc));
+        const float m1 = __fmul_rn(rd_f16(rd, b + 2), static_cast<float>(mn));
+        const unsigned byte = rd(b + 48 + (i >> 6) * 32 + l);
+        const unsigned nib = (i & 32) ? (byte >> 4) : (byte & 0xFu);
+        const unsigned q = nib + (((rd(b + 16 + l) >> sub) & 1u) << 4);
+        return __fsub_rn(__fmul_rn(d1, static_cast<float>(q)), m1);
+    } else {  // LOKAL_Q6_K, :512-535: ql[128], qh[64], int8 scales[16], d
+        const unsigned b = (col >> 8) * 210, i = col & 255;
+        const unsigned h = i >> 7, k = (i >> 5) & 3, l = i & 31;
+        const unsigned qlb = rd(b + h * 64 + (k & 1) * 32 + l);
+        const unsigned nib = (k & 2) ? (qlb >> 4) : (qlb & 15u);
+        const int q = static_cast<int>(nib | (((rd(b + 128 + h * 32 + l) >> (2 * k)) & 3u) << 4)) - 32;
+        const int sc = static_cast<int>(static_cast<signed char>(rd(b + 192 + h * 8 + 2 * k + (l >> 4))));
+        return __fmul_rn(__fmul_rn(rd_f16(rd, b + 208), static_cast<float>(sc)), static_cast<float>(q));
+    }
+}
+
 template <int QT, int EPL>
 __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned e, float (&y)[EPL]) {
-    if (QT == LOKAL_Q8_0) decode_q8_0<EPL>(row, e, y);
-    else decode_q4_k<EPL>(row, e, y);
+    if constexpr (QT == LOKAL_Q8_0) decode_q8_0<EPL>(row, e, y);
+    else if constexpr (QT == LOKAL_Q4_K) decode_q4_k<EPL>(row, e, y);
+    else {
+        const SharedBytes rd{row};
+#pragma unroll
+        for (int k = 0; k < EPL; k++) y[k] = dequant_elem<QT>(rd, e + k);
+    }
+}
+
+// Calls f(std::integral_constant<int, type>) for a quantised table type.
+template <typename F>
+void for_quant_type(int t, F&& f) {
+    switch (t) {
+#define LOKAL_QT_CASE(T) case T: f(std::integral_constant<int, T>{}); break;
+        LOKAL_QT_CASE(LOKAL_Q4_0) LOKAL_QT_CASE(LOKAL_Q5_0) LOKAL_QT_CASE(LOKAL_Q8_0) LOKAL_QT_CASE(LOKAL_Q2_K)
+        LOKAL_QT_CASE(LOKAL_Q3_K) LOKAL_QT_CASE(LOKAL_Q4_K) LOKAL_QT_CASE(LOKAL_Q5_K) LOKAL_QT_CASE(LOKAL_Q6_K)
+        LOKAL_QT_CASE(LOKAL_IQ4_NL) LOKAL_QT_CASE(LOKAL_IQ4_XS)
+#undef LOKAL_QT_CASE
+        default: break;
+    }
 }
 
 template <typename OutT>
@@ -207,36 +348,8 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
 // ---- plain kernel for quantised tables: any alignment, any row size ----
 // One warp per row, one element per lane step, byte loads straight from global
 // memory (the per-element index form of src/gpu/kernels.metal:77-81, 889-904).
-__device__ __forceinline__ float dequant_elem_global(int qt, const unsigned char* row, unsigned col) {
-    if (qt == LOKAL_Q8_0) {
-        const unsigned char* b = row + (col >> 5) * 34;
-        const unsigned short hb = static_cast<unsigned short>(__ldg(b) | (__ldg(b + 1) << 8));
-        const float d = __half2float(__ushort_as_half(hb));
-        const int q = static_cast<int>(static_cast<signed char>(__ldg(b + 2 + (col & 31))));
-        return __fmul_rn(static_cast<float>(q), d);
-    }
-    const unsigned char* b = row + (col >> 8) * 144;
-    const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(__ldg(b) | (__ldg(b + 1) << 8))));
-    const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(__ldg(b + 2) | (__ldg(b + 3) << 8))));
-    const unsigned char* sb = b + 4;
-    const unsigned ib = col & 255, j = ib >> 5;
-    unsigned sc, mn;
-    if (j < 4) {
-        sc = __ldg(sb + j) & 63u;
-        mn = __ldg(sb + j + 4) & 63u;
-    } else {
-        sc = (__ldg(sb + j + 4) & 0x0Fu) | ((static_cast<unsigned>(__ldg(sb + j - 4)) >> 6) << 4);
-        mn = (static_cast<unsigned>(__ldg(sb + j + 4)) >> 4) | ((static_cast<unsigned>(__ldg(sb + j)) >> 6) << 4);
-    }
-    const float d1 = __fmul_rn(d, static_cast<float>(sc));
-    const float m1 = __fmul_rn(dmin, static_cast<float>(mn));
-    const unsigned byte = __ldg(b + 16 + (ib >> 6) * 32 + (ib & 31));
-    const unsigned q = (ib & 32) ? (byte >> 4) : (byte & 0xFu);
-    return __fsub_rn(__fmul_rn(d1, static_cast<float>(q)), m1);
-}
-
-template <typename OutT>
-__global__ void __launch_bounds__(256) gather_quant_plain_kernel(const GatherArgs a, int qt) {
+template <int QT, typename OutT>
+__global__ void __launch_bounds__(256) gather_quant_plain_kernel(const GatherArgs a) {
     pdl_sync();
     const unsigned long long i = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (i >= a.n) return;
@@ -248,8 +361,8 @@ __global__ void __launch_bounds__(256) gather_quant_plain_kernel(const GatherArg
         for (unsigned e = lane; e < a.dim; e += 32) orow[e] = from_f32<OutT>(0.0f);
         return;
     }
-    const unsigned char* row = a.table + id * a.row_bytes;
-    for (unsigned e = lane; e < a.dim; e += 32) orow[e] = from_f32<OutT>(dequant_elem_global(qt, row, e));
+    const GlobalBytes rd{a.table + id * a.row_bytes};
+    for (unsigned e = lane; e < a.dim; e += 32) orow[e] = from_f32<OutT>(dequant_elem<QT>(rd, e));
 }
 
 // ---- float tables (F32 / F16 / BF16): copy or widen/narrow a row ----
@@ -318,11 +431,14 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
     const size_t smem = ((warps * 2 * 8 + 127u) & ~127u) + static_cast<size_t>(warps) * 2 * a.stage_bytes;
     const bool staged = aligned && smem <= 200u * 1024u && (a.row_bytes % 2 == 0);
     if (!staged) {
-        launch_k(gather_quant_plain_kernel<OutT>, static_cast<unsigned>(row_warps_blocks), 256, 0, s, a, ggml_type);
+        for_quant_type(ggml_type, [&](auto qt) {
+            launch_k(gather_quant_plain_kernel<decltype(qt)::value, OutT>, static_cast<unsigned>(row_warps_blocks), 256, 0, s, a);
+        });
         LOKAL_CHECK_LAUNCH(ctx, "gather_quant_plain_kernel");
         return LOKAL_OK;
     }
-    auto kern = ggml_type == LOKAL_Q8_0 ? gather_quant_staged_kernel<LOKAL_Q8_0, OutT> : gather_quant_staged_kernel<LOKAL_Q4_K, OutT>;
+    void (*kern)(const GatherArgs) = nullptr;
+    for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT>; });
     if (smem > 48u * 1024u) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "embed_gather: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -344,7 +460,7 @@ int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int gg
                   const uint32_t* ids, size_t n, void* out, int out_dtype) {
     if (!table || !out) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: table and out must be non-null");
     const size_t be = lokal_cuda_blk_elems(ggml_type);
-    if (be == 0) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: ggml type %d is not F32/F16/BF16/Q8_0/Q4_K", ggml_type);
+    if (be == 0) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: ggml type %d is not a float type or one of Q4_0 Q5_0 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS", ggml_type);
     if (!is_act_type(out_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: output type %d is not F32/F16/BF16", out_dtype);
     if (dim == 0 || dim > 0x7fffffffu) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: dim %zu out of range", dim);
     if (dim % be != 0)

@@ -51,6 +51,9 @@ def test_enums_match_header_and_gguf_ids():
         if name.startswith("LOKAL_ERR") or name == "LOKAL_OK":
             assert getattr(capi, name[len("LOKAL_"):]) == int(val)
     assert (capi.F32, capi.F16, capi.Q8_0, capi.Q4_K, capi.BF16) == (0, 1, 8, 12, 30)  # src/gguf/dequant.rs:21-41
+    for name, val in re.findall(r"LOKAL_(I?Q\d\w+) = (\d+)", HEADER):
+        assert getattr(capi, name) == int(val) and int(val) in capi.QUANT_TYPES
+    assert len(capi.QUANT_TYPES) == 10
 
 
 def test_block_geometry_matches_reference_table():
@@ -59,7 +62,11 @@ def test_block_geometry_matches_reference_table():
     assert lokal_b200.blk_elems(capi.Q8_0) == 32 and lokal_b200.blk_elems(capi.Q4_K) == 256
     assert lokal_b200.row_bytes(capi.Q4_K, 512) == 288 and lokal_b200.row_bytes(capi.Q8_0, 896) == 952
     assert lokal_b200.row_bytes(capi.F16, 10) == 20 and lokal_b200.row_bytes(capi.BF16, 10) == 20
-    assert lokal_b200.blk_elems(14) == 0 and lokal_b200.row_bytes(14, 256) == 0
+    want = {2: (32, 18), 6: (32, 22), 8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176),
+            14: (256, 210), 20: (32, 18), 23: (256, 136)}
+    for ty, geom in want.items():
+        assert (lokal_b200.blk_elems(ty), lokal_b200.blk_bytes(ty)) == geom
+    assert lokal_b200.blk_elems(16) == 0 and lokal_b200.row_bytes(16, 256) == 0  # IQ2_XXS: a codebook type, not covered
 
 
 def test_shard_rows_partitions_every_row_once():
