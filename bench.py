@@ -508,12 +508,18 @@ def gather_workload(args, rank, world, local_rank):
     peak, peak_kind = measured_peak()
     variants = [("q8_0_f32", L.Q8_0, synth.C4_DIM_Q8, L.F32), ("q8_0_f16", L.Q8_0, synth.C4_DIM_Q8, L.F16),
                 ("q4_k_f32", L.Q4_K, synth.C4_DIM_Q4K, L.F32), ("q4_k_f16", L.Q4_K, synth.C4_DIM_Q4K, L.F16)]
+    # the other block types of the gather, f32 out: 32-element blocks at the Q8_0 width, 256-element ones at the Q4_K width
+    for ty in L.QUANT_TYPES:
+        if ty not in (L.Q8_0, L.Q4_K):
+            dim = synth.C4_DIM_Q8 if synth.QUANT_GEOMETRY[ty][0] == 32 else synth.C4_DIM_Q4K
+            variants.append((synth.QUANT_NAMES[ty] + "_f32", ty, dim, L.F32))
     tables, kern = {}, {}
     O.build()
     threads = O.hardware_threads()
     for name, ty, dim, odt in variants:
         if (ty, dim) not in tables:
-            host = (synth.q8_0_table if ty == L.Q8_0 else synth.q4_k_table)(vocab, dim, synth.C4_SEED + ty)
+            gen = {L.Q8_0: synth.q8_0_table, L.Q4_K: synth.q4_k_table}.get(ty)
+            host = gen(vocab, dim, synth.C4_SEED + ty) if gen else synth.quant_table(ty, vocab, dim, synth.C4_SEED + ty)
             tables[(ty, dim)] = (host, torch.from_numpy(host).to(dev))
         host, table = tables[(ty, dim)]
         es = 4 if odt == L.F32 else 2

@@ -45,60 +45,32 @@ struct GatherArgs {
     unsigned* err_word;
 };
 
-// ---- block decoders: EPL consecutive elements starting at element e (e % EPL == 0) ----
+// ---- block decoders: EPL consecutive elements starting at element e (e % EPL == 0), as EPL/2 pairs ----
 
-// Q8_0 (src/gguf/dequant.rs:231-239): 34-byte block = f16 d, then 32 int8; y = q * d.
-template <int EPL>
-__device__ __forceinline__ void decode_q8_0(const unsigned char* row, unsigned e, float (&y)[EPL]) {
-    const unsigned char* b = row + (e >> 5) * 34;
-    const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(b)));
-    const unsigned short* q = reinterpret_cast<const unsigned short*>(b + 2 + (e & 31));
-#pragma unroll
-    for (int j = 0; j < EPL / 2; j++) {
-        const unsigned short two = q[j];
-        const int q0 = static_cast<int>(static_cast<signed char>(two & 0xFF));
-        const int q1 = static_cast<int>(static_cast<signed char>(two >> 8));
-        y[2 * j] = __fmul_rn(static_cast<float>(q0), d);
-        y[2 * j + 1] = __fmul_rn(static_cast<float>(q1), d);
-    }
+// Exact float of byte k of `word` (0..255) without the conversion pipe: the byte becomes the low mantissa bits of
+// 2^23, and subtracting 2^23 (an exact operation) leaves the integer. The caller folds a further integer bias
+// (128 for int8 stored as q ^ 0x80) into the subtracted constant; 2^23 + 128 is exact too.
+template <int K>
+__device__ __forceinline__ float byte_plus_2p23(unsigned word) {
+    return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540u | K));
 }
 
-// Q4_K (src/gguf/dequant.rs:462-483): 144-byte super-block = f16 d, f16 dmin,
-// 12 bytes of packed 6-bit scales/mins, 128 bytes of nibbles. For group j of
-// 32 elements: y = (d * sc_j) * q - (dmin * m_j), products and difference each
-// rounded to f32.
-template <int EPL>
-__device__ __forceinline__ void decode_q4_k(const unsigned char* row, unsigned e, float (&y)[EPL]) {
-    const unsigned char* b = row + (e >> 8) * 144;
-    const unsigned ib = e & 255;
-    const unsigned dd = *reinterpret_cast<const unsigned*>(b);
-    const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(dd & 0xFFFF)));
-    const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(dd >> 16)));
-    const unsigned char* sb = b + 4;
-    const unsigned j = ib >> 5;
-    unsigned sc, mn;
-    if (j < 4) {
-        sc = sb[j] & 63u;
-        mn = sb[j + 4] & 63u;
-    } else {
-        sc = (sb[j + 4] & 0x0Fu) | ((static_cast<unsigned>(sb[j - 4]) >> 6) << 4);
-        mn = (static_cast<unsigned>(sb[j + 4]) >> 4) | ((static_cast<unsigned>(sb[j]) >> 6) << 4);
-    }
-    const float d1 = __fmul_rn(d, static_cast<float>(sc));
-    const float m1 = __fmul_rn(dmin, static_cast<float>(mn));
-    const unsigned char* qs = b + 16 + (ib >> 6) * 32 + (ib & 31);
-    const unsigned shift = (ib & 32) ? 4u : 0u;
-#pragma unroll
-    for (int w = 0; w < EPL / 4; w++) {
-        const unsigned four = reinterpret_cast<const unsigned*>(qs)[w];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const unsigned q = ((four >> (8 * k)) >> shift) & 0xFu;
-            y[4 * w + k] = __fsub_rn(__fmul_rn(d1, static_cast<float>(q)), m1);
-        }
-    }
+// Four bytes of `w`, each minus `bias`, as two pairs of exact floats. nb = -(2^23 + bias) in both halves.
+__device__ __forceinline__ void bytes_to_pairs(unsigned w, float2 nb, float2& a, float2& b) {
+    a = add2(make_float2(byte_plus_2p23<0>(w), byte_plus_2p23<1>(w)), nb);
+    b = add2(make_float2(byte_plus_2p23<2>(w), byte_plus_2p23<3>(w)), nb);
 }
+__device__ __forceinline__ float2 both(float v) { return make_float2(v, v); }
 
+// 32 bits from shared memory at a 2-byte-aligned address (rows of 18-, 22-, 34-, 110- and 210-byte blocks).
+__device__ __forceinline__ unsigned lds_u32_a2(const unsigned char* p) {
+    const unsigned short* h = reinterpret_cast<const unsigned short*>(p);
+    return static_cast<unsigned>(h[0]) | (static_cast<unsigned>(h[1]) << 16);
+}
+__device__ __forceinline__ unsigned lds_u32(const unsigned char* p) { return *reinterpret_cast<const unsigned*>(p); }
+__device__ __forceinline__ float lds_f16(const unsigned char* p) {
+    return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(p)));
+}
 
 // ---- one element of any block type, bytes fetched through rd(offset) ----
 // The element-indexed form of the reference's sequential decoders; each arm
@@ -217,14 +189,126 @@ __device__ __forceinline__ float dequant_elem(const Rd& rd, unsigned col) {
     }
 }
 
+// ---- vector decoders for the staged kernel ----
+// EPL (4 or 8) consecutive elements starting at e, e % EPL == 0, of the row staged at `row` in shared memory.
+// Such a run never crosses a 16-element sub-group, so it has one scale (and one min), its quants sit in EPL
+// consecutive bytes of each plane, and the same shift and mask extract all of them: four elements per 32-bit
+// word. The values and the order of the rounded f32 operations are those of dequant_elem above, arm by arm;
+// integers become floats through byte_plus_2p23, products and sums go through the packed f32x2 instructions.
+// `lut` is the IQ4 codebook as 16 floats in shared memory (one bank each, so a warp's lookups never conflict).
 template <int QT, int EPL>
-__device__ __forceinline__ void decode_block(const unsigned char* row, unsigned e, float (&y)[EPL]) {
-    if constexpr (QT == LOKAL_Q8_0) decode_q8_0<EPL>(row, e, y);
-    else if constexpr (QT == LOKAL_Q4_K) decode_q4_k<EPL>(row, e, y);
-    else {
-        const SharedBytes rd{row};
+__device__ __forceinline__ void decode_block(const unsigned char* row, unsigned e, const float* lut, float2 (&y)[EPL / 2]) {
+    constexpr int W = EPL / 4;
+    constexpr float k2p23 = 8388608.0f;
+    if constexpr (QT == LOKAL_Q8_0) {
+        const unsigned char* b = row + (e >> 5) * 34;
+        const float2 dd = both(lds_f16(b)), nb = both(-(k2p23 + 128.0f));
 #pragma unroll
-        for (int k = 0; k < EPL; k++) y[k] = dequant_elem<QT>(rd, e + k);
+        for (int w = 0; w < W; w++) {
+            float2 f0, f1;
+            bytes_to_pairs(lds_u32_a2(b + 2 + (e & 31) + 4 * w) ^ 0x80808080u, nb, f0, f1);  // int8 -> biased uint8
+            y[2 * w] = mul2(f0, dd);
+            y[2 * w + 1] = mul2(f1, dd);
+        }
+    } else if constexpr (QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL || QT == LOKAL_Q5_0) {
+        constexpr unsigned BB = QT == LOKAL_Q5_0 ? 22 : 18, QS = QT == LOKAL_Q5_0 ? 6 : 2;
+        const unsigned char* b = row + (e >> 5) * BB;
+        const unsigned j = e & 31, shift = (j & 16) ? 4u : 0u;
+        const float2 dd = both(lds_f16(b));
+        unsigned qh = 0;
+        if constexpr (QT == LOKAL_Q5_0) qh = lds_u32_a2(b + 2) >> j;  // bit k: fifth bit of element e + k
+#pragma unroll
+        for (int w = 0; w < W; w++) {
+            unsigned four = (lds_u32_a2(b + QS + (j & 15) + 4 * w) >> shift) & 0x0F0F0F0Fu;
+            if constexpr (QT == LOKAL_IQ4_NL) {
+                y[2 * w] = mul2(dd, make_float2(lut[four & 15u], lut[(four >> 8) & 15u]));
+                y[2 * w + 1] = mul2(dd, make_float2(lut[(four >> 16) & 15u], lut[four >> 24]));
+            } else {
+                if constexpr (QT == LOKAL_Q5_0) four |= ((((qh >> (4 * w)) & 15u) * 0x00204081u) & 0x01010101u) << 4;
+                float2 f0, f1;
+                bytes_to_pairs(four, both(-(k2p23 + (QT == LOKAL_Q5_0 ? 16.0f : 8.0f))), f0, f1);
+                y[2 * w] = mul2(f0, dd);
+                y[2 * w + 1] = mul2(f1, dd);
+            }
+        }
+    } else if constexpr (QT == LOKAL_IQ4_XS) {
+        const unsigned char* b = row + (e >> 8) * 136;
+        const unsigned i = e & 255, ib = i >> 5, j = i & 31, shift = (j & 16) ? 4u : 0u;
+        const unsigned hdr = lds_u32(b);  // f16 d, u16 scales_h
+        const unsigned ls = ((static_cast<unsigned>(b[4 + (ib >> 1)]) >> (4 * (ib & 1))) & 15u) | ((((hdr >> 16) >> (2 * ib)) & 3u) << 4);
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(hdr & 0xFFFF)));
+        const float2 dl = both(__fmul_rn(d, static_cast<float>(static_cast<int>(ls) - 32)));
+#pragma unroll
+        for (int w = 0; w < W; w++) {
+            const unsigned four = (lds_u32(b + 8 + 16 * ib + (j & 15) + 4 * w) >> shift) & 0x0F0F0F0Fu;
+            y[2 * w] = mul2(dl, make_float2(lut[four & 15u], lut[(four >> 8) & 15u]));
+            y[2 * w + 1] = mul2(dl, make_float2(lut[(four >> 16) & 15u], lut[four >> 24]));
+        }
+    } else if constexpr (QT == LOKAL_Q2_K) {
+        const unsigned char* b = row + (e >> 8) * 84;
+        const unsigned i = e & 255, nh = i >> 7, j = (i >> 5) & 3, half = (i >> 4) & 1, l = i & 15;
+        const unsigned sc = b[nh * 8 + j * 2 + half];
+        const unsigned dm = lds_u32(b + 80);  // f16 d, f16 dmin
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(dm & 0xFFFF)));
+        const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(dm >> 16)));
+        const float2 dl = both(__fmul_rn(d, static_cast<float>(sc & 15u))), nml = both(-__fmul_rn(dmin, static_cast<float>(sc >> 4)));
+#pragma unroll
+        for (int w = 0; w < W; w++) {
+            float2 f0, f1;
+            bytes_to_pairs((lds_u32(b + 16 + nh * 32 + half * 16 + l + 4 * w) >> (2 * j)) & 0x03030303u, both(-k2p23), f0, f1);
+            y[2 * w] = add2(mul2(dl, f0), nml);
+            y[2 * w + 1] = add2(mul2(dl, f1), nml);
+        }
+    } else if constexpr (QT == LOKAL_Q3_K) {
+        const unsigned char* b = row + (e >> 8) * 110;
+        const unsigned i = e & 255, nh = i >> 7, j = (i >> 5) & 3, half = (i >> 4) & 1, l = i & 15;
+        const unsigned s = nh * 8 + j * 2 + half, a = s >> 2, k = s & 3;
+        const unsigned pb = b[96 + (a & 1) * 4 + k];
+        const unsigned lo = (a < 2) ? (pb & 15u) : (pb >> 4);
+        const unsigned hi = (static_cast<unsigned>(b[104 + k]) >> (2 * a)) & 3u;
+        const float2 dl = both(__fmul_rn(lds_f16(b + 108), static_cast<float>(static_cast<int>(lo | (hi << 4)) - 32)));
+#pragma unroll
+        for (int w = 0; w < W; w++) {
+            const unsigned q = (lds_u32_a2(b + 32 + nh * 32 + half * 16 + l + 4 * w) >> (2 * j)) & 0x03030303u;
+            const unsigned hb = (lds_u32_a2(b + half * 16 + l + 4 * w) >> (nh * 4 + j)) & 0x01010101u;
+            float2 f0, f1;
+            bytes_to_pairs(q | (hb << 2), both(-(k2p23 + 4.0f)), f0, f1);  // q - (hbit ? 0 : 4) = (q + 4 hbit) - 4
+            y[2 * w] = mul2(dl, f0);
+            y[2 * w + 1] = mul2(dl, f1);
+        }
+    } else if constexpr (QT == LOKAL_Q4_K || QT == LOKAL_Q5_K) {
+        constexpr unsigned BB = QT == LOKAL_Q4_K ? 144 : 176, QS = QT == LOKAL_Q4_K ? 16 : 48;
+        const unsigned char* b = row + (e >> 8) * BB;
+        const unsigned i = e & 255, sub = i >> 5, l = i & 31, shift = (i & 32) ? 4u : 0u;
+        const unsigned dm = lds_u32(b);  // f16 d, f16 dmin
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(dm & 0xFFFF)));
+        const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(dm >> 16)));
+        unsigned sc, mn;
+        scale_min_k4(SharedBytes{b}, 4, sub, sc, mn);
+        const float2 d1 = both(__fmul_rn(d, static_cast<float>(sc))), nm1 = both(-__fmul_rn(dmin, static_cast<float>(mn)));
+#pragma unroll
+        for (int w = 0; w < W; w++) {
+            unsigned four = (lds_u32(b + QS + (i >> 6) * 32 + l + 4 * w) >> shift) & 0x0F0F0F0Fu;
+            if constexpr (QT == LOKAL_Q5_K) four |= ((lds_u32(b + 16 + l + 4 * w) >> sub) & 0x01010101u) << 4;
+            float2 f0, f1;
+            bytes_to_pairs(four, both(-k2p23), f0, f1);
+            y[2 * w] = add2(mul2(d1, f0), nm1);
+            y[2 * w + 1] = add2(mul2(d1, f1), nm1);
+        }
+    } else {  // LOKAL_Q6_K
+        const unsigned char* b = row + (e >> 8) * 210;
+        const unsigned i = e & 255, h = i >> 7, k = (i >> 5) & 3, l = i & 31, shift = (k & 2) ? 4u : 0u;
+        const int sc = static_cast<int>(static_cast<signed char>(b[192 + h * 8 + 2 * k + (l >> 4)]));
+        const float2 dsc = both(__fmul_rn(lds_f16(b + 208), static_cast<float>(sc)));
+#pragma unroll
+        for (int w = 0; w < W; w++) {
+            const unsigned nib = (lds_u32_a2(b + h * 64 + (k & 1) * 32 + l + 4 * w) >> shift) & 0x0F0F0F0Fu;
+            const unsigned hb = (lds_u32_a2(b + 128 + h * 32 + l + 4 * w) >> (2 * k)) & 0x03030303u;
+            float2 f0, f1;
+            bytes_to_pairs(nib | (hb << 4), both(-(k2p23 + 32.0f)), f0, f1);
+            y[2 * w] = mul2(dsc, f0);
+            y[2 * w + 1] = mul2(dsc, f1);
+        }
     }
 }
 
@@ -242,8 +326,8 @@ void for_quant_type(int t, F&& f) {
 }
 
 template <typename OutT>
-__device__ __forceinline__ void store_out16(OutT* dst, const float (&y)[VecOf<OutT>::N]) {
-    st_stream(dst, pack16<OutT>(y));
+__device__ __forceinline__ void store_out16(OutT* dst, const float2 (&y)[VecOf<OutT>::N / 2]) {
+    st_stream(dst, pack16p<OutT>(y));
 }
 
 // ---- staged (bulk-copy) kernel for quantised tables ----
@@ -264,6 +348,11 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
         mbar_init_fence();
     }
     __syncwarp();
+    __shared__ float lut[16];  // the IQ4 codebook as floats; unused by the other block types
+    if constexpr (QT == LOKAL_IQ4_NL || QT == LOKAL_IQ4_XS) {
+        if (threadIdx.x < 16) lut[threadIdx.x] = iq4_value(threadIdx.x);
+        __syncthreads();
+    }
 
     const unsigned long long total_warps = static_cast<unsigned long long>(gridDim.x) * warps_per_cta;
     const unsigned long long first = static_cast<unsigned long long>(blockIdx.x) * warps_per_cta + warp_in_cta;
@@ -280,8 +369,9 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
     auto mode_of = [&](unsigned s) { return (state >> (2 * s)) & 3u; };
     auto stage_ptr = [&](unsigned s) { return stage0 + s * a.stage_bytes; };
 
-    auto issue = [&](unsigned long long i, unsigned s) {
-        const unsigned long long id = a.ids ? static_cast<unsigned long long>(__ldg(a.ids + i)) : i;
+    // The id of a row is fetched one iteration before the row's copy is issued, so the copy never waits for it.
+    auto id_of = [&](unsigned long long i) { return a.ids ? static_cast<unsigned long long>(__ldg(a.ids + i)) : i; };
+    auto issue = [&](unsigned long long id, unsigned s) {
         if (id >= a.vocab) {
             set_stage(s, 0, 0);
             if (lane == 0) atomicOr(a.err_word, kErrIdRange);
@@ -306,13 +396,21 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
         }
     };
 
-    if (first < a.n) issue(first, 0);
+    unsigned long long id_next = 0;
+    if (first < a.n) {
+        issue(id_of(first), 0);
+        if (first + total_warps < a.n) id_next = id_of(first + total_warps);
+    }
     unsigned it = 0;
     for (unsigned long long i = first; i < a.n; i += total_warps, it++) {
         const unsigned s = it & 1u;
         const unsigned long long nxt = i + total_warps;
-        if (nxt < a.n) issue(nxt, s ^ 1u);
-        else set_stage(s ^ 1u, 0, 0);
+        if (nxt < a.n) {
+            issue(id_next, s ^ 1u);
+            if (nxt + total_warps < a.n) id_next = id_of(nxt + total_warps);
+        } else {
+            set_stage(s ^ 1u, 0, 0);
+        }
         OutT* orow = reinterpret_cast<OutT*>(a.out) + i * a.dim;
         const unsigned mode = mode_of(s);
         if (mode == 1) {
@@ -329,15 +427,15 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
             __syncwarp();
         }
         if (mode == 0) {
-            float z[EPL];
+            float2 z[EPL / 2];
 #pragma unroll
-            for (int k = 0; k < EPL; k++) z[k] = 0.0f;
+            for (int k = 0; k < EPL / 2; k++) z[k] = make_float2(0.0f, 0.0f);
             for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) store_out16<OutT>(orow + e, z);
         } else {
             const unsigned char* row = stage_ptr(s) + ((state >> (8 + 4 * s)) & 15u);
             for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
-                float y[EPL];
-                decode_block<QT, EPL>(row, e, y);
+                float2 y[EPL / 2];
+                decode_block<QT, EPL>(row, e, lut, y);
                 store_out16<OutT>(orow + e, y);
             }
         }

@@ -136,6 +136,24 @@ def q4_k_table(vocab: int, dim: int, seed: int) -> np.ndarray:
     return blocks.reshape(-1)
 
 
+# (block elements, block bytes, offsets of the f16 scale fields) per GGUF type id
+QUANT_GEOMETRY = {2: (32, 18, (0,)), 6: (32, 22, (0,)), 8: (32, 34, (0,)), 10: (256, 84, (80, 82)), 11: (256, 110, (108,)),
+                  12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 20: (32, 18, (0,)), 23: (256, 136, (0,))}
+QUANT_NAMES = {2: "q4_0", 6: "q5_0", 8: "q8_0", 10: "q2_k", 11: "q3_k", 12: "q4_k", 13: "q5_k", 14: "q6_k", 20: "iq4_nl", 23: "iq4_xs"}
+
+
+def quant_table(ty: int, vocab: int, dim: int, seed: int) -> np.ndarray:
+    """Bytes of a vocab x dim table of any covered block type: uniform random payload, f16 scales |N(0, 0.01)|."""
+    be, bb, offs = QUANT_GEOMETRY[ty]
+    assert dim % be == 0
+    rng = np.random.default_rng(seed)
+    nb = vocab * dim // be
+    blocks = rng.integers(0, 256, (nb, bb), dtype=np.uint8)
+    for off in offs:
+        blocks[:, off:off + 2] = _abs_normal_f16_bytes(rng, nb, 0.01)
+    return blocks.reshape(-1)
+
+
 def f32_table(vocab: int, dim: int, seed: int, std: float = 0.02) -> np.ndarray:
     rng = np.random.default_rng(seed)
     return rng.standard_normal((vocab, dim), dtype=np.float32) * np.float32(std)
