@@ -587,13 +587,100 @@ def gather_workload(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def row_ops_workload(args, rank, world, local_rank):
+    """The ops either side of the layer path, each timed alone as a graph of launches over rotating buffers:
+    K/V staging after RoPE and the gated-deltanet per-row siblings, at 8192 token rows of the qwen35-27B geometry
+    (d_state 128, 48 V heads, 16 K heads, 24 attention heads of 256)."""
+    import torch
+
+    import lokal_b200 as L
+    from oracle import lokal_oracle as O
+
+    if rank != 0:
+        return
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = L.Context(local_rank)
+    stream = ctx.stream_create()
+    tstream = torch.cuda.ExternalStream(stream, device=dev)
+    peak, peak_kind = measured_peak()
+    T, S, HV, HK, HA, HD = args.rows or 8192, 128, 48, 16, 24, 256
+    nbuf, reps = 6, 12
+    rnd = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.float32)
+    kern = {}
+
+    def timed(name, alg_bytes, launch):
+        ctx.graph_begin(stream)
+        for r in range(reps):
+            launch(r % nbuf)
+        g = ctx.graph_end(stream)
+        times = []
+        for rep in range(max(args.warmup, 3) + max(3, min(args.steps, 10))):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(tstream)
+            ctx.graph_launch(g, stream)
+            a1.record(tstream)
+            ctx.stream_sync(stream)
+            if rep >= max(args.warmup, 3):
+                times.append(a0.elapsed_time(a1) / reps)
+        ctx.graph_destroy(g)
+        ms = float(np.mean(times))
+        kern[name] = {"us_per_launch": 1e3 * ms, "bytes_per_launch": int(alg_bytes), "gbs": alg_bytes / (ms * 1e-3) / 1e9,
+                      "frac": alg_bytes / (ms * 1e-3) / 1e9 / peak, "launches_timed": len(times) * reps}
+
+    # l2norm over the q and k heads of every token: read + write
+    x = rnd(nbuf, T, 2 * HK * S)
+    timed("l2norm_rows_f32", 2 * T * 2 * HK * S * 4, lambda b: ctx.l2norm_rows(x[b], dim=S, eps=1e-6, rows_per_token=T * 2 * HK, stream=stream))
+    # one row against the oracle, every run
+    probe = rnd(4, S)
+    want = O.l2norm_rows(probe.cpu().numpy(), S, 1e-6)
+    ctx.l2norm_rows(probe, dim=S, eps=1e-6, rows_per_token=4, stream=stream)
+    ctx.stream_sync(stream)
+    kern["l2norm_rows_f32"]["max_rel_err_vs_oracle"] = float(np.max(np.abs(probe.cpu().numpy() - want) / np.maximum(np.abs(want), 1e-30)))
+    del x
+    # gated output norm: o and z read, y written
+    o, z, w = rnd(nbuf, T * HV, S), rnd(nbuf, T * HV, S), rnd(S)
+    timed("gated_output_norm_f32", 3 * T * HV * S * 4, lambda b: ctx.gated_output_norm(o[b], w, z[b], rows=T * HV, dim=S, eps=1e-6, stream=stream))
+    del o, z
+    # attention out-gate and the q/gate split it depends on
+    a, gt = rnd(nbuf, T, HA * HD), rnd(nbuf, T, HA * HD)
+    timed("attn_out_gate_f32", 3 * T * HA * HD * 4, lambda b: ctx.attn_out_gate(a[b], gt[b], n=T * HA * HD, stream=stream))
+    src = rnd(2, T, HA * 2 * HD)
+    timed("split_q_gate_f32", 2 * T * HA * 2 * HD * 4,
+          lambda b: ctx.split_q_gate(src[b % 2], a[b], gt[b], rows=T, n_heads=HA, head_dim=HD, stream=stream))
+    del a, gt, src
+    # K/V staging: f32 rows of 8 KV heads x 128 narrowed to f16 and scattered into a windowed cache (sink 4, ring 8704)
+    kvd = 1024
+    lay = L.window_cfg(8192, 4)
+    cap = lay.sink_pad + lay.ring
+    fresh = rnd(nbuf, T, kvd)
+    cache = torch.zeros(nbuf, cap, kvd, device=dev, dtype=torch.float16)
+    idx = torch.empty(T, device=dev, dtype=torch.int32)
+    timed("kv_rows_windowed", T * 4, lambda b: ctx.kv_rows(idx, layout=lay, rows=T, pos0=20000, slot0=0, stream=stream))
+    timed("kv_stage_f32_to_f16", T * (kvd * 6 + 4), lambda b: ctx.kv_stage(fresh[b], cache[b], src_dtype=L.F32, dst_dtype=L.F16, rows=T, width=kvd,
+                                                                            dst_rows=idx, stream=stream))
+    first = kern["gated_output_norm_f32"]
+    line = {
+        "metric": "gated output norm rows/s", "value": T * HV / (first["us_per_launch"] * 1e-6), "unit": "rows/s", "n_gpus": 1,
+        "steps": first["launches_timed"], "warmup": max(args.warmup, 3), "ms_per_step": first["us_per_launch"] * 1e-3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "row-ops-next-to-the-layer-path", "token_rows": T, "d_state": S, "v_heads": HV, "k_heads": HK,
+                   "attn_heads": HA, "head_dim": HD, "l2": f"each op rotates over {nbuf} buffer sets far larger than L2"},
+        "gpu_launches": sum(k["launches_timed"] for k in kern.values()),
+        "roofline": {"bound": "hbm", "kernel": "deltanet_rows_kernel<f32,1,gated>", "achieved": first["gbs"], "peak": peak,
+                     "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": first["frac"], "traffic": None, "kernels": kern},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(synth.CONFIGS) + ["c4"], default="c5")
+    ap.add_argument("--workload", choices=sorted(synth.CONFIGS) + ["c4", "rows"], default="c5")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures under a profiler)")
@@ -608,6 +695,10 @@ def main():
         if args.impl == "reference":
             sys.exit("--impl reference is defined for the layer workloads; the c4 line carries its own cpu_baseline")
         return gather_workload(args, rank, world, local_rank)
+    if args.workload == "rows":
+        if args.impl == "reference":
+            sys.exit("--impl reference is defined for the layer workloads")
+        return row_ops_workload(args, rank, world, local_rank)
     cfg = synth.CONFIGS[args.workload]
     if args.layers or args.rows:  # reduced sizes for profiler captures; the default is the full workload
         import dataclasses

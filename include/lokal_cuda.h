@@ -286,6 +286,34 @@ LOKAL_API int lokal_cuda_kv_stage(lokal_cuda_ctx* ctx, lokal_cuda_stream s, cons
                                   size_t src_row_stride, void* dst, int dst_dtype, size_t dst_row_stride,
                                   const uint32_t* dst_rows, size_t rows, size_t width);
 
+/* ---- Per-row siblings in the gated-deltanet (qwen35) blocks ----------------------
+ * The same shape of work as the ops above (one pass over token rows), used by the
+ * reference's qwen35 layers. Sums of squares are taken in f64, as the reference's CPU
+ * code does (src/deltanet_ref.rs:61-78); its Metal kernels sum in f32 only for want of
+ * f64. Rows are F32 / F16 / BF16 with f32 arithmetic and one rounding on store; y may
+ * be x (in place, as the reference works). */
+
+/* l2_norm (src/deltanet_ref.rs:61-67; l2norm_rows, src/gpu/kernels.metal:3697-3735):
+ *   y = x * (1 / max(sqrt(sum x^2), eps))       -- a zero row stays zero, never NaN.
+ * Row r of token t starts at element t*tok_stride + r*dim, the batched kernel's
+ * addressing; with n_tokens == 1 tok_stride is ignored. */
+LOKAL_API int lokal_cuda_l2norm_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* x, void* y, size_t rows_per_token,
+                                     size_t n_tokens, size_t tok_stride, size_t dim, float eps, int dtype);
+/* gated_output_norm (src/deltanet_ref.rs:187-198; src/gpu/kernels.metal:3936-3975), per row (V head) of `dim`:
+ *   scale = 1 / sqrt(mean(o^2) + eps);   y = ((o * scale) * w) * (z * sigmoid(z))
+ * in that association; w[dim] is shared by all rows. */
+LOKAL_API int lokal_cuda_gated_output_norm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* o, const void* w, const void* z,
+                                           void* y, size_t rows, size_t dim, float eps, int dtype, int w_dtype);
+/* attn_out_gate (src/deltanet_ref.rs:203-207; src/gpu/kernels.metal:3667-3676):
+ *   out = attn * (1 / (1 + exp(-gate))), elementwise over n elements; out may be attn. */
+LOKAL_API int lokal_cuda_attn_out_gate(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* attn, const void* gate, void* out,
+                                       size_t n, int dtype);
+/* split_q_gate (src/gpu/kernels.metal:4106-4124): a row of the joint projection is
+ * [q(head_dim) | gate(head_dim)] per head; q and gate come out compact,
+ * [rows][n_heads][head_dim] each. A pure copy. */
+LOKAL_API int lokal_cuda_split_q_gate(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* src, void* q, void* gate, size_t rows,
+                                      size_t n_heads, size_t head_dim, int dtype);
+
 /* ---- Token-row sharding over GPUs ---------------------------------------------
  * Rows are independent, so GPU `rank` of `n_gpus` owns the contiguous block
  * [row0, row0+count); no exchange happens on the path. The reference has no

@@ -117,6 +117,10 @@ SIGNATURES = {
     "lokal_cuda_window_write_spans": (_i, [C.POINTER(KvLayout), C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
     "lokal_cuda_kv_rows": (_i, [_vp, _vp, C.POINTER(KvLayout), _vp, _i64, _vp, _u32, _sz, _vp]),
     "lokal_cuda_kv_stage": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _sz, _vp, _sz, _sz]),
+    "lokal_cuda_l2norm_rows": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _f, _i]),
+    "lokal_cuda_gated_output_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _i]),
+    "lokal_cuda_attn_out_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i]),
+    "lokal_cuda_split_q_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "lokal_cuda_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "lokal_cuda_pass_create": (_i, [_vp, C.POINTER(PassConfig), C.POINTER(PassWeights), _pp]),
     "lokal_cuda_pass_destroy": (_i, [_vp, _vp]),

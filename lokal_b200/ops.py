@@ -202,6 +202,25 @@ class Context:
                                                   dst_dtype, width if dst_row_stride is None else dst_row_stride,
                                                   _ptr(dst_rows), rows, width))
 
+    # -- per-row siblings in the gated-deltanet blocks ------------------------------
+    def l2norm_rows(self, x, y=None, *, dim, eps, rows_per_token, n_tokens=1, tok_stride=0, dtype=F32, stream=None):
+        """deltanet_ref::l2_norm over rows: y = x / max(sqrt(sum x^2), eps); in place when y is None."""
+        self._check(self._lib.lokal_cuda_l2norm_rows(self._h, stream, _ptr(x), _ptr(x if y is None else y), rows_per_token,
+                                                     n_tokens, tok_stride, dim, eps, dtype))
+
+    def gated_output_norm(self, o, w, z, y=None, *, rows, dim, eps, dtype=F32, w_dtype=F32, stream=None):
+        """deltanet_ref::gated_output_norm: per row rmsnorm(o; w) * silu(z); in place when y is None."""
+        self._check(self._lib.lokal_cuda_gated_output_norm(self._h, stream, _ptr(o), _ptr(w), _ptr(z), _ptr(o if y is None else y),
+                                                           rows, dim, eps, dtype, w_dtype))
+
+    def attn_out_gate(self, attn, gate, out=None, *, n, dtype=F32, stream=None):
+        """deltanet_ref::attn_out_gate: attn * sigmoid(gate); in place when out is None."""
+        self._check(self._lib.lokal_cuda_attn_out_gate(self._h, stream, _ptr(attn), _ptr(gate), _ptr(attn if out is None else out), n, dtype))
+
+    def split_q_gate(self, src, q, gate, *, rows, n_heads, head_dim, dtype=F32, stream=None):
+        """[q | gate] per head -> compact q and gate."""
+        self._check(self._lib.lokal_cuda_split_q_gate(self._h, stream, _ptr(src), _ptr(q), _ptr(gate), rows, n_heads, head_dim, dtype))
+
     # -- host-slice mirrors of the reference's CPU signatures ----------------------
     def host_rmsnorm(self, x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
         """math::rmsnorm(x, weight, eps) -> new vector; x may be [dim] or [rows, dim]."""

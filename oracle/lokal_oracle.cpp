@@ -305,6 +305,65 @@ ORACLE_API void lokal_ref_swiglu(const float* gate, const float* up, size_t n, f
 }
 
 // ---------------------------------------------------------------------------
+// Per-row siblings of the path in the gated-deltanet (qwen35) blocks
+// (src/deltanet_ref.rs). They accumulate in f64 where the ops above use f32.
+// ---------------------------------------------------------------------------
+
+// src/deltanet_ref.rs:51-57
+static inline float ref_sigmoid(float x) { return 1.0f / (1.0f + std::exp(-x)); }
+static inline float ref_silu_deltanet(float x) { return x * ref_sigmoid(x); }
+ORACLE_API float lokal_ref_sigmoid(float x) { return ref_sigmoid(x); }
+
+// l2_norm (src/deltanet_ref.rs:61-67): x / max(sqrt(sum x^2), eps), sum in f64, in order; the root is taken in f64
+// and narrowed to f32 before the clamp. Rows are addressed as the batched kernel addresses them
+// (src/gpu/kernels.metal:3708-3720): row r of token t starts at t*tok_stride + r*dim.
+ORACLE_API void lokal_ref_l2norm_rows(float* x, size_t rows_per_token, size_t n_tokens, size_t tok_stride, size_t dim, float eps) {
+    for (size_t t = 0; t < n_tokens; t++)
+        for (size_t r = 0; r < rows_per_token; r++) {
+            float* v = x + t * tok_stride + r * dim;
+            double sum = 0.0;
+            for (size_t i = 0; i < dim; i++) sum += (double)v[i] * (double)v[i];
+            const float scale = 1.0f / std::max((float)std::sqrt(sum), eps);
+            for (size_t i = 0; i < dim; i++) v[i] *= scale;
+        }
+}
+
+// rmsnorm with ggml's accumulation (src/deltanet_ref.rs:71-78): mean of squares in f64 narrowed to f32, then
+// (x * scale) * w with scale = 1 / sqrt(mean + eps).
+static void ref_rmsnorm_f64(float* x, const float* w, size_t n, float eps) {
+    double sum = 0.0;
+    for (size_t i = 0; i < n; i++) sum += (double)x[i] * (double)x[i];
+    const float mean = (float)(sum / (double)n);
+    const float scale = 1.0f / std::sqrt(mean + eps);
+    for (size_t i = 0; i < n; i++) x[i] = x[i] * scale * w[i];
+}
+
+// gated_output_norm (src/deltanet_ref.rs:187-198): per head, rmsnorm(o; w) then o *= silu(z); w is shared by heads.
+ORACLE_API void lokal_ref_gated_output_norm(float* o, const float* w, const float* z, size_t heads, size_t dim, float eps) {
+    for (size_t h = 0; h < heads; h++) {
+        float* oh = o + h * dim;
+        ref_rmsnorm_f64(oh, w, dim, eps);
+        for (size_t i = 0; i < dim; i++) oh[i] *= ref_silu_deltanet(z[h * dim + i]);
+    }
+}
+
+// attn_out_gate (src/deltanet_ref.rs:203-207): attn *= sigmoid(gate), elementwise.
+ORACLE_API void lokal_ref_attn_out_gate(float* attn, const float* gate, size_t n) {
+    for (size_t i = 0; i < n; i++) attn[i] *= ref_sigmoid(gate[i]);
+}
+
+// split_q_gate (src/gpu/kernels.metal:4106-4124): a row of the joint projection is [q(hd) | gate(hd)] per head;
+// q and gate come out compact, [rows][heads][hd] each.
+ORACLE_API void lokal_ref_split_q_gate(const float* src, float* q, float* gate, size_t rows, size_t heads, size_t hd) {
+    for (size_t r = 0; r < rows; r++)
+        for (size_t h = 0; h < heads; h++) {
+            const float* s = src + (r * heads + h) * 2 * hd;
+            std::memcpy(q + (r * heads + h) * hd, s, hd * sizeof(float));
+            std::memcpy(gate + (r * heads + h) * hd, s + hd, hd * sizeof(float));
+        }
+}
+
+// ---------------------------------------------------------------------------
 // GGUF block formats (src/gguf/dequant.rs:21-41, 81-119)
 // ---------------------------------------------------------------------------
 

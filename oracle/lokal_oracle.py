@@ -59,6 +59,11 @@ def lib() -> C.CDLL:
             "lokal_ref_add_rmsnorm_rows": (None, [vp, vp, vp, vp, sz, sz, f32, C.c_int]),
             "lokal_ref_qk_rope_rows": (None, [vp, vp, vp, vp, vp, vp, vp, i64, sz, sz, sz, sz, sz, f32, f32, C.c_int]),
             "lokal_ref_swiglu": (None, [vp, vp, sz, vp, C.c_int]),
+            "lokal_ref_sigmoid": (f32, [f32]),
+            "lokal_ref_l2norm_rows": (None, [vp, sz, sz, sz, sz, f32]),
+            "lokal_ref_gated_output_norm": (None, [vp, vp, vp, sz, sz, f32]),
+            "lokal_ref_attn_out_gate": (None, [vp, vp, sz]),
+            "lokal_ref_split_q_gate": (None, [vp, vp, vp, sz, sz, sz]),
             "lokal_ref_blk_elems": (sz, [u32]),
             "lokal_ref_blk_bytes": (sz, [u32]),
             "lokal_ref_row_bytes": (sz, [u32, sz]),
@@ -191,6 +196,46 @@ def swiglu(gate, up, threads: int = 1) -> np.ndarray:
     out = np.empty_like(gate)
     lib().lokal_ref_swiglu(_p(gate), _p(up), gate.size, _p(out), threads)
     return out
+
+
+# ---- gated-deltanet (qwen35) per-row siblings ---------------------------------
+
+def sigmoid(x: float) -> float:
+    return float(lib().lokal_ref_sigmoid(x))
+
+
+def l2norm_rows(x, dim: int, eps: float, rows_per_token: int | None = None, n_tokens: int = 1, tok_stride: int = 0) -> np.ndarray:
+    """x / max(sqrt(sum x^2), eps) per row of `dim`; with n_tokens > 1, row r of token t starts at t*tok_stride + r*dim."""
+    x = _f32c(x).copy()
+    flat = x.reshape(-1)
+    if rows_per_token is None:
+        rows_per_token = flat.size // dim
+    lib().lokal_ref_l2norm_rows(_p(flat), rows_per_token, n_tokens, tok_stride, dim, eps)
+    return x
+
+
+def gated_output_norm(o, w, z, eps: float) -> np.ndarray:
+    """o: [heads, dim], w: [dim], z: [heads, dim] -> rmsnorm(o; w) * silu(z) per head."""
+    o, w, z = _f32c(o).copy(), _f32c(w), _f32c(z)
+    assert o.shape == z.shape and o.shape[-1] == w.size
+    lib().lokal_ref_gated_output_norm(_p(o), _p(w), _p(z), o.size // w.size, w.size, eps)
+    return o
+
+
+def attn_out_gate(attn, gate) -> np.ndarray:
+    attn, gate = _f32c(attn).copy(), _f32c(gate)
+    assert attn.size == gate.size
+    lib().lokal_ref_attn_out_gate(_p(attn), _p(gate), attn.size)
+    return attn
+
+
+def split_q_gate(src, rows: int, heads: int, head_dim: int):
+    src = _f32c(src)
+    assert src.size == rows * heads * 2 * head_dim
+    q = np.empty((rows, heads * head_dim), np.float32)
+    gate = np.empty_like(q)
+    lib().lokal_ref_split_q_gate(_p(src), _p(q), _p(gate), rows, heads, head_dim)
+    return q, gate
 
 
 # ---- gguf dequant ------------------------------------------------------------
