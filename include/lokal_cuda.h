@@ -50,7 +50,10 @@ typedef enum lokal_status {
     LOKAL_ERR_CUDA = 4,        /* a CUDA runtime call failed; message has the detail */
     LOKAL_ERR_ID_RANGE = 5,    /* a token id was >= vocab (row zero-filled on the device) */
     LOKAL_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up */
-    LOKAL_ERR_NO_DEVICE = 7    /* no usable CUDA device */
+    LOKAL_ERR_NO_DEVICE = 7,   /* no usable CUDA device */
+    LOKAL_ERR_IO = 8,          /* a file could not be opened or mapped */
+    LOKAL_ERR_FORMAT = 9,      /* a GGUF file is malformed, truncated or of an unsupported version */
+    LOKAL_ERR_NOT_FOUND = 10   /* a tensor name or metadata key is not in the file */
 } lokal_status;
 
 /* GGUF tensor type ids (src/gguf/dequant.rs:21-41; BF16 = 30 per ggml.h).
@@ -313,6 +316,48 @@ LOKAL_API int lokal_cuda_attn_out_gate(lokal_cuda_ctx* ctx, lokal_cuda_stream s,
  * [rows][n_heads][head_dim] each. A pure copy. */
 LOKAL_API int lokal_cuda_split_q_gate(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* src, void* q, void* gate, size_t rows,
                                       size_t n_heads, size_t head_dim, int dtype);
+
+/* ---- GGUF container reader -------------------------------------------------------
+ * GgufFile (src/gguf/container.rs:152-384): v2/v3, little-endian, mapped read-only.
+ * Host only. Enough to find token_embd.weight, norm weights and biases
+ * (names: src/gguf/arch.rs:229-263) and feed their bytes to the ops above.
+ * open fails with one message that names EVERY tensor type this library does not
+ * decode, with counts and an example tensor each (container.rs:190-245). */
+typedef struct lokal_gguf lokal_gguf;
+typedef struct lokal_gguf_tensor {
+    const char* name;      /* owned by the file handle */
+    uint32_t n_dims;       /* 1..4 */
+    uint64_t dims[4];      /* row-major (the file's ne[] reversed); unused entries are 1 */
+    int32_t ggml_type;     /* lokal_type */
+    uint64_t file_offset;  /* of the first byte, from the start of the file */
+    uint64_t data_offset;  /* the same, from the start of the data section (what the file stores) */
+    uint64_t nbytes;       /* row_bytes(type, product of dims) */
+    const void* data;      /* into the mapping; valid until lokal_gguf_close */
+} lokal_gguf_tensor;
+
+/* GgufFile::open. On failure *out is NULL and `err` (may be NULL) receives the message. */
+LOKAL_API int lokal_gguf_open(const char* path, lokal_gguf** out, char* err, size_t err_len);
+LOKAL_API void lokal_gguf_close(lokal_gguf* g);
+LOKAL_API const char* lokal_gguf_last_error(const lokal_gguf* g);
+LOKAL_API uint32_t lokal_gguf_version(const lokal_gguf* g);
+LOKAL_API size_t lokal_gguf_n_tensors(const lokal_gguf* g);
+LOKAL_API uint64_t lokal_gguf_data_start(const lokal_gguf* g);
+/* GgufFile::tensors (by index, file order) and GgufFile::tensor (by name). */
+LOKAL_API int lokal_gguf_tensor_at(const lokal_gguf* g, size_t i, lokal_gguf_tensor* out);
+LOKAL_API int lokal_gguf_find_tensor(const lokal_gguf* g, const char* name, lokal_gguf_tensor* out);
+/* Typed metadata accessors: has_key, get_usize, get_f32, get_str, get_arr_i64, get_arr_str.
+ * A missing key is LOKAL_ERR_NOT_FOUND, a value of another kind LOKAL_ERR_BAD_ARG; the
+ * message names the key and what was found. Returned pointers are owned by the handle. */
+LOKAL_API int lokal_gguf_has_key(const lokal_gguf* g, const char* key);
+LOKAL_API int lokal_gguf_get_u64(const lokal_gguf* g, const char* key, uint64_t* out);
+LOKAL_API int lokal_gguf_get_f32(const lokal_gguf* g, const char* key, float* out);
+LOKAL_API int lokal_gguf_get_str(const lokal_gguf* g, const char* key, const char** out, size_t* len);
+LOKAL_API int lokal_gguf_get_arr_i64(const lokal_gguf* g, const char* key, const int64_t** out, size_t* n);
+LOKAL_API int lokal_gguf_get_arr_str(const lokal_gguf* g, const char* key, const char* const** out, size_t* n);
+/* Copies one tensor's raw bytes into a fresh device allocation (free with lokal_cuda_free);
+ * blocks until the copy is done. `info` (may be NULL) receives the tensor's description. */
+LOKAL_API int lokal_cuda_gguf_upload(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_gguf* g, const char* name, void** dptr,
+                                     lokal_gguf_tensor* info);
 
 /* ---- Token-row sharding over GPUs ---------------------------------------------
  * Rows are independent, so GPU `rank` of `n_gpus` owns the contiguous block

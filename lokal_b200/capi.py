@@ -18,10 +18,12 @@ QUANT_TYPES = (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS)
 
 # lokal_status
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_CUDA, ERR_ID_RANGE, ERR_TIMEOUT, ERR_NO_DEVICE = range(8)
+ERR_IO, ERR_FORMAT, ERR_NOT_FOUND = 8, 9, 10
 STATUS_NAMES = {
     OK: "LOKAL_OK", ERR_BAD_ARG: "LOKAL_ERR_BAD_ARG", ERR_UNSUPPORTED: "LOKAL_ERR_UNSUPPORTED",
     ERR_MISALIGNED: "LOKAL_ERR_MISALIGNED", ERR_CUDA: "LOKAL_ERR_CUDA", ERR_ID_RANGE: "LOKAL_ERR_ID_RANGE",
-    ERR_TIMEOUT: "LOKAL_ERR_TIMEOUT", ERR_NO_DEVICE: "LOKAL_ERR_NO_DEVICE",
+    ERR_TIMEOUT: "LOKAL_ERR_TIMEOUT", ERR_NO_DEVICE: "LOKAL_ERR_NO_DEVICE", ERR_IO: "LOKAL_ERR_IO",
+    ERR_FORMAT: "LOKAL_ERR_FORMAT", ERR_NOT_FOUND: "LOKAL_ERR_NOT_FOUND",
 }
 
 
@@ -43,6 +45,14 @@ class QkRopeParams(C.Structure):
 class KvLayout(C.Structure):
     """Mirror of lokal_kv_layout."""
     _fields_ = [("max_seq", C.c_uint64), ("sink", C.c_uint64), ("sink_pad", C.c_uint64), ("ring", C.c_uint64)]
+
+
+class GgufTensor(C.Structure):
+    """Mirror of lokal_gguf_tensor."""
+    _fields_ = [
+        ("name", C.c_char_p), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4), ("ggml_type", C.c_int32),
+        ("file_offset", C.c_uint64), ("data_offset", C.c_uint64), ("nbytes", C.c_uint64), ("data", C.c_void_p),
+    ]
 
 
 class PassConfig(C.Structure):
@@ -121,6 +131,21 @@ SIGNATURES = {
     "lokal_cuda_gated_output_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _i]),
     "lokal_cuda_attn_out_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i]),
     "lokal_cuda_split_q_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
+    "lokal_gguf_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p), C.c_char_p, _sz]),
+    "lokal_gguf_close": (None, [_vp]),
+    "lokal_gguf_last_error": (C.c_char_p, [_vp]),
+    "lokal_gguf_version": (_u32, [_vp]),
+    "lokal_gguf_n_tensors": (_sz, [_vp]),
+    "lokal_gguf_data_start": (C.c_uint64, [_vp]),
+    "lokal_gguf_tensor_at": (_i, [_vp, _sz, C.POINTER(GgufTensor)]),
+    "lokal_gguf_find_tensor": (_i, [_vp, C.c_char_p, C.POINTER(GgufTensor)]),
+    "lokal_gguf_has_key": (_i, [_vp, C.c_char_p]),
+    "lokal_gguf_get_u64": (_i, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "lokal_gguf_get_f32": (_i, [_vp, C.c_char_p, C.POINTER(C.c_float)]),
+    "lokal_gguf_get_str": (_i, [_vp, C.c_char_p, C.POINTER(C.c_char_p), C.POINTER(_sz)]),
+    "lokal_gguf_get_arr_i64": (_i, [_vp, C.c_char_p, C.POINTER(C.POINTER(C.c_int64)), C.POINTER(_sz)]),
+    "lokal_gguf_get_arr_str": (_i, [_vp, C.c_char_p, C.POINTER(C.POINTER(C.c_char_p)), C.POINTER(_sz)]),
+    "lokal_cuda_gguf_upload": (_i, [_vp, _vp, _vp, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(GgufTensor)]),
     "lokal_cuda_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "lokal_cuda_pass_create": (_i, [_vp, C.POINTER(PassConfig), C.POINTER(PassWeights), _pp]),
     "lokal_cuda_pass_destroy": (_i, [_vp, _vp]),

@@ -99,6 +99,12 @@ class Context:
     def free(self, p):
         self._check(self._lib.lokal_cuda_free(self._h, p))
 
+    def gguf_upload(self, gguf, name: str, stream=None):
+        """One tensor of an open GgufFile copied into a fresh device allocation: (device pointer, GgufTensor)."""
+        p, info = C.c_void_p(), capi.GgufTensor()
+        self._check(self._lib.lokal_cuda_gguf_upload(self._h, stream, gguf.handle, name.encode(), C.byref(p), C.byref(info)))
+        return p.value or 0, info
+
     def host_alloc(self, nbytes: int) -> int:
         p = C.c_void_p()
         self._check(self._lib.lokal_cuda_host_alloc(self._h, nbytes, C.byref(p)))

@@ -14,7 +14,7 @@ HEADER = open(os.path.join(ROOT, "include", "lokal_cuda.h")).read()
 
 
 def declared_functions():
-    return re.findall(r"LOKAL_API\s+[\w\s\*]+?\b(lokal_cuda_\w+)\s*\(", HEADER)
+    return re.findall(r"LOKAL_API\s+[\w\s\*]+?\b(lokal_(?:cuda|gguf)_\w+)\s*\(", HEADER)
 
 
 def test_library_exports_every_declared_symbol():
