@@ -31,6 +31,7 @@ struct NormArgs {
     int w_dtype;
     int h_dtype;
     int w_vec_ok;
+    int prefetch;  // ask L2 for the row before waiting for the previous kernel
 };
 
 template <typename T, int N>
@@ -57,7 +58,7 @@ __device__ __forceinline__ void store_h_copy(void* base, int h_dtype, size_t ele
 
 template <typename T, int VPT, bool CTA_MODE>
 __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const NormArgs a) {
-    pdl_sync();
+    pdl_launch();
     constexpr int N = VecOf<T>::N;
     const unsigned tpr = CTA_MODE ? blockDim.x : 32u;
     const unsigned t = CTA_MODE ? threadIdx.x : (threadIdx.x & 31u);
@@ -67,6 +68,17 @@ __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const 
 
     const T* xr = reinterpret_cast<const T*>(a.x) + row * a.dim;
     const T* dr = a.delta ? reinterpret_cast<const T*>(a.delta) + row * a.dim : nullptr;
+    if (a.prefetch) {  // one request per 128-byte line of the row, while the kernel before this one drains
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+            const unsigned idx = t + j * tpr;
+            if (idx < a.nvec && (idx & 7u) == 0) {
+                prefetch_l2(xr + static_cast<size_t>(idx) * N);
+                if (dr) prefetch_l2(dr + static_cast<size_t>(idx) * N);
+            }
+        }
+    }
+    pdl_wait();
 
     // All loads of the row are issued before any is consumed.
     uint4 xv[VPT], dv[VPT];
@@ -250,6 +262,7 @@ int launch_norm(lokal_cuda_ctx* ctx, cudaStream_t s, void* x, const void* delta,
     a.w_dtype = w_dtype;
     a.h_dtype = h_dtype;
     a.w_vec_ok = aligned_to(w, 16);
+    a.prefetch = prefetch_enabled();
     const bool aligned = aligned_to(x, 16) && aligned_to(xn, 16) && (!delta || aligned_to(delta, 16)) &&
                          (!xn_h || aligned_to(xn_h, 8)) && (dim * es) % 16 == 0;
     switch (dtype) {

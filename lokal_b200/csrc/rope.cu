@@ -80,6 +80,7 @@ struct QkArgs {
     unsigned wpr;      // warps per row
     unsigned q_row_bytes, k_row_bytes;  // n_q*head_dim*sizeof(T), n_kv*head_dim*sizeof(T) (staged kernel)
     unsigned stage_bytes;               // per-warp staging area, multiple of 128
+    int prefetch;                       // ask L2 for the row before waiting for the previous kernel (staged kernel)
     unsigned* err_word;
 };
 
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
 // global memory. Same lane mapping, arithmetic and results as qk_rope_kernel.
 template <typename T, int HD, bool NORM, bool BIAS>
 __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) {
-    pdl_sync();
+    pdl_launch();
     using R = RopeRow<T, HD, NORM, BIAS>;
     constexpr int N = R::N, HALF = R::HALF, HPW = R::HPW;
     extern __shared__ __align__(128) unsigned char dyn_smem[];
@@ -309,6 +310,13 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
     const unsigned long long warp = static_cast<unsigned long long>(blockIdx.x) * warps_per_cta + warp_in_cta;
     const bool valid = warp < a.rows;
     const unsigned long long row = valid ? warp : a.rows - 1;
+    if (a.prefetch && valid) {  // the row's lines are asked of L2 while the kernel before this one drains
+        const unsigned char* qrow = reinterpret_cast<const unsigned char*>(reinterpret_cast<const T*>(a.q) + row * a.q_stride);
+        const unsigned char* krow = reinterpret_cast<const unsigned char*>(reinterpret_cast<const T*>(a.k) + row * a.k_stride);
+        for (unsigned off = lane * 128u; off < a.q_row_bytes; off += 32u * 128u) prefetch_l2(qrow + off);
+        for (unsigned off = lane * 128u; off < a.k_row_bytes; off += 32u * 128u) prefetch_l2(krow + off);
+    }
+    pdl_wait();
     if (lane == 0) {
         mbar_init(bar, 1);
         mbar_init_fence();
@@ -443,6 +451,7 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     a.k_row_bytes = a.n_kv * a.head_dim * static_cast<unsigned>(sizeof(T));
     a.stage_bytes = (a.q_row_bytes + a.k_row_bytes + 127u) & ~127u;
     a.err_word = ctx->err_word;
+    a.prefetch = prefetch_enabled();
     // Staged kernel: whole rows through shared memory by bulk copy. Needs one warp per row, row starts that are
     // 16-byte aligned (true on this path) and a row small enough that several warps' stages fit in shared memory.
     const bool staged_ok = a.wpr == 1 && a.stage_bytes <= 24u * 1024u && tune_env("LOKAL_CUDA_ROPE_STAGED", 1) != 0;

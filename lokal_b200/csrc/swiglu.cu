@@ -32,6 +32,7 @@ struct SwigluArgs {
     unsigned long long nvec;  // whole 16-byte vectors
     unsigned long long n;     // elements
     int h_dtype;
+    int prefetch;  // ask L2 for the tile before waiting for the previous kernel
 };
 
 constexpr int kSwigluUnroll = 4;
@@ -62,7 +63,7 @@ __device__ __forceinline__ void swiglu_store(const SwigluArgs& a, uint4* o, unsi
 
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
-    pdl_sync();
+    pdl_launch();
     // Each CTA owns a contiguous tile of kSwigluUnroll * 256 vectors (16 KB per stream); a thread's vectors are
     // 256 apart, so every load instruction of a warp is one 512-byte run. Many small CTAs: the machine drains
     // evenly at the end of the kernel. All 64-bit address arithmetic is done once per CTA.
@@ -72,6 +73,16 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
     const uint4* u = reinterpret_cast<const uint4*>(a.up) + tile0 + threadIdx.x;
     uint4* o = reinterpret_cast<uint4*>(a.out) + tile0 + threadIdx.x;
     const unsigned long long left = a.nvec - tile0;
+    if (a.prefetch && (threadIdx.x & 7u) == 0) {  // one request per 128-byte line of the tile, before the wait
+#pragma unroll
+        for (int j = 0; j < kSwigluUnroll; j++) {
+            if (threadIdx.x + j * 256 < left) {
+                prefetch_l2(g + j * 256);
+                prefetch_l2(u + j * 256);
+            }
+        }
+    }
+    pdl_wait();
     uint4 gv[kSwigluUnroll], uv[kSwigluUnroll];
     if (left >= kTile) {
 #pragma unroll
@@ -157,6 +168,7 @@ int launch_swiglu(lokal_cuda_ctx* ctx, cudaStream_t s, const void* gate, const v
     a.out_h = out_h;
     a.n = n;
     a.h_dtype = h_dtype;
+    a.prefetch = prefetch_enabled();
     const bool aligned = aligned_to(gate, 16) && aligned_to(up, 16) && aligned_to(out, 16) && (!out_h || aligned_to(out_h, 8));
     switch (dtype) {
         case LOKAL_F32: return launch_typed<float>(ctx, s, a, aligned);
