@@ -59,8 +59,9 @@ typedef enum lokal_status {
 /* GGUF tensor type ids (src/gguf/dequant.rs:21-41; BF16 = 30 per ggml.h).
  * F32/F16/BF16 are the activation and weight-vector types of every op; all of
  * them are table types of embed_gather / dequant_rows (block sizes
- * src/gguf/dequant.rs:94-114). The codebook types (IQ1/IQ2/IQ3) and the
- * activation-only Q8_1/Q8_K are not covered: LOKAL_ERR_UNSUPPORTED. */
+ * src/gguf/dequant.rs:94-114). The codebook types (IQ1_S .. IQ3_S) decode once the
+ * caller has handed over their codebooks (lokal_cuda_set_iq_grid). Q4_1, Q5_1 and the
+ * activation-only Q8_1/Q8_K are not covered: LOKAL_ERR_UNSUPPORTED, as in the reference. */
 typedef enum lokal_type {
     LOKAL_F32 = 0,
     LOKAL_F16 = 1,
@@ -72,8 +73,15 @@ typedef enum lokal_type {
     LOKAL_Q4_K = 12,
     LOKAL_Q5_K = 13,
     LOKAL_Q6_K = 14,
+    LOKAL_IQ2_XXS = 16,
+    LOKAL_IQ2_XS = 17,
+    LOKAL_IQ3_XXS = 18,
+    LOKAL_IQ1_S = 19,
     LOKAL_IQ4_NL = 20,
+    LOKAL_IQ3_S = 21,
+    LOKAL_IQ2_S = 22,
     LOKAL_IQ4_XS = 23,
+    LOKAL_IQ1_M = 29,
     LOKAL_BF16 = 30
 } lokal_type;
 
@@ -115,6 +123,24 @@ LOKAL_API int lokal_cuda_graph_destroy(lokal_cuda_ctx* ctx, lokal_cuda_graph* g)
 LOKAL_API size_t lokal_cuda_blk_elems(int ggml_type);
 LOKAL_API size_t lokal_cuda_blk_bytes(int ggml_type);
 LOKAL_API size_t lokal_cuda_row_bytes(int ggml_type, size_t n);
+
+/* The i-quant codebooks (src/lowmem/iq_grids.rs: iq2xxs_grid ... iq1s_grid of ggml-common.h).
+ * They are fitted tables of the file format, not formulas, and this library does not carry
+ * them: the host application uploads its own copy once per context. Until then a table of the
+ * corresponding type is refused with LOKAL_ERR_UNSUPPORTED. ksigns_iq2xs / kmask_iq2xs are
+ * derivable (7 bits + even parity; powers of two) and are computed.
+ *   which                entries     used by
+ *   LOKAL_GRID_IQ2XXS    256 x u64   IQ2_XXS
+ *   LOKAL_GRID_IQ2XS     512 x u64   IQ2_XS
+ *   LOKAL_GRID_IQ2S     1024 x u64   IQ2_S
+ *   LOKAL_GRID_IQ3XXS    256 x u32   IQ3_XXS
+ *   LOKAL_GRID_IQ3S      512 x u32   IQ3_S
+ *   LOKAL_GRID_IQ1S     2048 x u64   IQ1_S, IQ1_M
+ * `table` is a host pointer, `bytes` must be entries x entry size. Blocking. */
+typedef enum lokal_iq_grid {
+    LOKAL_GRID_IQ2XXS = 0, LOKAL_GRID_IQ2XS = 1, LOKAL_GRID_IQ2S = 2, LOKAL_GRID_IQ3XXS = 3, LOKAL_GRID_IQ3S = 4, LOKAL_GRID_IQ1S = 5
+} lokal_iq_grid;
+LOKAL_API int lokal_cuda_set_iq_grid(lokal_cuda_ctx* ctx, int which, const void* table, size_t bytes);
 
 /* ---- RMSNorm --------------------------------------------------------------
  * math::rmsnorm (src/math.rs:45-49) over `rows` rows of `dim`; GPU twins

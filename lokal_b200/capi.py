@@ -15,6 +15,10 @@ from . import _build
 F32, F16, Q8_0, Q4_K, BF16 = 0, 1, 8, 12, 30
 Q4_0, Q5_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 2, 6, 10, 11, 13, 14, 20, 23
 QUANT_TYPES = (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS)
+# codebook types: decodable once their codebooks have been handed over (Context.set_iq_grids)
+IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M = 16, 17, 18, 19, 21, 22, 29
+GRID_TYPES = (IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M)
+GRID_ORDER = ("iq2xxs", "iq2xs", "iq2s", "iq3xxs", "iq3s", "iq1s")  # index = lokal_iq_grid
 
 # lokal_status
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_CUDA, ERR_ID_RANGE, ERR_TIMEOUT, ERR_NO_DEVICE = range(8)
@@ -146,6 +150,7 @@ SIGNATURES = {
     "lokal_gguf_get_arr_i64": (_i, [_vp, C.c_char_p, C.POINTER(C.POINTER(C.c_int64)), C.POINTER(_sz)]),
     "lokal_gguf_get_arr_str": (_i, [_vp, C.c_char_p, C.POINTER(C.POINTER(C.c_char_p)), C.POINTER(_sz)]),
     "lokal_cuda_gguf_upload": (_i, [_vp, _vp, _vp, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(GgufTensor)]),
+    "lokal_cuda_set_iq_grid": (_i, [_vp, _i, _vp, _sz]),
     "lokal_cuda_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "lokal_cuda_pass_create": (_i, [_vp, C.POINTER(PassConfig), C.POINTER(PassWeights), _pp]),
     "lokal_cuda_pass_destroy": (_i, [_vp, _vp]),

@@ -116,6 +116,8 @@ void lokal_cuda_destroy(lokal_cuda_ctx* ctx) {
     if (ctx->err_word_host) cudaFreeHost(ctx->err_word_host);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->staging) cudaFreeHost(ctx->staging);
+    for (void* g : ctx->iq_grids)
+        if (g) cudaFree(g);
     delete ctx;
 }
 
@@ -243,7 +245,9 @@ size_t lokal_cuda_blk_elems(int t) {
     switch (t) {
         case LOKAL_F32: case LOKAL_F16: case LOKAL_BF16: return 1;
         case LOKAL_Q4_0: case LOKAL_Q5_0: case LOKAL_Q8_0: case LOKAL_IQ4_NL: return 32;
-        case LOKAL_Q2_K: case LOKAL_Q3_K: case LOKAL_Q4_K: case LOKAL_Q5_K: case LOKAL_Q6_K: case LOKAL_IQ4_XS: return 256;
+        case LOKAL_Q2_K: case LOKAL_Q3_K: case LOKAL_Q4_K: case LOKAL_Q5_K: case LOKAL_Q6_K: case LOKAL_IQ4_XS:
+        case LOKAL_IQ2_XXS: case LOKAL_IQ2_XS: case LOKAL_IQ2_S: case LOKAL_IQ3_XXS: case LOKAL_IQ3_S: case LOKAL_IQ1_S: case LOKAL_IQ1_M:
+            return 256;
         default: return 0;
     }
 }
@@ -261,8 +265,32 @@ size_t lokal_cuda_blk_bytes(int t) {
         case LOKAL_Q5_K: return 176;
         case LOKAL_Q6_K: return 210;
         case LOKAL_IQ4_XS: return 136;
+        case LOKAL_IQ1_S: return 50;
+        case LOKAL_IQ1_M: return 56;
+        case LOKAL_IQ2_XXS: return 66;
+        case LOKAL_IQ2_XS: return 74;
+        case LOKAL_IQ2_S: return 82;
+        case LOKAL_IQ3_XXS: return 98;
+        case LOKAL_IQ3_S: return 110;
         default: return 0;
     }
+}
+
+// Codebook entries and entry size of lokal_iq_grid `which`.
+static const size_t kIqGridEntries[6] = {256, 512, 1024, 256, 512, 2048};
+static const size_t kIqGridEntryBytes[6] = {8, 8, 8, 4, 4, 8};
+
+int lokal_cuda_set_iq_grid(lokal_cuda_ctx* ctx, int which, const void* table, size_t bytes) {
+    LOKAL_ENTER(ctx);
+    if (which < 0 || which > 5) return ctx->fail(LOKAL_ERR_BAD_ARG, "set_iq_grid: codebook %d does not exist", which);
+    const size_t want = kIqGridEntries[which] * kIqGridEntryBytes[which];
+    if (!table || bytes != want)
+        return ctx->fail(LOKAL_ERR_BAD_ARG, "set_iq_grid: codebook %d holds %zu entries of %zu bytes = %zu bytes, got %zu", which,
+                         kIqGridEntries[which], kIqGridEntryBytes[which], want, bytes);
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (!ctx->iq_grids[which]) LOKAL_CUDA_TRY(ctx, cudaMalloc(&ctx->iq_grids[which], want));
+    LOKAL_CUDA_TRY(ctx, cudaMemcpy(ctx->iq_grids[which], table, want, cudaMemcpyHostToDevice));
+    return LOKAL_OK;
 }
 
 size_t lokal_cuda_row_bytes(int t, size_t n) {

@@ -42,6 +42,7 @@ struct GatherArgs {
     unsigned dim;
     unsigned row_bytes;
     unsigned stage_bytes;  // per warp per stage, multiple of 16
+    const void* grid;      // the codebook of an IQ1 / IQ2 / IQ3 table type (device memory), else null
     unsigned* err_word;
 };
 
@@ -189,6 +190,94 @@ __device__ __forceinline__ float dequant_elem(const Rd& rd, unsigned col) {
     }
 }
 
+// ---- codebook types (IQ1_S, IQ1_M, IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S) ----
+// A 256-element super-block is eight groups of 32; a group is four runs of eight values; a run is one codebook
+// entry of eight bytes (IQ1 / IQ2) or two entries of four bytes (IQ3). `grid` is the caller's codebook in device
+// memory (lokal_cuda_set_iq_grid); every lookup is a load that L1 serves after the first touch. Element (group ib,
+// run l, value j) exactly as src/gguf/dequant.rs:255-394 index it.
+template <int QT>
+constexpr bool kIsGridType = QT == LOKAL_IQ1_S || QT == LOKAL_IQ1_M || QT == LOKAL_IQ2_XXS || QT == LOKAL_IQ2_XS ||
+                             QT == LOKAL_IQ2_S || QT == LOKAL_IQ3_XXS || QT == LOKAL_IQ3_S;
+
+// ksigns_iq2xs[i]: the 7-bit value with bit 7 set so that the byte has even parity (src/lowmem/iq_grids.rs:12-22).
+__device__ __forceinline__ unsigned ksigns_iq2xs(unsigned i) { return i | ((__popc(i) & 1u) << 7); }
+
+template <typename Rd>
+__device__ __forceinline__ unsigned rd_u16(const Rd& rd, unsigned off) { return rd(off) | (rd(off + 1) << 8); }
+
+template <int QT, typename Rd>
+__device__ __forceinline__ float dequant_grid_elem(const Rd& rd, const void* grid, unsigned col) {
+    const unsigned i = col & 255, ib = i >> 5, l = (i >> 3) & 3, j = i & 7;
+    const unsigned long long* g64 = static_cast<const unsigned long long*>(grid);
+    const unsigned* g32 = static_cast<const unsigned*>(grid);
+    auto signed_of = [](float t, unsigned signs, unsigned bit) { return ((signs >> bit) & 1u) ? -t : t; };  // t * (+-1.0)
+    if constexpr (QT == LOKAL_IQ1_S) {  // :255-270: d | qs[32] | qh[8 x u16]
+        const unsigned b = (col >> 8) * 50;
+        const unsigned qh = rd_u16(rd, b + 34 + 2 * ib);
+        const float dl = __fmul_rn(rd_f16(rd, b), static_cast<float>(2 * ((qh >> 12) & 7u) + 1));
+        const float delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+        const unsigned gi = rd(b + 2 + 4 * ib + l) | (((qh >> (3 * l)) & 7u) << 8);
+        const int g = static_cast<int>(static_cast<signed char>((__ldg(g64 + gi) >> (8 * j)) & 0xFF));
+        return __fmul_rn(dl, __fadd_rn(static_cast<float>(g), delta));
+    } else if constexpr (QT == LOKAL_IQ1_M) {  // :274-293: qs[32] | qh[16] | scales[4 x u16], the f16 d in their top nibbles
+        const unsigned b = (col >> 8) * 56;
+        const unsigned s0 = rd_u16(rd, b + 48), s1 = rd_u16(rd, b + 50), s2 = rd_u16(rd, b + 52), s3 = rd_u16(rd, b + 54);
+        const unsigned bits = (s0 >> 12) | ((s1 >> 8) & 0x00F0u) | ((s2 >> 4) & 0x0F00u) | (s3 & 0xF000u);
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(bits)));
+        const unsigned sw = (ib >> 1) == 0 ? s0 : (ib >> 1) == 1 ? s1 : (ib >> 1) == 2 ? s2 : s3;
+        const unsigned shift = 6 * (ib & 1) + (l < 2 ? 0 : 3);
+        const float dl = __fmul_rn(d, static_cast<float>(2 * ((sw >> shift) & 7u) + 1));
+        const unsigned qh = rd(b + 32 + 2 * ib + (l >> 1));
+        const bool even = (l & 1) == 0;
+        const unsigned gi = rd(b + 4 * ib + l) | ((qh << (even ? 8 : 4)) & 0x700u);
+        const float delta = (qh & (even ? 0x08u : 0x80u)) ? -0.125f : 0.125f;
+        const int g = static_cast<int>(static_cast<signed char>((__ldg(g64 + gi) >> (8 * j)) & 0xFF));
+        return __fmul_rn(dl, __fadd_rn(static_cast<float>(g), delta));
+    } else if constexpr (QT == LOKAL_IQ2_XXS) {  // :295-312: d | 8 x (4 grid bytes, u32: 4 x 7 sign bits + 4-bit scale)
+        const unsigned b = (col >> 8) * 66 + 2 + 8 * ib;
+        const unsigned a1 = rd_u16(rd, b + 4) | (rd_u16(rd, b + 6) << 16);
+        const float db = __fmul_rn(__fmul_rn(rd_f16(rd, (col >> 8) * 66), __fadd_rn(0.5f, static_cast<float>(a1 >> 28))), 0.25f);
+        const unsigned g = static_cast<unsigned>(__ldg(g64 + rd(b + l)) >> (8 * j)) & 0xFFu;
+        return signed_of(__fmul_rn(db, static_cast<float>(g)), ksigns_iq2xs((a1 >> (7 * l)) & 127u), j);
+    } else if constexpr (QT == LOKAL_IQ2_XS || QT == LOKAL_IQ2_S) {  // :314-352: 4-bit scales, two runs to a nibble
+        constexpr unsigned BB = QT == LOKAL_IQ2_XS ? 74 : 82, SC = QT == LOKAL_IQ2_XS ? 66 : 74;
+        const unsigned b = (col >> 8) * BB;
+        const unsigned sc = rd(b + SC + ib);
+        const float db = __fmul_rn(__fmul_rn(rd_f16(rd, b), __fadd_rn(0.5f, static_cast<float>(l < 2 ? (sc & 15u) : (sc >> 4)))), 0.25f);
+        unsigned gi, signs;
+        if constexpr (QT == LOKAL_IQ2_XS) {  // qs[32 x u16]: 9-bit grid index, 7-bit sign selector
+            const unsigned qv = rd_u16(rd, b + 2 + 2 * (4 * ib + l));
+            gi = qv & 511u;
+            signs = ksigns_iq2xs(qv >> 9);
+        } else {  // qs[32 grid bytes + 32 sign bytes] | qh[8]: two more index bits
+            gi = rd(b + 2 + 4 * ib + l) | ((rd(b + 66 + ib) << (8 - 2 * l)) & 0x300u);
+            signs = rd(b + 34 + 4 * ib + l);
+        }
+        const unsigned g = static_cast<unsigned>(__ldg(g64 + gi) >> (8 * j)) & 0xFFu;
+        return signed_of(__fmul_rn(db, static_cast<float>(g)), signs, j);
+    } else if constexpr (QT == LOKAL_IQ3_XXS) {  // :354-374: d | qs[64 grid bytes] | 8 x u32 (4 x 7 sign bits + 4-bit scale)
+        const unsigned b = (col >> 8) * 98;
+        const unsigned aux = rd_u16(rd, b + 66 + 4 * ib) | (rd_u16(rd, b + 68 + 4 * ib) << 16);
+        const float db = __fmul_rn(__fmul_rn(rd_f16(rd, b), __fadd_rn(0.5f, static_cast<float>(aux >> 28))), 0.5f);
+        const unsigned g = (__ldg(g32 + rd(b + 2 + 8 * ib + 2 * l + (j >> 2))) >> (8 * (j & 3))) & 0xFFu;
+        return signed_of(__fmul_rn(db, static_cast<float>(g)), ksigns_iq2xs((aux >> (7 * l)) & 127u), j);
+    } else {  // LOKAL_IQ3_S, :376-394: d | qs[64] | qh[8] | signs[32] | scales[4]; qh gives a ninth index bit
+        const unsigned b = (col >> 8) * 110, hf = j >> 2;
+        const unsigned scb = rd(b + 106 + (ib >> 1));
+        const float db = __fmul_rn(rd_f16(rd, b), static_cast<float>(1 + 2 * ((ib & 1) ? (scb >> 4) : (scb & 15u))));
+        const unsigned gi = rd(b + 2 + 8 * ib + 2 * l + hf) | ((rd(b + 66 + ib) << (8 - 2 * l - hf)) & 256u);
+        const unsigned g = (__ldg(g32 + gi) >> (8 * (j & 3))) & 0xFFu;
+        return signed_of(__fmul_rn(db, static_cast<float>(g)), rd(b + 74 + 4 * ib + l), j);
+    }
+}
+
+// Any quantised type: the arms above, chosen at compile time.
+template <int QT, typename Rd>
+__device__ __forceinline__ float dequant_any_elem(const Rd& rd, const void* grid, unsigned col) {
+    if constexpr (kIsGridType<QT>) return dequant_grid_elem<QT>(rd, grid, col);
+    else return dequant_elem<QT>(rd, col);
+}
+
 // ---- vector decoders for the staged kernel ----
 // EPL (4 or 8) consecutive elements starting at e, e % EPL == 0, of the row staged at `row` in shared memory.
 // Such a run never crosses a 16-element sub-group, so it has one scale (and one min), its quants sit in EPL
@@ -312,6 +401,15 @@ __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned 
     }
 }
 
+// Codebook types in the staged kernel: the element decoder over the staged row.
+template <int QT, int EPL>
+__device__ __forceinline__ void decode_grid_block(const unsigned char* row, unsigned e, const void* grid, float2 (&y)[EPL / 2]) {
+    const SharedBytes rd{row};
+#pragma unroll
+    for (int k = 0; k < EPL / 2; k++)
+        y[k] = make_float2(dequant_grid_elem<QT>(rd, grid, e + 2 * k), dequant_grid_elem<QT>(rd, grid, e + 2 * k + 1));
+}
+
 // Calls f(std::integral_constant<int, type>) for a quantised table type.
 template <typename F>
 void for_quant_type(int t, F&& f) {
@@ -319,7 +417,9 @@ void for_quant_type(int t, F&& f) {
 #define LOKAL_QT_CASE(T) case T: f(std::integral_constant<int, T>{}); break;
         LOKAL_QT_CASE(LOKAL_Q4_0) LOKAL_QT_CASE(LOKAL_Q5_0) LOKAL_QT_CASE(LOKAL_Q8_0) LOKAL_QT_CASE(LOKAL_Q2_K)
         LOKAL_QT_CASE(LOKAL_Q3_K) LOKAL_QT_CASE(LOKAL_Q4_K) LOKAL_QT_CASE(LOKAL_Q5_K) LOKAL_QT_CASE(LOKAL_Q6_K)
-        LOKAL_QT_CASE(LOKAL_IQ4_NL) LOKAL_QT_CASE(LOKAL_IQ4_XS)
+        LOKAL_QT_CASE(LOKAL_IQ4_NL) LOKAL_QT_CASE(LOKAL_IQ4_XS) LOKAL_QT_CASE(LOKAL_IQ1_S) LOKAL_QT_CASE(LOKAL_IQ1_M)
+        LOKAL_QT_CASE(LOKAL_IQ2_XXS) LOKAL_QT_CASE(LOKAL_IQ2_XS) LOKAL_QT_CASE(LOKAL_IQ2_S) LOKAL_QT_CASE(LOKAL_IQ3_XXS)
+        LOKAL_QT_CASE(LOKAL_IQ3_S)
 #undef LOKAL_QT_CASE
         default: break;
     }
@@ -435,7 +535,8 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
             const unsigned char* row = stage_ptr(s) + ((state >> (8 + 4 * s)) & 15u);
             for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
                 float2 y[EPL / 2];
-                decode_block<QT, EPL>(row, e, lut, y);
+                if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
+                else decode_block<QT, EPL>(row, e, lut, y);
                 store_out16<OutT>(orow + e, y);
             }
         }
@@ -460,7 +561,7 @@ __global__ void __launch_bounds__(256) gather_quant_plain_kernel(const GatherArg
         return;
     }
     const GlobalBytes rd{a.table + id * a.row_bytes};
-    for (unsigned e = lane; e < a.dim; e += 32) orow[e] = from_f32<OutT>(dequant_elem<QT>(rd, e));
+    for (unsigned e = lane; e < a.dim; e += 32) orow[e] = from_f32<OutT>(dequant_any_elem<QT>(rd, a.grid, e));
 }
 
 // ---- float tables (F32 / F16 / BF16): copy or widen/narrow a row ----
@@ -558,7 +659,7 @@ int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int gg
                   const uint32_t* ids, size_t n, void* out, int out_dtype) {
     if (!table || !out) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: table and out must be non-null");
     const size_t be = lokal_cuda_blk_elems(ggml_type);
-    if (be == 0) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: ggml type %d is not a float type or one of Q4_0 Q5_0 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS", ggml_type);
+    if (be == 0) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: ggml type %d is not a float type, a Q*_0 / Q*_K block type or an i-quant (Q4_1, Q5_1, Q8_1, Q8_K are not covered)", ggml_type);
     if (!is_act_type(out_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: output type %d is not F32/F16/BF16", out_dtype);
     if (dim == 0 || dim > 0x7fffffffu) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: dim %zu out of range", dim);
     if (dim % be != 0)
@@ -581,6 +682,17 @@ int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int gg
     a.dim = static_cast<unsigned>(dim);
     a.row_bytes = static_cast<unsigned>(rb);
     a.err_word = ctx->err_word;
+    static const struct { int type, grid; const char* name; } kGridOf[] = {
+        {LOKAL_IQ2_XXS, LOKAL_GRID_IQ2XXS, "iq2xxs"}, {LOKAL_IQ2_XS, LOKAL_GRID_IQ2XS, "iq2xs"}, {LOKAL_IQ2_S, LOKAL_GRID_IQ2S, "iq2s"},
+        {LOKAL_IQ3_XXS, LOKAL_GRID_IQ3XXS, "iq3xxs"}, {LOKAL_IQ3_S, LOKAL_GRID_IQ3S, "iq3s"}, {LOKAL_IQ1_S, LOKAL_GRID_IQ1S, "iq1s"},
+        {LOKAL_IQ1_M, LOKAL_GRID_IQ1S, "iq1s"}};
+    for (const auto& g : kGridOf) {
+        if (g.type != ggml_type) continue;
+        a.grid = ctx->iq_grids[g.grid];
+        if (!a.grid)
+            return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: ggml type %d needs the %s codebook: hand it over with lokal_cuda_set_iq_grid first",
+                             ggml_type, g.name);
+    }
     const bool aligned = aligned_to(table, 16) && aligned_to(out, 16) && (dim * type_size(out_dtype)) % 16 == 0;
     switch (out_dtype) {
         case LOKAL_F32: return launch_out<float>(ctx, s, a, ggml_type, aligned);

@@ -99,6 +99,15 @@ class Context:
     def free(self, p):
         self._check(self._lib.lokal_cuda_free(self._h, p))
 
+    def set_iq_grids(self, grids) -> None:
+        """Hands the i-quant codebooks to the library (a mapping with the keys of capi.GRID_ORDER: iq2xxs, iq2xs, iq2s
+        as uint64, iq3xxs, iq3s as uint32, iq1s as uint64). They are data of the file format kept by the host
+        application (src/lowmem/iq_grids.rs in the reference); the library carries no copy."""
+        for which, key in enumerate(capi.GRID_ORDER):
+            if key in grids:
+                a = np.ascontiguousarray(grids[key])
+                self._check(self._lib.lokal_cuda_set_iq_grid(self._h, which, _ptr(a), a.nbytes))
+
     def gguf_upload(self, gguf, name: str, stream=None):
         """One tensor of an open GgufFile copied into a fresh device allocation: (device pointer, GgufTensor)."""
         p, info = C.c_void_p(), capi.GgufTensor()

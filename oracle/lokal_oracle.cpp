@@ -369,17 +369,38 @@ ORACLE_API void lokal_ref_split_q_gate(const float* src, float* q, float* gate, 
 
 enum : uint32_t {
     GGML_F32 = 0, GGML_F16 = 1, GGML_Q4_0 = 2, GGML_Q5_0 = 6, GGML_Q8_0 = 8, GGML_Q2_K = 10, GGML_Q3_K = 11,
-    GGML_Q4_K = 12, GGML_Q5_K = 13, GGML_Q6_K = 14, GGML_IQ4_NL = 20, GGML_IQ4_XS = 23, GGML_BF16 = 30
+    GGML_Q4_K = 12, GGML_Q5_K = 13, GGML_Q6_K = 14, GGML_IQ2_XXS = 16, GGML_IQ2_XS = 17, GGML_IQ3_XXS = 18,
+    GGML_IQ1_S = 19, GGML_IQ4_NL = 20, GGML_IQ3_S = 21, GGML_IQ2_S = 22, GGML_IQ4_XS = 23, GGML_IQ1_M = 29, GGML_BF16 = 30
 };
 
 ORACLE_API size_t lokal_ref_blk_elems(uint32_t ty) {
     switch (ty) {
         case GGML_F32: case GGML_F16: case GGML_BF16: return 1;
         case GGML_Q4_0: case GGML_Q5_0: case GGML_Q8_0: case GGML_IQ4_NL: return 32;
-        case GGML_Q2_K: case GGML_Q3_K: case GGML_Q4_K: case GGML_Q5_K: case GGML_Q6_K: case GGML_IQ4_XS: return 256;
+        case GGML_Q2_K: case GGML_Q3_K: case GGML_Q4_K: case GGML_Q5_K: case GGML_Q6_K: case GGML_IQ4_XS:
+        case GGML_IQ2_XXS: case GGML_IQ2_XS: case GGML_IQ2_S: case GGML_IQ3_XXS: case GGML_IQ3_S: case GGML_IQ1_S: case GGML_IQ1_M:
+            return 256;
         default: return 0;
     }
 }
+
+// The i-quant codebooks (src/lowmem/iq_grids.rs: fitted tables, not formulas). They are handed in by the caller,
+// never written out here: 0 iq2xxs u64[256], 1 iq2xs u64[512], 2 iq2s u64[1024], 3 iq3xxs u32[256], 4 iq3s u32[512],
+// 5 iq1s u64[2048]. A row of a codebook type decodes only after its table has been set.
+static std::vector<uint64_t> g_grid64[6];
+static const size_t kGridLen[6] = {256, 512, 1024, 256, 512, 2048};
+ORACLE_API int lokal_ref_set_iq_grid(int which, const void* table, size_t entries) {
+    if (which < 0 || which > 5 || !table || entries != kGridLen[which]) return -1;
+    g_grid64[which].resize(entries);
+    const bool wide = which != 3 && which != 4;
+    for (size_t i = 0; i < entries; i++)
+        g_grid64[which][i] = wide ? static_cast<const uint64_t*>(table)[i] : static_cast<const uint32_t*>(table)[i];
+    return 0;
+}
+static inline const uint64_t* iq_grid(int which) { return g_grid64[which].empty() ? nullptr : g_grid64[which].data(); }
+// ksigns_iq2xs[i]: i with bit 7 set so that the byte has even parity (src/lowmem/iq_grids.rs:12-22 holds the
+// same 128 values as data; this is the rule they follow).
+static inline uint8_t ksigns_iq2xs(unsigned i) { return (uint8_t)(i | ((__builtin_popcount(i) & 1u) << 7)); }
 
 // sizeof(block_*) of ggml, as src/gguf/dequant.rs:94-114 lists them.
 ORACLE_API size_t lokal_ref_blk_bytes(uint32_t ty) {
@@ -396,6 +417,13 @@ ORACLE_API size_t lokal_ref_blk_bytes(uint32_t ty) {
         case GGML_Q4_K: return 2 + 2 + 12 + 128;
         case GGML_Q5_K: return 2 + 2 + 12 + 32 + 128;
         case GGML_Q6_K: return 128 + 64 + 16 + 2;
+        case GGML_IQ1_S: return 2 + 32 + 16;
+        case GGML_IQ1_M: return 32 + 16 + 8;
+        case GGML_IQ2_XXS: return 2 + 64;
+        case GGML_IQ2_XS: return 2 + 64 + 8;
+        case GGML_IQ2_S: return 2 + 64 + 8 + 8;
+        case GGML_IQ3_XXS: return 2 + 64 + 32;
+        case GGML_IQ3_S: return 2 + 64 + 8 + 32 + 4;
         default: return 0;
     }
 }
@@ -505,7 +533,160 @@ ORACLE_API int lokal_ref_dequant_row(uint32_t ty, const uint8_t* src, size_t src
                 }
             }
             return 0;
-        case GGML_IQ4_NL:  // src/gguf/dequant.rs:405-415: f16 d, nibbles index the 16-entry codebook
+        // ---- codebook types: 256-element super-blocks of eight 32-element groups; a group is four runs of eight
+        // values, each run one codebook entry (IQ1 / IQ2: eight bytes of a u64) or two (IQ3: four bytes of a u32).
+        case GGML_IQ1_S: {  // src/gguf/dequant.rs:255-270: d | qs[32] | qh[8 x u16]; value = dl * (grid + delta)
+            const uint64_t* grid = iq_grid(5);
+            if (!grid) return -3;
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 50;
+                const float d = f16_bits_at(blk, 0);
+                float* y = out + b * 256;
+                for (size_t ib = 0; ib < 8; ib++) {
+                    const unsigned qh = (unsigned)blk[34 + 2 * ib] | ((unsigned)blk[35 + 2 * ib] << 8);
+                    const float dl = d * (float)(2 * ((qh >> 12) & 7) + 1);
+                    const float delta = (qh & 0x8000) ? -0.125f : 0.125f;
+                    for (size_t l = 0; l < 4; l++) {
+                        const uint64_t g8 = grid[blk[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8)];
+                        for (size_t j = 0; j < 8; j++) y[32 * ib + 8 * l + j] = dl * ((float)(int8_t)(g8 >> (8 * j)) + delta);
+                    }
+                }
+            }
+            return 0;
+        }
+        case GGML_IQ1_M: {  // src/gguf/dequant.rs:274-293: qs[32] | qh[16] | scales[4 x u16]; the f16 d is spread over the scales' top nibbles
+            const uint64_t* grid = iq_grid(5);
+            if (!grid) return -3;
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 56;
+                unsigned sc[4];
+                for (size_t k = 0; k < 4; k++) sc[k] = (unsigned)blk[48 + 2 * k] | ((unsigned)blk[49 + 2 * k] << 8);
+                const float d = f16_to_f32((uint16_t)((sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0) | ((sc[2] >> 4) & 0x0f00) | (sc[3] & 0xf000)));
+                float* y = out + b * 256;
+                for (size_t ib = 0; ib < 8; ib++) {
+                    for (size_t l = 0; l < 4; l++) {
+                        const unsigned shift = 6 * (ib % 2) + (l < 2 ? 0 : 3);
+                        const float dl = d * (float)(2 * ((sc[ib / 2] >> shift) & 7) + 1);
+                        const unsigned qh = blk[32 + 2 * ib + (l >> 1)];
+                        const bool even = (l % 2) == 0;
+                        const uint64_t g8 = grid[blk[4 * ib + l] | ((qh << (even ? 8 : 4)) & 0x700)];
+                        const float delta = (qh & (even ? 0x08u : 0x80u)) ? -0.125f : 0.125f;
+                        for (size_t j = 0; j < 8; j++) y[32 * ib + 8 * l + j] = dl * ((float)(int8_t)(g8 >> (8 * j)) + delta);
+                    }
+                }
+            }
+            return 0;
+        }
+        case GGML_IQ2_XXS: {  // src/gguf/dequant.rs:295-312: d | 8 x (4 grid bytes, u32 of 4 x 7 sign bits + 4-bit scale)
+            const uint64_t* grid = iq_grid(0);
+            if (!grid) return -3;
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 66;
+                const float d = f16_bits_at(blk, 0);
+                float* y = out + b * 256;
+                for (size_t ib = 0; ib < 8; ib++) {
+                    const uint8_t* q = blk + 2 + 8 * ib;
+                    const uint32_t a1 = (uint32_t)q[4] | ((uint32_t)q[5] << 8) | ((uint32_t)q[6] << 16) | ((uint32_t)q[7] << 24);
+                    const float db = d * (0.5f + (float)(a1 >> 28)) * 0.25f;
+                    for (size_t l = 0; l < 4; l++) {
+                        const uint8_t signs = ksigns_iq2xs((a1 >> (7 * l)) & 127);
+                        const uint64_t g8 = grid[q[l]];
+                        for (size_t j = 0; j < 8; j++)
+                            y[32 * ib + 8 * l + j] = db * (float)((g8 >> (8 * j)) & 0xFF) * ((signs >> j) & 1 ? -1.0f : 1.0f);
+                    }
+                }
+            }
+            return 0;
+        }
+        case GGML_IQ2_XS: {  // src/gguf/dequant.rs:314-334: d | qs[32 x u16: 9-bit grid index, 7-bit sign selector] | scales[8]
+            const uint64_t* grid = iq_grid(1);
+            if (!grid) return -3;
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 74;
+                const float d = f16_bits_at(blk, 0);
+                float* y = out + b * 256;
+                for (size_t ib = 0; ib < 8; ib++) {
+                    const uint8_t sc = blk[66 + ib];
+                    for (size_t l = 0; l < 4; l++) {
+                        const float db = d * (0.5f + (float)(l < 2 ? (sc & 0xF) : (sc >> 4))) * 0.25f;
+                        const unsigned qv = (unsigned)blk[2 + 2 * (4 * ib + l)] | ((unsigned)blk[3 + 2 * (4 * ib + l)] << 8);
+                        const uint8_t signs = ksigns_iq2xs(qv >> 9);
+                        const uint64_t g8 = grid[qv & 511];
+                        for (size_t j = 0; j < 8; j++)
+                            y[32 * ib + 8 * l + j] = db * (float)((g8 >> (8 * j)) & 0xFF) * ((signs >> j) & 1 ? -1.0f : 1.0f);
+                    }
+                }
+            }
+            return 0;
+        }
+        case GGML_IQ2_S: {  // src/gguf/dequant.rs:336-352: d | qs[32 grid bytes + 32 sign bytes] | qh[8] | scales[8]
+            const uint64_t* grid = iq_grid(2);
+            if (!grid) return -3;
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 82;
+                const float d = f16_bits_at(blk, 0);
+                float* y = out + b * 256;
+                for (size_t ib = 0; ib < 8; ib++) {
+                    const uint8_t sc = blk[74 + ib];
+                    const unsigned qh = blk[66 + ib];
+                    for (size_t l = 0; l < 4; l++) {
+                        const float db = d * (0.5f + (float)(l < 2 ? (sc & 0xF) : (sc >> 4))) * 0.25f;
+                        const uint64_t g8 = grid[blk[2 + 4 * ib + l] | ((qh << (8 - 2 * l)) & 0x300)];
+                        const uint8_t signs = blk[2 + 32 + 4 * ib + l];
+                        for (size_t j = 0; j < 8; j++)
+                            y[32 * ib + 8 * l + j] = db * (float)((g8 >> (8 * j)) & 0xFF) * ((signs >> j) & 1 ? -1.0f : 1.0f);
+                    }
+                }
+            }
+            return 0;
+        }
+        case GGML_IQ3_XXS: {  // src/gguf/dequant.rs:354-374: d | qs[64 grid bytes] | 8 x u32 (4 x 7 sign bits + 4-bit scale)
+            const uint64_t* grid = iq_grid(3);
+            if (!grid) return -3;
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 98;
+                const float d = f16_bits_at(blk, 0);
+                float* y = out + b * 256;
+                for (size_t ib = 0; ib < 8; ib++) {
+                    const uint8_t* s = blk + 66 + 4 * ib;
+                    const uint32_t aux = (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+                    const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+                    for (size_t l = 0; l < 4; l++) {
+                        const uint8_t signs = ksigns_iq2xs((aux >> (7 * l)) & 127);
+                        for (size_t hf = 0; hf < 2; hf++) {
+                            const uint64_t g4 = grid[blk[2 + 8 * ib + 2 * l + hf]];
+                            for (size_t j = 0; j < 4; j++)
+                                y[32 * ib + 8 * l + 4 * hf + j] = db * (float)((g4 >> (8 * j)) & 0xFF) * ((signs >> (4 * hf + j)) & 1 ? -1.0f : 1.0f);
+                        }
+                    }
+                }
+            }
+            return 0;
+        }
+        case GGML_IQ3_S: {  // src/gguf/dequant.rs:376-394: d | qs[64] | qh[8] | signs[32] | scales[4]; qh gives a ninth index bit
+            const uint64_t* grid = iq_grid(4);
+            if (!grid) return -3;
+            for (size_t b = 0; b < n / 256; b++) {
+                const uint8_t* blk = src + b * 110;
+                const float d = f16_bits_at(blk, 0);
+                float* y = out + b * 256;
+                for (size_t g = 0; g < 8; g++) {
+                    const uint8_t scb = blk[106 + g / 2];
+                    const float db = d * (float)(1 + 2 * (unsigned)(g % 2 == 0 ? (scb & 0xF) : (scb >> 4)));
+                    const unsigned qh = blk[66 + g];
+                    for (size_t l = 0; l < 4; l++) {
+                        const uint8_t signs = blk[74 + 4 * g + l];
+                        for (size_t hf = 0; hf < 2; hf++) {
+                            const uint64_t g4 = grid[blk[2 + 8 * g + 2 * l + hf] | ((qh << (8 - 2 * l - hf)) & 256)];
+                            for (size_t j = 0; j < 4; j++)
+                                y[32 * g + 8 * l + 4 * hf + j] = db * (float)((g4 >> (8 * j)) & 0xFF) * ((signs >> (4 * hf + j)) & 1 ? -1.0f : 1.0f);
+                        }
+                    }
+                }
+            }
+            return 0;
+        }
+        case GGML_IQ4_NL:  // src/gguf/dequant.rs:396-409: f16 d, nibbles index the 16-entry codebook
             for (size_t b = 0; b < n / 32; b++) {
                 const uint8_t* blk = src + b * 18;
                 float d = f16_bits_at(blk, 0);
@@ -517,7 +698,7 @@ ORACLE_API int lokal_ref_dequant_row(uint32_t ty, const uint8_t* src, size_t src
                 }
             }
             return 0;
-        case GGML_IQ4_XS:  // src/gguf/dequant.rs:419-436: d | scales_h u16 | scales_l[4] | qs[128]; 6-bit scales biased by -32
+        case GGML_IQ4_XS:  // src/gguf/dequant.rs:410-425: d | scales_h u16 | scales_l[4] | qs[128]; 6-bit scales biased by -32
             for (size_t b = 0; b < n / 256; b++) {
                 const uint8_t* blk = src + b * 136;
                 float d = f16_bits_at(blk, 0);
@@ -534,7 +715,7 @@ ORACLE_API int lokal_ref_dequant_row(uint32_t ty, const uint8_t* src, size_t src
                 }
             }
             return 0;
-        case GGML_Q2_K:  // src/gguf/dequant.rs:437-451: scales[16] | qs[64] | d | dmin; (d*sc)*q - dmin*min
+        case GGML_Q2_K:  // src/gguf/dequant.rs:426-440: scales[16] | qs[64] | d | dmin; (d*sc)*q - dmin*min
             for (size_t b = 0; b < n / 256; b++) {
                 const uint8_t* blk = src + b * 84;
                 float d = f16_bits_at(blk, 80), dmin = f16_bits_at(blk, 82);
@@ -554,7 +735,7 @@ ORACLE_API int lokal_ref_dequant_row(uint32_t ty, const uint8_t* src, size_t src
                 }
             }
             return 0;
-        case GGML_Q3_K:  // src/gguf/dequant.rs:457-473: hmask[32] | qs[64] | scales[12] | d; a CLEAR hmask bit subtracts 4
+        case GGML_Q3_K:  // src/gguf/dequant.rs:441-461 (scale shuffle :171-189): hmask[32] | qs[64] | scales[12] | d; a CLEAR hmask bit subtracts 4
             for (size_t b = 0; b < n / 256; b++) {
                 const uint8_t* blk = src + b * 110;
                 float d_all = f16_bits_at(blk, 108);
@@ -730,8 +911,13 @@ ORACLE_API int lokal_ref_adversarial_rows(uint32_t ty, size_t n_blocks, size_t n
                 lcg = lcg * 1664525u + 1013904223u;
                 b[i] = (uint8_t)(lcg >> 16);
             }
-            b[d_off] = scale_bytes[variant][0];
-            b[d_off + 1] = scale_bytes[variant][1];
+            if (ty == GGML_IQ1_M) {  // no d field: the f16 goes in through the top nibbles of the four scale u16s
+                const unsigned bits = (unsigned)scale_bytes[variant][0] | ((unsigned)scale_bytes[variant][1] << 8);
+                for (int k = 0; k < 4; k++) b[49 + 2 * k] = (uint8_t)((b[49 + 2 * k] & 0x0F) | (((bits >> (4 * k)) & 0x0F) << 4));
+            } else {
+                b[d_off] = scale_bytes[variant][0];
+                b[d_off + 1] = scale_bytes[variant][1];
+            }
             if (dmin_off >= 0) {
                 b[dmin_off] = scale_bytes[3 - variant + 1][0];
                 b[dmin_off + 1] = scale_bytes[3 - variant + 1][1];
@@ -755,6 +941,16 @@ ORACLE_API int lokal_ref_adversarial_rows(uint32_t ty, size_t n_blocks, size_t n
                     std::memset(b, 0xFF, 192);
                     std::memset(b + 192, 0x80, 16);  // scales = -128
                     break;
+                // codebook types: grid indices stay random, the max case drives scales and signs
+                case GGML_IQ3_XXS: std::memset(b + 66, 0xFF, 32); break;
+                case GGML_IQ2_XXS:
+                    for (int g = 0; g < 8; g++) b[2 + 8 * g + 7] = 0xFF;  // top nibble of each group's second u32 is the scale
+                    break;
+                case GGML_IQ2_XS: std::memset(b + 66, 0xFF, 8); break;
+                case GGML_IQ1_S: std::memset(b + 34, 0xFF, 16); break;  // qh: max scale, negative delta
+                case GGML_IQ1_M: std::memset(b + 32, 0xFF, 16); break;  // qh only; the scales carry the f16
+                case GGML_IQ2_S: std::memset(b + 34, 0xFF, 48); break;  // sign half of qs, qh, scales
+                case GGML_IQ3_S: std::memset(b + 66, 0xFF, 44); break;  // qh, signs, scales
                 default: break;
             }
         }

@@ -19,6 +19,9 @@ _SO = os.path.join(_HERE, "liblokal_oracle.so")
 F32, F16, Q8_0, Q4_K, BF16 = 0, 1, 8, 12, 30
 Q4_0, Q5_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 2, 6, 10, 11, 13, 14, 20, 23
 QUANT_TYPES = (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS)
+IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M = 16, 17, 18, 19, 21, 22, 29
+GRID_TYPES = (IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M)
+GRID_ORDER = ("iq2xxs", "iq2xs", "iq2s", "iq3xxs", "iq3s", "iq1s")  # index = the `which` of lokal_ref_set_iq_grid
 
 
 def build(force: bool = False) -> str:
@@ -64,6 +67,7 @@ def lib() -> C.CDLL:
             "lokal_ref_gated_output_norm": (None, [vp, vp, vp, sz, sz, f32]),
             "lokal_ref_attn_out_gate": (None, [vp, vp, sz]),
             "lokal_ref_split_q_gate": (None, [vp, vp, vp, sz, sz, sz]),
+            "lokal_ref_set_iq_grid": (C.c_int, [C.c_int, vp, sz]),
             "lokal_ref_blk_elems": (sz, [u32]),
             "lokal_ref_blk_bytes": (sz, [u32]),
             "lokal_ref_row_bytes": (sz, [u32, sz]),
@@ -252,6 +256,15 @@ def row_bytes(ty: int, n: int) -> int:
     return lib().lokal_ref_row_bytes(ty, n)
 
 
+def set_iq_grids(grids) -> None:
+    """Hands the i-quant codebooks (a mapping with the keys of GRID_ORDER) to the oracle; they are data of the
+    format, kept by the caller (src/lowmem/iq_grids.rs in the reference)."""
+    for which, key in enumerate(GRID_ORDER):
+        a = np.ascontiguousarray(grids[key])
+        if lib().lokal_ref_set_iq_grid(which, _p(a), a.size) != 0:
+            raise ValueError(f"codebook {key}: {a.size} entries of {a.dtype} is not what the format has")
+
+
 def dequant_row_ref(ty: int, src, n: int) -> np.ndarray:
     """gguf::dequant_row_ref(ty, src, out[n]); raises where the reference panics."""
     src = np.ascontiguousarray(src, dtype=np.uint8)
@@ -259,6 +272,8 @@ def dequant_row_ref(ty: int, src, n: int) -> np.ndarray:
     rc = lib().lokal_ref_dequant_row(ty, _p(src), src.size, _p(out), n)
     if rc == -1:
         raise ValueError(f"src/out size mismatch for ggml type {ty}")
+    if rc == -3:
+        raise ValueError(f"the codebook of ggml type {ty} has not been set (set_iq_grids)")
     if rc != 0:
         raise ValueError(f"ggml type {ty} is not on this path")
     return out

@@ -148,6 +148,119 @@ def q6_k(raw):
     return np.stack(parts, axis=2).astype(F32).reshape(-1)
 
 
+# ---- codebook types: take the i-quant grids as a mapping (keys iq2xxs, iq2xs, iq2s, iq3xxs, iq3s, iq1s) ----
+
+KSIGNS = np.array([i | ((bin(i).count("1") & 1) << 7) for i in range(128)], np.uint8)  # 7 bits + an even-parity bit
+
+
+def _grid_bytes(grid, idx, width, signed=False):
+    """Codebook entries grid[idx] split into `width` bytes, lowest first: shape idx.shape + (width,)."""
+    g = np.asarray(grid)[idx].astype(np.uint64)
+    by = ((g[..., None] >> (8 * np.arange(width, dtype=np.uint64))) & np.uint64(0xFF)).astype(np.uint8)
+    return (by.view(np.int8) if signed else by).astype(F32)
+
+
+def _sign_factors(sign_bytes):
+    """Bit j of each byte set -> -1 for value j of the run: shape sign_bytes.shape + (8,)."""
+    bits = (sign_bytes[..., None].astype(np.int32) >> np.arange(8)) & 1
+    return np.where(bits == 1, F32(-1), F32(1)).astype(F32)
+
+
+def _u32(b):
+    return np.ascontiguousarray(b).view("<u4")
+
+
+def iq2_xxs(raw, grids):
+    b = _blocks(raw, 66)
+    q = b[:, 2:].reshape(-1, 8, 8)                                  # per group: 4 grid bytes, then a u32
+    a1 = _u32(q[:, :, 4:8])[:, :, 0].astype(np.int64)
+    db = (_f16(b, 0)[:, None] * (F32(0.5) + (a1 >> 28).astype(F32))).astype(F32) * F32(0.25)
+    signs = KSIGNS[(a1[:, :, None] >> (7 * np.arange(4))) & 127]
+    g = _grid_bytes(grids["iq2xxs"], q[:, :, :4].astype(np.int64), 8)
+    return ((db[:, :, None, None] * g).astype(F32) * _sign_factors(signs)).astype(F32).reshape(-1)
+
+
+def _db_nibbles(d, sc):
+    nib = np.stack([sc & 15, sc & 15, sc >> 4, sc >> 4], axis=2).astype(F32)  # runs 0,1 use the low nibble, 2,3 the high
+    return (d[:, None, None] * (F32(0.5) + nib)).astype(F32) * F32(0.25)
+
+
+def iq2_xs(raw, grids):
+    b = _blocks(raw, 74)
+    qv = np.ascontiguousarray(b[:, 2:66]).view("<u2").reshape(-1, 8, 4).astype(np.int64)
+    db = _db_nibbles(_f16(b, 0), b[:, 66:74].astype(np.int32))
+    g = _grid_bytes(grids["iq2xs"], qv & 511, 8)
+    return ((db[..., None] * g).astype(F32) * _sign_factors(KSIGNS[qv >> 9])).astype(F32).reshape(-1)
+
+
+def iq2_s(raw, grids):
+    b = _blocks(raw, 82)
+    lo = b[:, 2:34].reshape(-1, 8, 4).astype(np.int64)
+    signs = b[:, 34:66].reshape(-1, 8, 4)
+    qh = b[:, 66:74].astype(np.int64)
+    db = _db_nibbles(_f16(b, 0), b[:, 74:82].astype(np.int32))
+    gi = lo | ((qh[:, :, None] << (8 - 2 * np.arange(4))) & 0x300)
+    g = _grid_bytes(grids["iq2s"], gi, 8)
+    return ((db[..., None] * g).astype(F32) * _sign_factors(signs)).astype(F32).reshape(-1)
+
+
+def iq3_xxs(raw, grids):
+    b = _blocks(raw, 98)
+    qs = b[:, 2:66].reshape(-1, 8, 4, 2).astype(np.int64)            # [group, run, half of the run]
+    aux = _u32(b[:, 66:98]).astype(np.int64)                        # [nb, 8]
+    db = (_f16(b, 0)[:, None] * (F32(0.5) + (aux >> 28).astype(F32))).astype(F32) * F32(0.5)
+    signs = KSIGNS[(aux[:, :, None] >> (7 * np.arange(4))) & 127]
+    g = _grid_bytes(grids["iq3xxs"], qs, 4).reshape(-1, 8, 4, 8)
+    return ((db[:, :, None, None] * g).astype(F32) * _sign_factors(signs)).astype(F32).reshape(-1)
+
+
+def iq3_s(raw, grids):
+    b = _blocks(raw, 110)
+    qs = b[:, 2:66].reshape(-1, 8, 4, 2).astype(np.int64)
+    qh = b[:, 66:74].astype(np.int64)
+    signs = b[:, 74:106].reshape(-1, 8, 4)
+    scb = b[:, 106:110].astype(np.int32)
+    sc = np.stack([scb & 15, scb >> 4], axis=2).reshape(-1, 8)       # group g: low nibble when g is even
+    db = (_f16(b, 0)[:, None] * (1 + 2 * sc).astype(F32)).astype(F32)
+    shift = 8 - 2 * np.arange(4)[:, None] - np.arange(2)[None, :]
+    gi = qs | ((qh[:, :, None, None] << shift) & 256)
+    g = _grid_bytes(grids["iq3s"], gi, 4).reshape(-1, 8, 4, 8)
+    return ((db[:, :, None, None] * g).astype(F32) * _sign_factors(signs)).astype(F32).reshape(-1)
+
+
+def iq1_s(raw, grids):
+    b = _blocks(raw, 50)
+    qs = b[:, 2:34].reshape(-1, 8, 4).astype(np.int64)
+    qh = np.ascontiguousarray(b[:, 34:50]).view("<u2").astype(np.int64)  # [nb, 8]
+    dl = (_f16(b, 0)[:, None] * (2 * ((qh >> 12) & 7) + 1).astype(F32)).astype(F32)
+    delta = np.where(qh & 0x8000, F32(-0.125), F32(0.125)).astype(F32)
+    gi = qs | (((qh[:, :, None] >> (3 * np.arange(4))) & 7) << 8)
+    g = _grid_bytes(grids["iq1s"], gi, 8, signed=True)
+    return (dl[:, :, None, None] * (g + delta[:, :, None, None]).astype(F32)).astype(F32).reshape(-1)
+
+
+def iq1_m(raw, grids):
+    b = _blocks(raw, 56)
+    qs = b[:, :32].reshape(-1, 8, 4).astype(np.int64)
+    qh = np.repeat(b[:, 32:48].reshape(-1, 8, 2), 2, axis=2).astype(np.int64)   # runs 0,1 share a byte, runs 2,3 the next
+    sc = np.ascontiguousarray(b[:, 48:56]).view("<u2").astype(np.int64)          # [nb, 4]
+    dbits = (sc[:, 0] >> 12) | ((sc[:, 1] >> 8) & 0x00F0) | ((sc[:, 2] >> 4) & 0x0F00) | (sc[:, 3] & 0xF000)
+    d = dbits.astype(np.uint16).view(np.float16).astype(F32)
+    ib, run = np.arange(8)[:, None], np.arange(4)[None, :]
+    shift = 6 * (ib % 2) + np.where(run < 2, 0, 3)
+    s = (np.repeat(sc, 2, axis=1)[:, :, None] >> shift) & 7           # group ib reads scale word ib // 2
+    dl = (d[:, None, None] * (2 * s + 1).astype(F32)).astype(F32)
+    even = (run % 2) == 0
+    gi = qs | ((qh << np.where(even, 8, 4)) & 0x700)
+    delta = np.where(qh & np.where(even, 0x08, 0x80), F32(-0.125), F32(0.125)).astype(F32)
+    g = _grid_bytes(grids["iq1s"], gi, 8, signed=True)
+    return (dl[..., None] * (g + delta[..., None]).astype(F32)).astype(F32).reshape(-1)
+
+
+GRID_DECODERS = {16: iq2_xxs, 17: iq2_xs, 18: iq3_xxs, 19: iq1_s, 21: iq3_s, 22: iq2_s, 29: iq1_m}
+GRID_NAMES = {16: "IQ2_XXS", 17: "IQ2_XS", 18: "IQ3_XXS", 19: "IQ1_S", 21: "IQ3_S", 22: "IQ2_S", 29: "IQ1_M"}
+GRID_BLOCK_BYTES = {16: 66, 17: 74, 18: 98, 19: 50, 21: 110, 22: 82, 29: 56}
+
 DECODERS = {2: q4_0, 6: q5_0, 8: q8_0, 10: q2_k, 11: q3_k, 12: q4_k, 13: q5_k, 14: q6_k, 20: iq4_nl, 23: iq4_xs}
 NAMES = {2: "Q4_0", 6: "Q5_0", 8: "Q8_0", 10: "Q2_K", 11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 20: "IQ4_NL", 23: "IQ4_XS"}
 

@@ -52,8 +52,10 @@ def test_enums_match_header_and_gguf_ids():
             assert getattr(capi, name[len("LOKAL_"):]) == int(val)
     assert (capi.F32, capi.F16, capi.Q8_0, capi.Q4_K, capi.BF16) == (0, 1, 8, 12, 30)  # src/gguf/dequant.rs:21-41
     for name, val in re.findall(r"LOKAL_(I?Q\d\w+) = (\d+)", HEADER):
-        assert getattr(capi, name) == int(val) and int(val) in capi.QUANT_TYPES
-    assert len(capi.QUANT_TYPES) == 10
+        assert getattr(capi, name) == int(val) and int(val) in capi.QUANT_TYPES + capi.GRID_TYPES
+    assert len(capi.QUANT_TYPES) == 10 and len(capi.GRID_TYPES) == 7
+    grids = dict(re.findall(r"LOKAL_GRID_(\w+) = (\d+)", HEADER))
+    assert [k.lower() for k, v in sorted(grids.items(), key=lambda kv: int(kv[1]))] == list(capi.GRID_ORDER)
 
 
 def test_block_geometry_matches_reference_table():
@@ -66,7 +68,11 @@ def test_block_geometry_matches_reference_table():
             14: (256, 210), 20: (32, 18), 23: (256, 136)}
     for ty, geom in want.items():
         assert (lokal_b200.blk_elems(ty), lokal_b200.blk_bytes(ty)) == geom
-    assert lokal_b200.blk_elems(16) == 0 and lokal_b200.row_bytes(16, 256) == 0  # IQ2_XXS: a codebook type, not covered
+    grid_types = {16: 66, 17: 74, 18: 98, 19: 50, 21: 110, 22: 82, 29: 56}  # the codebook types
+    for ty, bb in grid_types.items():
+        assert (lokal_b200.blk_elems(ty), lokal_b200.blk_bytes(ty)) == (256, bb)
+    for ty in (3, 7, 9, 15, 24, 28):  # Q4_1, Q5_1, Q8_1, Q8_K, I8, F64: refused by the reference too (src/gguf/dequant.rs:58-76)
+        assert lokal_b200.blk_elems(ty) == 0 and lokal_b200.row_bytes(ty, 256) == 0
 
 
 def test_shard_rows_partitions_every_row_once():

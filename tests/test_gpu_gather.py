@@ -164,7 +164,7 @@ def test_refusals(ctx, dev):
     ids = dev.put(np.zeros(2, np.uint32))
     out = dev.empty((2, 64), F32)
     for kw, status in [
-        (dict(ggml_type=16, dim=256), L.capi.ERR_UNSUPPORTED),   # IQ2_XXS: a codebook type, refused by name
+        (dict(ggml_type=3, dim=256), L.capi.ERR_UNSUPPORTED),    # Q4_1: refused by name, as the reference refuses it
         (dict(ggml_type=Q8_0, dim=48), L.capi.ERR_BAD_ARG),      # not whole blocks (src/gguf/container.rs:220-226)
         (dict(ggml_type=Q4_K, dim=896), L.capi.ERR_BAD_ARG),     # 3.5 super-blocks cannot exist
         (dict(ggml_type=Q8_0, dim=64, out_dtype=Q8_0), L.capi.ERR_UNSUPPORTED),

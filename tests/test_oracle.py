@@ -29,7 +29,7 @@ def test_block_size_table(oracle):
     for row in KATS["block_sizes"]["row_bytes"]:
         assert oracle.row_bytes(row["type"], row["n"]) == row["bytes"]
     assert oracle.row_bytes(oracle.Q8_0, 896) == 952
-    assert oracle.blk_elems(16) == 0  # IQ2_XXS: a codebook type outside this path
+    assert oracle.blk_elems(3) == 0  # Q4_1: refused by the reference too (src/gguf/dequant.rs:58)
 
 
 @pytest.mark.parametrize("key,ty", [("q8_0_hand_vector", 8), ("q4_k_hand_vector", 12)])
@@ -63,7 +63,7 @@ def test_size_mismatch_is_refused(oracle):
     with pytest.raises(ValueError):
         oracle.dequant_row_ref(8, np.zeros(33, np.uint8), 32)  # the reference panics (src/gguf/dequant.rs:192)
     with pytest.raises(ValueError):
-        oracle.dequant_row_ref(16, np.zeros(66, np.uint8), 256)
+        oracle.dequant_row_ref(3, np.zeros(20, np.uint8), 32)
 
 
 def test_dot_and_rmsnorm_reference_vectors(oracle):
