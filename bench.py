@@ -509,13 +509,17 @@ def gather_workload(args, rank, world, local_rank):
     variants = [("q8_0_f32", L.Q8_0, synth.C4_DIM_Q8, L.F32), ("q8_0_f16", L.Q8_0, synth.C4_DIM_Q8, L.F16),
                 ("q4_k_f32", L.Q4_K, synth.C4_DIM_Q4K, L.F32), ("q4_k_f16", L.Q4_K, synth.C4_DIM_Q4K, L.F16)]
     # the other block types of the gather, f32 out: 32-element blocks at the Q8_0 width, 256-element ones at the Q4_K width
-    for ty in L.QUANT_TYPES:
+    for ty in L.QUANT_TYPES + L.capi.GRID_TYPES:
         if ty not in (L.Q8_0, L.Q4_K):
             dim = synth.C4_DIM_Q8 if synth.QUANT_GEOMETRY[ty][0] == 32 else synth.C4_DIM_Q4K
             variants.append((synth.QUANT_NAMES[ty] + "_f32", ty, dim, L.F32))
     tables, kern = {}, {}
     O.build()
     threads = O.hardware_threads()
+    # the codebook types read the i-quant codebooks the caller hands over (the test fixture's copy of the format's tables)
+    grids = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests", "golden", "iq_grids.npz"))
+    ctx.set_iq_grids(grids)
+    O.set_iq_grids(grids)
     for name, ty, dim, odt in variants:
         if (ty, dim) not in tables:
             gen = {L.Q8_0: synth.q8_0_table, L.Q4_K: synth.q4_k_table}.get(ty)

@@ -401,13 +401,100 @@ __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned 
     }
 }
 
-// Codebook types in the staged kernel: the element decoder over the staged row.
+// Codebook types in the staged kernel. EPL consecutive elements are half a run (EPL = 4) or one run (EPL = 8): one
+// scale, one byte of signs (or one delta), and one 8-byte codebook entry (IQ1 / IQ2) or two 4-byte entries (IQ3),
+// fetched once. Same values and rounding order as dequant_grid_elem; a sign is applied by flipping the sign bit,
+// which is what multiplying by -1.0 does.
 template <int QT, int EPL>
 __device__ __forceinline__ void decode_grid_block(const unsigned char* row, unsigned e, const void* grid, float2 (&y)[EPL / 2]) {
-    const SharedBytes rd{row};
+    constexpr int W = EPL / 4;
+    constexpr float k2p23 = 8388608.0f;
+    constexpr bool kIq1 = QT == LOKAL_IQ1_S || QT == LOKAL_IQ1_M, kIq3 = QT == LOKAL_IQ3_XXS || QT == LOKAL_IQ3_S;
+    const unsigned i = e & 255, ib = i >> 5, l = (i >> 3) & 3, j0 = i & 7;
+    const unsigned long long* g64 = static_cast<const unsigned long long*>(grid);
+    const unsigned* g32 = static_cast<const unsigned*>(grid);
+    auto u16 = [](const unsigned char* p) { return static_cast<unsigned>(*reinterpret_cast<const unsigned short*>(p)); };
+    float scale, delta = 0.0f;
+    unsigned signs = 0, gi = 0, gi2 = 0;  // gi2: the second entry of a run (IQ3 only)
+    if constexpr (QT == LOKAL_IQ1_S) {
+        const unsigned char* b = row + (e >> 8) * 50;
+        const unsigned qh = u16(b + 34 + 2 * ib);
+        scale = __fmul_rn(lds_f16(b), static_cast<float>(2 * ((qh >> 12) & 7u) + 1));
+        delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+        gi = b[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7u) << 8);
+    } else if constexpr (QT == LOKAL_IQ1_M) {
+        const unsigned char* b = row + (e >> 8) * 56;
+        const unsigned s01 = lds_u32(b + 48), s23 = lds_u32(b + 52);  // 56-byte blocks keep the scale words 4-byte aligned
+        const unsigned bits = ((s01 >> 12) & 0xFu) | ((s01 >> 24) & 0x00F0u) | ((s23 >> 4) & 0x0F00u) | ((s23 >> 16) & 0xF000u);
+        const unsigned sw = ((ib & 4) ? s23 : s01) >> ((ib & 2) ? 16 : 0);
+        scale = __fmul_rn(__half2float(__ushort_as_half(static_cast<unsigned short>(bits))),
+                          static_cast<float>(2 * ((sw >> (6 * (ib & 1) + (l < 2 ? 0 : 3))) & 7u) + 1));
+        const unsigned qh = b[32 + 2 * ib + (l >> 1)];
+        const bool even = (l & 1) == 0;
+        gi = b[4 * ib + l] | ((qh << (even ? 8 : 4)) & 0x700u);
+        delta = (qh & (even ? 0x08u : 0x80u)) ? -0.125f : 0.125f;
+    } else if constexpr (QT == LOKAL_IQ2_XXS) {
+        const unsigned char* b = row + (e >> 8) * 66;
+        const unsigned a1 = lds_u32_a2(b + 2 + 8 * ib + 4);
+        scale = __fmul_rn(__fmul_rn(lds_f16(b), __fadd_rn(0.5f, static_cast<float>(a1 >> 28))), 0.25f);
+        signs = ksigns_iq2xs((a1 >> (7 * l)) & 127u);
+        gi = b[2 + 8 * ib + l];
+    } else if constexpr (QT == LOKAL_IQ2_XS || QT == LOKAL_IQ2_S) {
+        constexpr unsigned BB = QT == LOKAL_IQ2_XS ? 74 : 82, SC = QT == LOKAL_IQ2_XS ? 66 : 74;
+        const unsigned char* b = row + (e >> 8) * BB;
+        const unsigned sc = b[SC + ib];
+        scale = __fmul_rn(__fmul_rn(lds_f16(b), __fadd_rn(0.5f, static_cast<float>(l < 2 ? (sc & 15u) : (sc >> 4)))), 0.25f);
+        if constexpr (QT == LOKAL_IQ2_XS) {
+            const unsigned qv = u16(b + 2 + 2 * (4 * ib + l));
+            gi = qv & 511u;
+            signs = ksigns_iq2xs(qv >> 9);
+        } else {
+            gi = b[2 + 4 * ib + l] | ((static_cast<unsigned>(b[66 + ib]) << (8 - 2 * l)) & 0x300u);
+            signs = b[34 + 4 * ib + l];
+        }
+    } else if constexpr (QT == LOKAL_IQ3_XXS) {
+        const unsigned char* b = row + (e >> 8) * 98;
+        const unsigned aux = lds_u32_a2(b + 66 + 4 * ib);
+        scale = __fmul_rn(__fmul_rn(lds_f16(b), __fadd_rn(0.5f, static_cast<float>(aux >> 28))), 0.5f);
+        signs = ksigns_iq2xs((aux >> (7 * l)) & 127u);
+        gi = b[2 + 8 * ib + 2 * l];
+        gi2 = b[2 + 8 * ib + 2 * l + 1];
+    } else {  // LOKAL_IQ3_S
+        const unsigned char* b = row + (e >> 8) * 110;
+        const unsigned scb = b[106 + (ib >> 1)], qh = b[66 + ib];
+        scale = __fmul_rn(lds_f16(b), static_cast<float>(1 + 2 * ((ib & 1) ? (scb >> 4) : (scb & 15u))));
+        signs = b[74 + 4 * ib + l];
+        gi = b[2 + 8 * ib + 2 * l] | ((qh << (8 - 2 * l)) & 256u);
+        gi2 = b[2 + 8 * ib + 2 * l + 1] | ((qh << (7 - 2 * l)) & 256u);
+    }
+    unsigned word[2];  // values 0..3 and 4..7 of the run, one byte each
+    if constexpr (kIq3) {
+        if (W == 2 || j0 == 0) word[0] = __ldg(g32 + gi);
+        if (W == 2 || j0 != 0) word[1] = __ldg(g32 + gi2);
+    } else {
+        const unsigned long long entry = __ldg(g64 + gi);
+        word[0] = static_cast<unsigned>(entry);
+        word[1] = static_cast<unsigned>(entry >> 32);
+    }
+    const float2 sc2 = both(scale);
 #pragma unroll
-    for (int k = 0; k < EPL / 2; k++)
-        y[k] = make_float2(dequant_grid_elem<QT>(rd, grid, e + 2 * k), dequant_grid_elem<QT>(rd, grid, e + 2 * k + 1));
+    for (int w = 0; w < W; w++) {
+        const unsigned first = W == 2 ? 4u * w : j0;  // index in the run of this word's first value
+        const unsigned bytes = (W == 2) ? word[w] : (j0 ? word[1] : word[0]);
+        float2 f0, f1;
+        if constexpr (kIq1) {  // signed codebook bytes: dl * (g + delta)
+            bytes_to_pairs(bytes ^ 0x80808080u, both(-(k2p23 + 128.0f)), f0, f1);
+            y[2 * w] = mul2(sc2, add2(f0, both(delta)));
+            y[2 * w + 1] = mul2(sc2, add2(f1, both(delta)));
+        } else {  // (db * g) * (+-1)
+            bytes_to_pairs(bytes, both(-k2p23), f0, f1);
+            f0 = mul2(sc2, f0);
+            f1 = mul2(sc2, f1);
+            const unsigned sg = signs >> first;
+            y[2 * w] = make_float2(__uint_as_float(__float_as_uint(f0.x) ^ ((sg & 1u) << 31)), __uint_as_float(__float_as_uint(f0.y) ^ ((sg & 2u) << 30)));
+            y[2 * w + 1] = make_float2(__uint_as_float(__float_as_uint(f1.x) ^ ((sg & 4u) << 29)), __uint_as_float(__float_as_uint(f1.y) ^ ((sg & 8u) << 28)));
+        }
+    }
 }
 
 // Calls f(std::integral_constant<int, type>) for a quantised table type.

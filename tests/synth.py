@@ -138,8 +138,12 @@ def q4_k_table(vocab: int, dim: int, seed: int) -> np.ndarray:
 
 # (block elements, block bytes, offsets of the f16 scale fields) per GGUF type id
 QUANT_GEOMETRY = {2: (32, 18, (0,)), 6: (32, 22, (0,)), 8: (32, 34, (0,)), 10: (256, 84, (80, 82)), 11: (256, 110, (108,)),
-                  12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 20: (32, 18, (0,)), 23: (256, 136, (0,))}
-QUANT_NAMES = {2: "q4_0", 6: "q5_0", 8: "q8_0", 10: "q2_k", 11: "q3_k", 12: "q4_k", 13: "q5_k", 14: "q6_k", 20: "iq4_nl", 23: "iq4_xs"}
+                  12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 20: (32, 18, (0,)), 23: (256, 136, (0,)),
+                  # codebook types; IQ1_M (29) has no f16 field, its scale sits in four nibbles
+                  16: (256, 66, (0,)), 17: (256, 74, (0,)), 18: (256, 98, (0,)), 19: (256, 50, (0,)), 21: (256, 110, (0,)),
+                  22: (256, 82, (0,)), 29: (256, 56, ())}
+QUANT_NAMES = {2: "q4_0", 6: "q5_0", 8: "q8_0", 10: "q2_k", 11: "q3_k", 12: "q4_k", 13: "q5_k", 14: "q6_k", 20: "iq4_nl", 23: "iq4_xs",
+               16: "iq2_xxs", 17: "iq2_xs", 18: "iq3_xxs", 19: "iq1_s", 21: "iq3_s", 22: "iq2_s", 29: "iq1_m"}
 
 
 def quant_table(ty: int, vocab: int, dim: int, seed: int) -> np.ndarray:
@@ -151,6 +155,10 @@ def quant_table(ty: int, vocab: int, dim: int, seed: int) -> np.ndarray:
     blocks = rng.integers(0, 256, (nb, bb), dtype=np.uint8)
     for off in offs:
         blocks[:, off:off + 2] = _abs_normal_f16_bytes(rng, nb, 0.01)
+    if ty == 29:  # the f16 scale spread over the top nibbles of bytes 49, 51, 53, 55
+        bits = _abs_normal_f16_bytes(rng, nb, 0.01).view(np.uint16).reshape(nb)
+        for k in range(4):
+            blocks[:, 49 + 2 * k] = (blocks[:, 49 + 2 * k] & 0x0F) | (((bits >> (4 * k)) & 0x0F) << 4).astype(np.uint8)
     return blocks.reshape(-1)
 
 
