@@ -85,10 +85,15 @@ struct QkArgs {
 };
 
 // ---------------------------------------------------------------------------
-// Fast path: rot_dim == head_dim == HD, 16-byte aligned rows.
+// Fast path: head_dim == HD, rot_dim == ROT (ROT == HD, or partial RoPE with
+// ROT < HD as qwen35 has it: 64 of 256), 16-byte aligned rows.
 //
-// Lane mapping: a group of LPH lanes owns one head; each lane holds N elements
-// of the head's first half and the N partner elements of the second half, so a
+// Lane mapping: a group of LPH lanes owns one head and each lane holds two
+// 16-byte vectors of it. The first ROT/(2N) lanes of the group hold N elements
+// of the rotated prefix's first half and their N partners (i, i + ROT/2); the
+// remaining lanes hold two consecutive vectors of the unrotated tail, which
+// take part in the bias add and the norm and are stored as they come out of
+// those (bit-identical to the reference's untouched tail on f32 rows). A
 // warp covers HPW heads per pass and the q heads followed by the k heads of a
 // row are "head slots" 0 .. n_q+n_kv-1. The row's cos/sin live in registers;
 // the per-head norm weights are staged once per CTA in shared memory as f32,
@@ -100,56 +105,74 @@ struct QkArgs {
 // applied while the reduction's shuffles are still in flight, the scale is
 // multiplied in last, and one product of each rotated pair rides in an FMA.
 // ---------------------------------------------------------------------------
-template <typename T, int HD, bool NORM, bool BIAS>
+template <typename T, int HD, int ROT, bool NORM, bool BIAS>
 struct RopeRow {
     static constexpr int N = VecOf<T>::N;
     static constexpr int P = N / 2;        // f32 pairs per 16-byte vector
     static constexpr int HALF = HD / 2;
     static constexpr int LPH = HALF / N;   // lanes per head
     static constexpr int HPW = 32 / LPH;   // heads per warp pass
+    static constexpr int RL = ROT / (2 * N);  // lanes of a group that hold rotated pairs
+    static constexpr bool FULL = ROT == HD;
     static_assert(LPH >= 1 && LPH <= 32 && (LPH & (LPH - 1)) == 0, "head must map onto a power-of-two lane group");
+    static_assert(ROT <= HD && RL >= 1 && ROT % (2 * N) == 0, "the rotated prefix must be whole lanes");
 
     float2 cs[P], sn[P], nsn[P];
     T* q_dst;
     T* k_dst;  // pre-shifted by -n_q heads so that both are indexed by the head slot
     const float* w_s;
     unsigned sub, hsel, slots;
+    unsigned lo_off, hi_off;  // element offsets inside a head of this lane's two vectors
+    bool rot_lane;            // this lane holds a rotated pair (always, when ROT == HD)
+
+    // The two vectors of lane `s` of a group: a rotated pair, or two consecutive vectors of the tail.
+    static __device__ __forceinline__ unsigned lo_of(unsigned s) { return (FULL || s < RL) ? s * N : ROT + (s - RL) * 2 * N; }
+    static __device__ __forceinline__ unsigned hi_of(unsigned s) { return (FULL || s < RL) ? ROT / 2 + s * N : ROT + (s - RL) * 2 * N + N; }
 
     __device__ __forceinline__ void init(const QkArgs& a, unsigned long long row, unsigned lane, const float* w_shared) {
         sub = lane % LPH;
         hsel = lane / LPH;
         slots = a.n_q + a.n_kv;
         w_s = w_shared;
-        const float* tr = a.cos_sin + row * HD + sub * N;
+        lo_off = lo_of(sub);
+        hi_off = hi_of(sub);
+        rot_lane = FULL || sub < RL;
+        if (rot_lane) {
+            const float* tr = a.cos_sin + row * ROT + sub * N;
 #pragma unroll
-        for (int j = 0; j < N / 4; j++) {
-            float2 t[2];
-            unpack16p<float>(ld_keep(tr + 4 * j), t);
-            cs[2 * j] = t[0];
-            cs[2 * j + 1] = t[1];
-            unpack16p<float>(ld_keep(tr + HALF + 4 * j), t);
-            sn[2 * j] = t[0];
-            sn[2 * j + 1] = t[1];
+            for (int j = 0; j < N / 4; j++) {
+                float2 t[2];
+                unpack16p<float>(ld_keep(tr + 4 * j), t);
+                cs[2 * j] = t[0];
+                cs[2 * j + 1] = t[1];
+                unpack16p<float>(ld_keep(tr + ROT / 2 + 4 * j), t);
+                sn[2 * j] = t[0];
+                sn[2 * j + 1] = t[1];
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < P; i++) cs[i] = sn[i] = make_float2(0.0f, 0.0f);
         }
 #pragma unroll
         for (int i = 0; i < P; i++) nsn[i] = make_float2(-sn[i].x, -sn[i].y);
         const long long k_shift = static_cast<long long>(a.n_q) * HD;
-        q_dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride + sub * N;
+        q_dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride + lo_off;
         k_dst = nullptr;
         if (a.n_kv) {
             const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
-            k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + sub * N - k_shift;
+            k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + lo_off - k_shift;
         }
     }
 
-    // Norm weights into shared memory: [q first half | q second half | k first half | k second half], each half in
-    // (j, lane, e) order; a missing weight vector is staged as ones. Called by every thread of the CTA.
+    // Norm weights into shared memory: [q first vectors | q second vectors | k first vectors | k second vectors] of
+    // the lanes, each block in (j, lane, e) order; a missing weight vector is staged as ones. Called by every thread
+    // of the CTA.
     static __device__ __forceinline__ void stage_weights(const QkArgs& a, float* w_shared) {
         for (unsigned i = threadIdx.x; i < 2u * HD; i += blockDim.x) {
-            const unsigned kind = i / HD, d = i % HD, half = d / HALF, r = d % HALF;
-            const unsigned lane_of = r / N, j = (r % N) / 4, e = r % 4;
+            const unsigned kind = i / HD, which = (i % HD) / HALF, lane_of = (i % HALF) / N, r = i % N;
+            const unsigned d = (which ? hi_of(lane_of) : lo_of(lane_of)) + r;  // element of the head this slot holds
             const void* src = kind ? a.k_norm_w : a.q_norm_w;
-            w_shared[kind * HD + half * HALF + (j * LPH + lane_of) * 4 + e] = src ? load_as_f32(src, a.w_dtype, d) : 1.0f;
+            w_shared[kind * HD + which * HALF + ((r / 4) * LPH + lane_of) * 4 + r % 4] = src ? load_as_f32(src, a.w_dtype, d) : 1.0f;
         }
     }
 
@@ -168,10 +191,10 @@ struct RopeRow {
         if (BIAS) {
             const void* bias = is_q ? a.q_bias : a.k_bias;
             if (bias && live) {
-                const size_t boff = static_cast<size_t>(is_q ? slot : slot - a.n_q) * HD + sub * N;
+                const size_t boff = static_cast<size_t>(is_q ? slot : slot - a.n_q) * HD;
                 float ba[N], bb[N];
-                load_w<N>(bias, a.w_dtype, boff, a.w_vec_ok, ba);
-                load_w<N>(bias, a.w_dtype, boff + HALF, a.w_vec_ok, bb);
+                load_w<N>(bias, a.w_dtype, boff + lo_off, a.w_vec_ok, ba);
+                load_w<N>(bias, a.w_dtype, boff + hi_off, a.w_vec_ok, bb);
 #pragma unroll
                 for (int i = 0; i < P; i++) {
                     va[i] = add2(va[i], make_float2(ba[2 * i], ba[2 * i + 1]));
@@ -222,6 +245,11 @@ struct RopeRow {
             float2 oa[P], ob[P];
 #pragma unroll
             for (int i = 0; i < P; i++) {
+                if (!FULL && !rot_lane) {  // the unrotated tail: out of the norm as it is
+                    oa[i] = (NORM && sizeof(T) == 2) ? mul2(va[i], s2) : va[i];
+                    ob[i] = (NORM && sizeof(T) == 2) ? mul2(vb[i], s2) : vb[i];
+                    continue;
+                }
                 // a*cos - b*sin written as a*cos + b*(-sin): the same bits
                 if (sizeof(T) == 2) {
                     oa[i] = fma2(va[i], cs[i], mul2(vb[i], nsn[i]));
@@ -237,18 +265,18 @@ struct RopeRow {
             }
             T* dst = (is_q ? q_dst : k_dst) + static_cast<size_t>(slot) * HD;
             *reinterpret_cast<uint4*>(dst) = pack16p<T>(oa);
-            *reinterpret_cast<uint4*>(dst + HALF) = pack16p<T>(ob);
+            *reinterpret_cast<uint4*>(dst + (hi_off - lo_off)) = pack16p<T>(ob);
         }
     }
 };
 
 // Register variant: one warp walks a range of head groups of one row; the loads of kRopeInFlight passes are issued
 // before the first is consumed. Used when a row is split over several warps (few rows) or is too large to stage.
-template <typename T, int HD, bool NORM, bool BIAS>
+template <typename T, int HD, int ROT, bool NORM, bool BIAS>
 __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const QkArgs a) {
     pdl_sync();
-    using R = RopeRow<T, HD, NORM, BIAS>;
-    constexpr int N = R::N, HALF = R::HALF, HPW = R::HPW;
+    using R = RopeRow<T, HD, ROT, NORM, BIAS>;
+    constexpr int HPW = R::HPW;
     __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
 
     const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -260,14 +288,14 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
     R r;
     r.init(a, row, threadIdx.x & 31u, w_s);
     // slot s of the row is at q_row + s*HD for s < n_q, at k_row + (s - n_q)*HD otherwise (second base pre-shifted)
-    const T* q_src = reinterpret_cast<const T*>(a.q) + row * a.q_stride + r.sub * N;
-    const T* k_src = reinterpret_cast<const T*>(a.k) + row * a.k_stride + r.sub * N - static_cast<long long>(a.n_q) * HD;
+    const T* q_src = reinterpret_cast<const T*>(a.q) + row * a.q_stride + r.lo_off;
+    const T* k_src = reinterpret_cast<const T*>(a.k) + row * a.k_stride + r.lo_off - static_cast<long long>(a.n_q) * HD;
     auto fetch = [&](unsigned c, uint4& lo, uint4& hi) {
         const unsigned slot = c * HPW + r.hsel;
         if (c < end_chunk && slot < r.slots) {
             const T* src = (slot < a.n_q ? q_src : k_src) + static_cast<size_t>(slot) * HD;
             lo = ld_stream(src);
-            hi = ld_stream(src + HALF);
+            hi = ld_stream(src + (r.hi_off - r.lo_off));
         }
     };
     unsigned c = first_chunk;
@@ -296,11 +324,11 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
 // two bulk asynchronous copies that complete on an mbarrier, so all of the row's bytes are in flight at once without
 // holding registers; the warp then walks the head groups out of shared memory and stores results straight to
 // global memory. Same lane mapping, arithmetic and results as qk_rope_kernel.
-template <typename T, int HD, bool NORM, bool BIAS>
+template <typename T, int HD, int ROT, bool NORM, bool BIAS>
 __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) {
     pdl_launch();
-    using R = RopeRow<T, HD, NORM, BIAS>;
-    constexpr int N = R::N, HALF = R::HALF, HPW = R::HPW;
+    using R = RopeRow<T, HD, ROT, NORM, BIAS>;
+    constexpr int HPW = R::HPW;
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
     const unsigned warps_per_cta = blockDim.x >> 5, warp_in_cta = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -336,7 +364,7 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
         mbar_wait_bounded(bar, 0);  // one more bounded chance for the copies in flight to land before leaving
         return;
     }
-    const T* srow = reinterpret_cast<const T*>(stage) + r.sub * N;
+    const T* srow = reinterpret_cast<const T*>(stage) + r.lo_off;
 #pragma unroll 2
     for (unsigned c = 0; c < a.chunks; c++) {
         const unsigned slot = c * HPW + r.hsel;
@@ -344,7 +372,7 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
         uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
         if (live) {
             lo = *reinterpret_cast<const uint4*>(srow + static_cast<size_t>(slot) * HD);
-            hi = *reinterpret_cast<const uint4*>(srow + static_cast<size_t>(slot) * HD + HALF);
+            hi = *reinterpret_cast<const uint4*>(srow + static_cast<size_t>(slot) * HD + (r.hi_off - r.lo_off));
         }
         r.pass(a, slot, live, lo, hi);
     }
@@ -415,7 +443,11 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     constexpr unsigned N = VecOf<T>::N;
     const unsigned slots = a.n_q + a.n_kv;
     if (slots == 0 || a.rows == 0) return LOKAL_OK;
-    const bool fast = fast_ok && a.rot_dim == a.head_dim && (a.head_dim == 64 || a.head_dim == 128 || a.head_dim == 256);
+    // (head_dim, rot_dim) pairs with a lane-mapped kernel: full rotation at 64 / 128 / 256, and the partial rotations
+    // 64 of 256 (qwen35) and 64 of 128.
+    const unsigned geom = a.head_dim * 1024u + a.rot_dim;
+    const bool fast = fast_ok && (geom == 64u * 1024u + 64u || geom == 128u * 1024u + 128u || geom == 256u * 1024u + 256u ||
+                                  geom == 256u * 1024u + 64u || geom == 128u * 1024u + 64u);
     if (!fast) {
         const unsigned long long warps = a.rows * slots;
         const unsigned long long blocks = (warps + 7) / 8;
@@ -460,33 +492,37 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
         while (swpc > 1 && 128u + swpc * a.stage_bytes > 48u * 1024u) swpc /= 2;
         const unsigned sgrid = static_cast<unsigned>((a.rows + swpc - 1) / swpc);
         const size_t smem = 128u + static_cast<size_t>(swpc) * a.stage_bytes;
-#define LOKAL_ROPE_LAUNCH_STAGED(HD_)                                                                      \
-    do {                                                                                                   \
-        if (norm && bias) launch_k(qk_rope_staged_kernel<T, HD_, true, true>, sgrid, swpc * 32, smem, s, a);   \
-        else if (norm) launch_k(qk_rope_staged_kernel<T, HD_, true, false>, sgrid, swpc * 32, smem, s, a);     \
-        else if (bias) launch_k(qk_rope_staged_kernel<T, HD_, false, true>, sgrid, swpc * 32, smem, s, a);     \
-        else launch_k(qk_rope_staged_kernel<T, HD_, false, false>, sgrid, swpc * 32, smem, s, a);              \
+#define LOKAL_ROPE_LAUNCH_STAGED(HD_, ROT_)                                                                      \
+    do {                                                                                                         \
+        if (norm && bias) launch_k(qk_rope_staged_kernel<T, HD_, ROT_, true, true>, sgrid, swpc * 32, smem, s, a);   \
+        else if (norm) launch_k(qk_rope_staged_kernel<T, HD_, ROT_, true, false>, sgrid, swpc * 32, smem, s, a);     \
+        else if (bias) launch_k(qk_rope_staged_kernel<T, HD_, ROT_, false, true>, sgrid, swpc * 32, smem, s, a);     \
+        else launch_k(qk_rope_staged_kernel<T, HD_, ROT_, false, false>, sgrid, swpc * 32, smem, s, a);              \
     } while (0)
-        switch (a.head_dim) {
-            case 64: LOKAL_ROPE_LAUNCH_STAGED(64); break;
-            case 128: LOKAL_ROPE_LAUNCH_STAGED(128); break;
-            default: LOKAL_ROPE_LAUNCH_STAGED(256); break;
+        switch (geom) {
+            case 64u * 1024u + 64u: LOKAL_ROPE_LAUNCH_STAGED(64, 64); break;
+            case 128u * 1024u + 128u: LOKAL_ROPE_LAUNCH_STAGED(128, 128); break;
+            case 128u * 1024u + 64u: LOKAL_ROPE_LAUNCH_STAGED(128, 64); break;
+            case 256u * 1024u + 64u: LOKAL_ROPE_LAUNCH_STAGED(256, 64); break;
+            default: LOKAL_ROPE_LAUNCH_STAGED(256, 256); break;
         }
 #undef LOKAL_ROPE_LAUNCH_STAGED
         LOKAL_CHECK_LAUNCH(ctx, "qk_rope_staged_kernel");
         return LOKAL_OK;
     }
-#define LOKAL_ROPE_LAUNCH(HD_)                                                               \
-    do {                                                                                     \
-        if (norm && bias) launch_k(qk_rope_kernel<T, HD_, true, true>, grid, cta, 0, s, a);        \
-        else if (norm) launch_k(qk_rope_kernel<T, HD_, true, false>, grid, cta, 0, s, a);          \
-        else if (bias) launch_k(qk_rope_kernel<T, HD_, false, true>, grid, cta, 0, s, a);          \
-        else launch_k(qk_rope_kernel<T, HD_, false, false>, grid, cta, 0, s, a);                   \
+#define LOKAL_ROPE_LAUNCH(HD_, ROT_)                                                               \
+    do {                                                                                           \
+        if (norm && bias) launch_k(qk_rope_kernel<T, HD_, ROT_, true, true>, grid, cta, 0, s, a);        \
+        else if (norm) launch_k(qk_rope_kernel<T, HD_, ROT_, true, false>, grid, cta, 0, s, a);          \
+        else if (bias) launch_k(qk_rope_kernel<T, HD_, ROT_, false, true>, grid, cta, 0, s, a);          \
+        else launch_k(qk_rope_kernel<T, HD_, ROT_, false, false>, grid, cta, 0, s, a);                   \
     } while (0)
-    switch (a.head_dim) {
-        case 64: LOKAL_ROPE_LAUNCH(64); break;
-        case 128: LOKAL_ROPE_LAUNCH(128); break;
-        default: LOKAL_ROPE_LAUNCH(256); break;
+    switch (geom) {
+        case 64u * 1024u + 64u: LOKAL_ROPE_LAUNCH(64, 64); break;
+        case 128u * 1024u + 128u: LOKAL_ROPE_LAUNCH(128, 128); break;
+        case 128u * 1024u + 64u: LOKAL_ROPE_LAUNCH(128, 64); break;
+        case 256u * 1024u + 64u: LOKAL_ROPE_LAUNCH(256, 64); break;
+        default: LOKAL_ROPE_LAUNCH(256, 256); break;
     }
 #undef LOKAL_ROPE_LAUNCH
     LOKAL_CHECK_LAUNCH(ctx, "qk_rope_kernel");

@@ -145,7 +145,7 @@ def test_reference_partial_rope_structure(ctx, dev, oracle):
 
 @pytest.mark.parametrize("dtype", [F32, F16, BF16])
 @pytest.mark.parametrize("hd,rot,nq,nkv", [(64, 64, 9, 3), (128, 128, 16, 8), (256, 256, 3, 1), (80, 80, 4, 2),
-                                            (128, 64, 4, 2), (32, 32, 5, 5), (96, 32, 2, 1)])
+                                            (128, 64, 4, 2), (32, 32, 5, 5), (96, 32, 2, 1), (256, 64, 24, 4)])
 def test_geometries_with_bias_and_norm(ctx, dev, oracle, dtype, hd, rot, nq, nkv):
     cfg = synth.LayerConfig("t", dtype, 37, 64, 64, nq, nkv, hd, 100, 1e6, 1e-6, 1, qk_bias=True, qk_norm=True,
                             seed=hd * 7 + rot)
@@ -261,3 +261,32 @@ def test_large_batches_staged_kernel_equals_register_kernel(ctx, dev, oracle, na
     else:
         synth.check_half(q1, rq, f"{name} q", cfg.dtype, atol=ROPE_HALF_ATOL)
         synth.check_half(k1, rk, f"{name} k", cfg.dtype, atol=ROPE_HALF_ATOL)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_qwen35_partial_rope_large_batch(ctx, dev, oracle, dtype, monkeypatch):
+    # head_dim 256 with 64 rotated dims, 24 q heads and 4 kv heads, per-head norm: the lane-mapped kernels
+    # (staged and register) against the oracle and against each other; on f32 rows the tail of every head must be
+    # exactly what the norm alone gives (the reference leaves it untouched, src/gpu/kernels.metal:2401-2425).
+    cfg = synth.LayerConfig("q35", dtype, 1500, 64, 64, 24, 4, 256, 100, 1e7, 1e-6, 1, qk_bias=False, qk_norm=True, seed=35)
+    rows = 1500
+    d = synth.layer_inputs(cfg, rows)
+    q1, k1 = run_qk(ctx, dev, cfg, d, rows, rot=64, pos0=77, w_dtype=F32)
+    monkeypatch.setenv("LOKAL_CUDA_ROPE_STAGED", "0")
+    q0, k0 = run_qk(ctx, dev, cfg, d, rows, rot=64, pos0=77, w_dtype=F32)
+    monkeypatch.delenv("LOKAL_CUDA_ROPE_STAGED")
+    synth.assert_bits_equal(q1, q0, "staged vs register kernel, q")
+    synth.assert_bits_equal(k1, k0, "staged vs register kernel, k")
+    rq, rk = oracle_qk(oracle, cfg, d, rot=64, pos0=77)
+    if dtype == F32:
+        synth.check_f32(q1, rq, "q")
+        synth.check_f32(k1, rk, "k")
+        # tails: norm only, never rotated. The parallel sum of squares may move the scale by an ulp against the
+        # oracle's 8-lane order, so most, not all, tail values are bit-identical; none is further than the f32 bar.
+        tail = q1.reshape(rows, 24, 256)[:, :, 64:]
+        ref_tail = rq.reshape(rows, 24, 256)[:, :, 64:]
+        rel = np.abs(tail - ref_tail) / np.maximum(np.abs(ref_tail), 1e-30)
+        assert rel.max() < 4e-7 and (tail.view(np.uint32) == ref_tail.view(np.uint32)).mean() > 0.5
+    else:
+        synth.check_half(q1, rq, "q", dtype, atol=ROPE_HALF_ATOL)
+        synth.check_half(k1, rk, "k", dtype, atol=ROPE_HALF_ATOL)
