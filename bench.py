@@ -654,6 +654,16 @@ def row_ops_workload(args, rank, world, local_rank):
     timed("split_q_gate_f32", 2 * T * HA * 2 * HD * 4,
           lambda b: ctx.split_q_gate(src[b % 2], a[b], gt[b], rows=T, n_heads=HA, head_dim=HD, stream=stream))
     del a, gt, src
+    # partial RoPE with per-head norm at the qwen35 attention geometry: 24 q heads + 4 kv heads of 256, 64 rotated dims
+    HKV, ROT = 4, 64
+    q, k = rnd(nbuf, T, HA * HD), rnd(nbuf, T, HKV * HD)
+    qw, kw = 1 + 0.1 * rnd(HD), 1 + 0.1 * rnd(HD)
+    table = torch.empty(T, ROT, device=dev, dtype=torch.float32)
+    ctx.rope_table(table, theta=1e7, rot_dim=ROT, rows=T, pos0=0, stream=stream)
+    params = [ctx.qk_rope_params(q=q[b], k=k[b], rows=T, n_q_heads=HA, n_kv_heads=HKV, head_dim=HD, rot_dim=ROT, eps=1e-6, q_norm_w=qw,
+                                 k_norm_w=kw, cos_sin=table, q_dtype=L.F32, k_dtype=L.F32, w_dtype=L.F32) for b in range(nbuf)]
+    timed("qk_rope_partial_64_of_256_f32", T * (2 * (HA + HKV) * HD * 4 + ROT * 4), lambda b: ctx.qk_rope(params[b], stream=stream))
+    del q, k
     # K/V staging: f32 rows of 8 KV heads x 128 narrowed to f16 and scattered into a windowed cache (sink 4, ring 8704)
     kvd = 1024
     lay = L.window_cfg(8192, 4)

@@ -13,6 +13,8 @@
 // x' and xn written once: 4*dim*sizeof(T) bytes of HBM traffic per row.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace lokal {
 namespace {
 
@@ -56,25 +58,30 @@ __device__ __forceinline__ void store_h_copy(void* base, int h_dtype, size_t ele
     }
 }
 
-template <typename T, int VPT, bool CTA_MODE>
+// WSAME: the weight vector has the rows' element type and is 16-byte aligned, so it is read like a row (the
+// usual case); otherwise through the type-switching loader. Arithmetic is packed f32x2 throughout: the same bits
+// as scalar round-to-nearest operations at half the instruction count (the kernel is as much issue-bound as
+// memory-bound: two loads and two stores per thread against some hundred instructions).
+template <typename T, int VPT, bool CTA_MODE, bool WSAME>
 __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const NormArgs a) {
     pdl_launch();
-    constexpr int N = VecOf<T>::N;
+    constexpr int N = VecOf<T>::N, P = N / 2;
     const unsigned tpr = CTA_MODE ? blockDim.x : 32u;
     const unsigned t = CTA_MODE ? threadIdx.x : (threadIdx.x & 31u);
     const size_t row = CTA_MODE ? static_cast<size_t>(blockIdx.x)
                                 : static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (!CTA_MODE && row >= a.rows) return;  // whole warps leave together
 
-    const T* xr = reinterpret_cast<const T*>(a.x) + row * a.dim;
-    const T* dr = a.delta ? reinterpret_cast<const T*>(a.delta) + row * a.dim : nullptr;
+    const size_t row_off = row * a.dim;
+    const T* xr = reinterpret_cast<const T*>(a.x) + row_off;
+    const T* dr = a.delta ? reinterpret_cast<const T*>(a.delta) + row_off : nullptr;
     if (a.prefetch) {  // one request per 128-byte line of the row, while the kernel before this one drains
 #pragma unroll
         for (int j = 0; j < VPT; j++) {
             const unsigned idx = t + j * tpr;
             if (idx < a.nvec && (idx & 7u) == 0) {
-                prefetch_l2(xr + static_cast<size_t>(idx) * N);
-                if (dr) prefetch_l2(dr + static_cast<size_t>(idx) * N);
+                prefetch_l2(xr + idx * N);
+                if (dr) prefetch_l2(dr + idx * N);
             }
         }
     }
@@ -86,55 +93,80 @@ __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const 
     for (int j = 0; j < VPT; j++) {
         const unsigned idx = t + j * tpr;
         if (idx < a.nvec) {
-            xv[j] = ld_stream(xr + static_cast<size_t>(idx) * N);
-            if (dr) dv[j] = ld_stream(dr + static_cast<size_t>(idx) * N);
+            xv[j] = ld_stream(xr + idx * N);
+            if (dr) dv[j] = ld_stream(dr + idx * N);
         }
     }
 
-    float v[VPT][N];
-    float acc = 0.0f;
+    float2 v[VPT][P];
+    float2 acc2 = make_float2(0.0f, 0.0f);
+    T* xo = reinterpret_cast<T*>(a.x_out) + row_off;
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const unsigned idx = t + j * tpr;
         if (idx < a.nvec) {
-            unpack16<T>(xv[j], v[j]);
+            unpack16p<T>(xv[j], v[j]);
             if (dr) {
-                float d[N];
-                unpack16<T>(dv[j], d);
+                float2 d[P];
+                unpack16p<T>(dv[j], d);
 #pragma unroll
-                for (int e = 0; e < N; e++) v[j][e] = v[j][e] + d[e];
-                T* xo = reinterpret_cast<T*>(a.x_out) + row * a.dim;
-                *reinterpret_cast<uint4*>(xo + static_cast<size_t>(idx) * N) = pack16<T>(v[j]);
+                for (int e = 0; e < P; e++) v[j][e] = add2(v[j][e], d[e]);
+                *reinterpret_cast<uint4*>(xo + idx * N) = pack16p<T>(v[j]);
             }
 #pragma unroll
-            for (int e = 0; e < N; e++) acc = sq_acc<T>(acc, v[j][e]);
+            for (int e = 0; e < P; e++) {
+                if (sizeof(T) == 2) acc2 = fma2(v[j][e], v[j][e], acc2);
+                else acc2 = add2(acc2, mul2(v[j][e], v[j][e]));  // separately rounded product and sum, as the reference
+            }
         }
     }
 
-    acc = warp_sum(acc);
+    float acc = warp_sum(acc2.x + acc2.y);
     if (CTA_MODE) {
-        __shared__ float partial[32];
+        __shared__ __align__(16) float partial[32];
         const unsigned warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
         if ((threadIdx.x & 31u) == 0) partial[warp] = acc;
         __syncthreads();
-        float total = 0.0f;
-        for (unsigned wv = 0; wv < nwarps; wv++) total += partial[wv];
+        float total;
+        if (nwarps == 4) {  // the usual shape (rows of 2 KB): one 16-byte read, the same left-to-right sum
+            const float4 p4 = *reinterpret_cast<const float4*>(partial);
+            total = ((p4.x + p4.y) + p4.z) + p4.w;
+        } else {
+            total = 0.0f;
+            for (unsigned wv = 0; wv < nwarps; wv++) total += partial[wv];
+        }
         acc = total;
     }
     const float scale = inv_rms<T>(acc, static_cast<float>(a.dim), a.inv_dim, a.eps);
+    const float2 s2 = make_float2(scale, scale);
 
-    T* yr = reinterpret_cast<T*>(a.xn) + row * a.dim;
+    T* yr = reinterpret_cast<T*>(a.xn) + row_off;
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const unsigned idx = t + j * tpr;
         if (idx < a.nvec) {
-            float wv[N];
-            load_w<N>(a.w, a.w_dtype, static_cast<size_t>(idx) * N, a.w_vec_ok, wv);
-            float y[N];
+            float2 w[P];
+            if (WSAME) {
+                unpack16p<T>(ld_keep(reinterpret_cast<const T*>(a.w) + idx * N), w);
+            } else {
+                float wv[N];
+                load_w<N>(a.w, a.w_dtype, static_cast<size_t>(idx) * N, a.w_vec_ok, wv);
 #pragma unroll
-            for (int e = 0; e < N; e++) y[e] = (v[j][e] * scale) * wv[e];
-            *reinterpret_cast<uint4*>(yr + static_cast<size_t>(idx) * N) = pack16<T>(y);
-            if (a.xn_h) store_h_copy<T, N>(a.xn_h, a.h_dtype, row * a.dim + static_cast<size_t>(idx) * N, y);
+                for (int e = 0; e < P; e++) w[e] = make_float2(wv[2 * e], wv[2 * e + 1]);
+            }
+            float2 y[P];
+#pragma unroll
+            for (int e = 0; e < P; e++) y[e] = mul2(mul2(v[j][e], s2), w[e]);  // (x * scale) * w
+            *reinterpret_cast<uint4*>(yr + idx * N) = pack16p<T>(y);
+            if (sizeof(T) == 4 && a.xn_h) {
+                float yf[N];
+#pragma unroll
+                for (int e = 0; e < P; e++) {
+                    yf[2 * e] = y[e].x;
+                    yf[2 * e + 1] = y[e].y;
+                }
+                store_h_copy<T, N>(a.xn_h, a.h_dtype, row_off + static_cast<size_t>(idx) * N, yf);
+            }
         }
     }
 }
@@ -180,7 +212,7 @@ __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a
     }
 }
 
-template <typename T, bool CTA_MODE>
+template <typename T, bool CTA_MODE, bool WSAME>
 cudaError_t launch_vec(const NormArgs& a, unsigned tpr, unsigned vpt, cudaStream_t s) {
     dim3 grid, block;
     if (CTA_MODE) {
@@ -191,13 +223,13 @@ cudaError_t launch_vec(const NormArgs& a, unsigned tpr, unsigned vpt, cudaStream
         grid = dim3(ceil_div(a.rows, 8));
     }
     switch (vpt) {
-        case 1: launch_k(norm_rows_kernel<T, 1, CTA_MODE>, grid, block, 0, s, a); break;
-        case 2: launch_k(norm_rows_kernel<T, 2, CTA_MODE>, grid, block, 0, s, a); break;
-        case 3: launch_k(norm_rows_kernel<T, 3, CTA_MODE>, grid, block, 0, s, a); break;
-        case 4: launch_k(norm_rows_kernel<T, 4, CTA_MODE>, grid, block, 0, s, a); break;
-        case 5: launch_k(norm_rows_kernel<T, 5, CTA_MODE>, grid, block, 0, s, a); break;
-        case 6: launch_k(norm_rows_kernel<T, 6, CTA_MODE>, grid, block, 0, s, a); break;
-        default: launch_k(norm_rows_kernel<T, 8, CTA_MODE>, grid, block, 0, s, a); break;
+        case 1: launch_k(norm_rows_kernel<T, 1, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
+        case 2: launch_k(norm_rows_kernel<T, 2, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
+        case 3: launch_k(norm_rows_kernel<T, 3, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
+        case 4: launch_k(norm_rows_kernel<T, 4, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
+        case 5: launch_k(norm_rows_kernel<T, 5, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
+        case 6: launch_k(norm_rows_kernel<T, 6, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
+        default: launch_k(norm_rows_kernel<T, 8, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
     }
     return cudaGetLastError();
 }
@@ -222,7 +254,12 @@ int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, NormArgs a, bool ptrs_alig
     while (tpr < 1024 && (a.nvec + tpr - 1) / tpr > 8) tpr *= 2;
     unsigned vpt = (a.nvec + tpr - 1) / tpr;
     if (vpt == 7) vpt = 8;
-    cudaError_t e = tpr == 32 ? launch_vec<T, false>(a, tpr, vpt, s) : launch_vec<T, true>(a, tpr, vpt, s);
+    // weights of the rows' own type, 16-byte aligned: read like a row
+    const int own_type = sizeof(T) == 4 ? LOKAL_F32 : (std::is_same<T, __half>::value ? LOKAL_F16 : LOKAL_BF16);
+    const bool wsame = a.w_dtype == own_type && a.w_vec_ok;
+    cudaError_t e;
+    if (tpr == 32) e = wsame ? launch_vec<T, false, true>(a, tpr, vpt, s) : launch_vec<T, false, false>(a, tpr, vpt, s);
+    else e = wsame ? launch_vec<T, true, true>(a, tpr, vpt, s) : launch_vec<T, true, false>(a, tpr, vpt, s);
     if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "launch of norm_rows_kernel failed: %s", cudaGetErrorString(e));
     return LOKAL_OK;
 }
