@@ -246,9 +246,13 @@ int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, NormArgs a, bool ptrs_alig
     a.nvec = a.dim / N;
     // Threads per row. One 16-byte vector per thread (a CTA per row, shared-memory combine) keeps every CTA small and
     // short-lived, so the machine drains evenly at the end of the kernel; rows wider than 1024 vectors give each
-    // thread several vectors, and rows of at most 32 vectors take one warp each, eight rows to a CTA.
+    // thread several vectors, and rows of at most 32 vectors take one warp each, eight rows to a CTA. With enough
+    // rows to give every SM 32 of them, rows of up to 128 vectors also take one warp each (four vectors per lane, no
+    // barrier): measured at 8192 x 2 KB rows 12.0 against 12.3 us alone and 1.84 against 1.86 ms for the step;
+    // at 2048 rows and fewer the one-vector shape wins.
     unsigned tpr = ((a.nvec + 31u) / 32u) * 32u;
     if (tpr > 1024) tpr = 1024;
+    if (a.nvec <= 128 && a.rows >= static_cast<size_t>(ctx->sm_count) * 32u) tpr = 32;
     const long forced = tune_env("LOKAL_CUDA_NORM_TPR", 0);
     if (forced >= 32 && forced <= 1024 && forced % 32 == 0) tpr = static_cast<unsigned>(forced);
     while (tpr < 1024 && (a.nvec + tpr - 1) / tpr > 8) tpr *= 2;
