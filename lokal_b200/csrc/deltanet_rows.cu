@@ -26,12 +26,28 @@ struct RowNormArgs {
     void* y;
     const void* w;  // gated_output_norm only
     const void* z;  // gated_output_norm only
-    unsigned long long rows, rows_per_token, tok_stride;  // row g = (t, r): element offset t*tok_stride + r*dim
+    unsigned long long rows, tok_stride;  // row g = (t, r): element offset t*tok_stride + r*dim; tok_stride 0 = contiguous rows
+    unsigned rows_per_token;
+    double inv_dim;  // 1 / dim when dim is a power of two (the product is then the quotient, exactly), else 0
     unsigned dim;
     float eps;
     int w_dtype;
     int w_vec_ok;
 };
+
+// Element offset of row g. Contiguous rows (one token, or tokens packed back to back) need one multiply; the strided
+// form divides in 32 bits (the host refuses more than 2^32 - 1 rows): a 64-bit division costs more than the rest of
+// the kernel.
+__device__ __forceinline__ unsigned long long row_offset(const RowNormArgs& a, unsigned long long g) {
+    if (a.tok_stride == 0) return g * a.dim;
+    const unsigned g32 = static_cast<unsigned>(g), t = g32 / a.rows_per_token;
+    return static_cast<unsigned long long>(t) * a.tok_stride + static_cast<unsigned long long>(g32 - t * a.rows_per_token) * a.dim;
+}
+
+// mean of squares as the reference takes it: the f64 sum divided by n, narrowed to f32
+__device__ __forceinline__ float mean_f32(const RowNormArgs& a, double sum) {
+    return static_cast<float>(a.inv_dim != 0.0 ? sum * a.inv_dim : sum / static_cast<double>(a.dim));
+}
 
 __device__ __forceinline__ double warp_sum_f64(double v) {
 #pragma unroll
@@ -62,7 +78,7 @@ __global__ void __launch_bounds__(256) deltanet_rows_kernel(const RowNormArgs a)
 #pragma unroll
     for (int r = 0; r < RPW; r++) {
         const unsigned long long g = g0 + r;
-        off[r] = (g / a.rows_per_token) * a.tok_stride + (g % a.rows_per_token) * a.dim;
+        off[r] = row_offset(a, g);
         if (g < a.rows) {
 #pragma unroll
             for (int j = 0; j < VPT; j++) {
@@ -90,7 +106,7 @@ __global__ void __launch_bounds__(256) deltanet_rows_kernel(const RowNormArgs a)
         acc = warp_sum_f64(acc);
         float scale;
         if (MODE == 0) scale = 1.0f / fmaxf(static_cast<float>(sqrt(acc)), a.eps);
-        else scale = 1.0f / sqrtf(static_cast<float>(acc / static_cast<double>(a.dim)) + a.eps);
+        else scale = 1.0f / sqrtf(mean_f32(a, acc) + a.eps);
         T* dst = reinterpret_cast<T*>(a.y) + off[r];
 #pragma unroll
         for (int j = 0; j < VPT; j++) {
@@ -120,7 +136,7 @@ __global__ void __launch_bounds__(256) deltanet_rows_generic_kernel(const RowNor
     pdl_sync();
     __shared__ double part[8];
     const unsigned long long g = blockIdx.x;
-    const unsigned long long off = (g / a.rows_per_token) * a.tok_stride + (g % a.rows_per_token) * a.dim;
+    const unsigned long long off = row_offset(a, g);
     const T* src = reinterpret_cast<const T*>(a.x) + off;
     T* dst = reinterpret_cast<T*>(a.y) + off;
     double acc = 0.0;
@@ -136,7 +152,7 @@ __global__ void __launch_bounds__(256) deltanet_rows_generic_kernel(const RowNor
     for (int j = 0; j < 8; j++) total += part[j];
     float scale;
     if (MODE == 0) scale = 1.0f / fmaxf(static_cast<float>(sqrt(total)), a.eps);
-    else scale = 1.0f / sqrtf(static_cast<float>(total / static_cast<double>(a.dim)) + a.eps);
+    else scale = 1.0f / sqrtf(mean_f32(a, total) + a.eps);
     for (unsigned i = threadIdx.x; i < a.dim; i += 256) {
         float f = to_f32<T>(src[i]);
         if (MODE == 0) {
@@ -254,8 +270,9 @@ int lokal_cuda_l2norm_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void*
     a.x = x;
     a.y = y;
     a.rows = static_cast<unsigned long long>(rows_per_token) * n_tokens;
-    a.rows_per_token = rows_per_token;
-    a.tok_stride = n_tokens > 1 ? tok_stride : 0;
+    if (a.rows > 0xffffffffull || rows_per_token > 0xffffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "l2norm_rows: too many rows for one launch");
+    a.rows_per_token = static_cast<unsigned>(rows_per_token);
+    a.tok_stride = (n_tokens > 1 && tok_stride != rows_per_token * dim) ? tok_stride : 0;  // 0: rows back to back
     a.dim = static_cast<unsigned>(dim);
     a.eps = eps;
     const bool vec_ok = lokal::aligned_to(x, 16) && lokal::aligned_to(y, 16) && (dim * es) % 16 == 0 && (a.tok_stride * es) % 16 == 0;
@@ -281,8 +298,10 @@ int lokal_cuda_gated_output_norm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const
     a.w = w;
     a.z = z;
     a.rows = rows;
-    a.rows_per_token = rows;
+    if (rows > 0xffffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "gated_output_norm: too many rows for one launch");
+    a.rows_per_token = static_cast<unsigned>(rows);
     a.tok_stride = 0;
+    a.inv_dim = (dim & (dim - 1)) == 0 ? 1.0 / static_cast<double>(dim) : 0.0;
     a.dim = static_cast<unsigned>(dim);
     a.eps = eps;
     a.w_dtype = w_dtype;

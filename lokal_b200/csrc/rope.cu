@@ -81,6 +81,7 @@ struct QkArgs {
     unsigned q_row_bytes, k_row_bytes;  // n_q*head_dim*sizeof(T), n_kv*head_dim*sizeof(T) (staged kernel)
     unsigned stage_bytes;               // per-warp staging area, multiple of 128
     int prefetch;                       // ask L2 for the row before waiting for the previous kernel (staged kernel)
+    unsigned swpr;                      // warps that share one staged row (staged kernel)
     unsigned* err_word;
 };
 
@@ -320,10 +321,11 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
     }
 }
 
-// Staged variant: lane 0 of each warp brings the whole row (its q heads, then its k heads) into shared memory with
-// two bulk asynchronous copies that complete on an mbarrier, so all of the row's bytes are in flight at once without
-// holding registers; the warp then walks the head groups out of shared memory and stores results straight to
-// global memory. Same lane mapping, arithmetic and results as qk_rope_kernel.
+// Staged variant: one lane brings the whole row (its q heads, then its k heads) into shared memory with two bulk
+// asynchronous copies that complete on an mbarrier, so all of the row's bytes are in flight at once without
+// holding registers; the row's warps (one for rows of a few KB, two or four for wider rows, which share the staged
+// row and split its head groups) then walk the heads out of shared memory and store results straight to global
+// memory. Same lane mapping, arithmetic and results as qk_rope_kernel.
 template <typename T, int HD, int ROT, bool NORM, bool BIAS>
 __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) {
     pdl_launch();
@@ -333,19 +335,20 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
     __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
     const unsigned warps_per_cta = blockDim.x >> 5, warp_in_cta = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(dyn_smem);
-    unsigned char* stage = dyn_smem + 128 + static_cast<size_t>(warp_in_cta) * a.stage_bytes;
-    const uint32_t bar = smem_addr(&bars[warp_in_cta]);
-    const unsigned long long warp = static_cast<unsigned long long>(blockIdx.x) * warps_per_cta + warp_in_cta;
-    const bool valid = warp < a.rows;
-    const unsigned long long row = valid ? warp : a.rows - 1;
-    if (a.prefetch && valid) {  // the row's lines are asked of L2 while the kernel before this one drains
+    const unsigned row_in_cta = warp_in_cta / a.swpr, part = warp_in_cta % a.swpr;  // a.swpr warps share a row
+    unsigned char* stage = dyn_smem + 128 + static_cast<size_t>(row_in_cta) * a.stage_bytes;
+    const uint32_t bar = smem_addr(&bars[row_in_cta]);
+    const unsigned long long grow = static_cast<unsigned long long>(blockIdx.x) * (warps_per_cta / a.swpr) + row_in_cta;
+    const bool valid = grow < a.rows;
+    const unsigned long long row = valid ? grow : a.rows - 1;
+    if (a.prefetch && valid && part == 0) {  // the row's lines are asked of L2 while the kernel before this one drains
         const unsigned char* qrow = reinterpret_cast<const unsigned char*>(reinterpret_cast<const T*>(a.q) + row * a.q_stride);
         const unsigned char* krow = reinterpret_cast<const unsigned char*>(reinterpret_cast<const T*>(a.k) + row * a.k_stride);
         for (unsigned off = lane * 128u; off < a.q_row_bytes; off += 32u * 128u) prefetch_l2(qrow + off);
         for (unsigned off = lane * 128u; off < a.k_row_bytes; off += 32u * 128u) prefetch_l2(krow + off);
     }
     pdl_wait();
-    if (lane == 0) {
+    if (lane == 0 && part == 0) {
         mbar_init(bar, 1);
         mbar_init_fence();
         if (valid) {
@@ -357,7 +360,7 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
     R r;
     r.init(a, row, lane, w_s);
     if (NORM) R::stage_weights(a, w_s);
-    __syncthreads();  // norm weights staged; every warp's mbarrier initialised before anyone waits on it
+    __syncthreads();  // norm weights staged; every row's mbarrier initialised before anyone waits on it
     if (!valid) return;
     if (!mbar_wait_bounded(bar, 0)) {
         if (lane == 0) atomicOr(a.err_word, kErrTimeout);
@@ -366,7 +369,7 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
     }
     const T* srow = reinterpret_cast<const T*>(stage) + r.lo_off;
 #pragma unroll 2
-    for (unsigned c = 0; c < a.chunks; c++) {
+    for (unsigned c = part; c < a.chunks; c += a.swpr) {
         const unsigned slot = c * HPW + r.hsel;
         const bool live = slot < r.slots;
         uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
@@ -486,12 +489,17 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     a.prefetch = prefetch_enabled();
     // Staged kernel: whole rows through shared memory by bulk copy. Needs one warp per row, row starts that are
     // 16-byte aligned (true on this path) and a row small enough that several warps' stages fit in shared memory.
-    const bool staged_ok = a.wpr == 1 && a.stage_bytes <= 24u * 1024u && tune_env("LOKAL_CUDA_ROPE_STAGED", 1) != 0;
+    const bool staged_ok = a.wpr == 1 && a.stage_bytes <= 47u * 1024u && tune_env("LOKAL_CUDA_ROPE_STAGED", 1) != 0;
     if (staged_ok) {
-        unsigned swpc = 8;
-        while (swpc > 1 && 128u + swpc * a.stage_bytes > 48u * 1024u) swpc /= 2;
-        const unsigned sgrid = static_cast<unsigned>((a.rows + swpc - 1) / swpc);
-        const size_t smem = 128u + static_cast<size_t>(swpc) * a.stage_bytes;
+        // Rows per CTA: as many as fit in 48 KB, at most eight; rows above 12 KB are shared by two warps, above 24 KB
+        // by four, so that a CTA still has several warps to work through its few wide rows.
+        a.swpr = a.stage_bytes <= 12u * 1024u ? 1u : (a.stage_bytes <= 24u * 1024u ? 2u : 4u);
+        if (a.swpr > a.chunks) a.swpr = a.chunks;
+        unsigned rpc = 8 / a.swpr;
+        while (rpc > 1 && 128u + rpc * a.stage_bytes > 48u * 1024u) rpc -= (rpc > 4 ? 4 : (rpc > 2 ? 2 : 1));
+        const unsigned swpc = rpc * a.swpr;  // warps per CTA
+        const unsigned sgrid = static_cast<unsigned>((a.rows + rpc - 1) / rpc);
+        const size_t smem = 128u + static_cast<size_t>(rpc) * a.stage_bytes;
 #define LOKAL_ROPE_LAUNCH_STAGED(HD_, ROT_)                                                                      \
     do {                                                                                                         \
         if (norm && bias) launch_k(qk_rope_staged_kernel<T, HD_, ROT_, true, true>, sgrid, swpc * 32, smem, s, a);   \
