@@ -81,7 +81,7 @@ struct QkArgs {
     unsigned q_row_bytes, k_row_bytes;  // n_q*head_dim*sizeof(T), n_kv*head_dim*sizeof(T) (staged kernel)
     unsigned stage_bytes;               // per-warp staging area, multiple of 128
     int prefetch;                       // ask L2 for the row before waiting for the previous kernel (staged kernel)
-    unsigned swpr;                      // warps that share one staged row (staged kernel)
+    unsigned swpr, swpr_shift;          // warps that share one staged row, a power of two, and its log2 (staged kernel)
     unsigned* err_word;
 };
 
@@ -335,10 +335,14 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
     __shared__ __align__(16) float w_s[NORM ? 2 * HD : 4];
     const unsigned warps_per_cta = blockDim.x >> 5, warp_in_cta = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(dyn_smem);
-    const unsigned row_in_cta = warp_in_cta / a.swpr, part = warp_in_cta % a.swpr;  // a.swpr warps share a row
+    // a.swpr (1, 2 or 4) warps share a row; the one-warp case keeps constant strides
+    const bool shared_row = a.swpr > 1;
+    const unsigned row_in_cta = shared_row ? warp_in_cta >> a.swpr_shift : warp_in_cta;
+    const unsigned part = shared_row ? warp_in_cta & (a.swpr - 1u) : 0u;
     unsigned char* stage = dyn_smem + 128 + static_cast<size_t>(row_in_cta) * a.stage_bytes;
     const uint32_t bar = smem_addr(&bars[row_in_cta]);
-    const unsigned long long grow = static_cast<unsigned long long>(blockIdx.x) * (warps_per_cta / a.swpr) + row_in_cta;
+    const unsigned long long grow =
+        static_cast<unsigned long long>(blockIdx.x) * (shared_row ? warps_per_cta >> a.swpr_shift : warps_per_cta) + row_in_cta;
     const bool valid = grow < a.rows;
     const unsigned long long row = valid ? grow : a.rows - 1;
     if (a.prefetch && valid && part == 0) {  // the row's lines are asked of L2 while the kernel before this one drains
@@ -368,8 +372,7 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
         return;
     }
     const T* srow = reinterpret_cast<const T*>(stage) + r.lo_off;
-#pragma unroll 2
-    for (unsigned c = part; c < a.chunks; c += a.swpr) {
+    auto one_pass = [&](unsigned c) {
         const unsigned slot = c * HPW + r.hsel;
         const bool live = slot < r.slots;
         uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
@@ -378,6 +381,12 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
             hi = *reinterpret_cast<const uint4*>(srow + static_cast<size_t>(slot) * HD + (r.hi_off - r.lo_off));
         }
         r.pass(a, slot, live, lo, hi);
+    };
+    if (!shared_row) {
+#pragma unroll 2
+        for (unsigned c = 0; c < a.chunks; c++) one_pass(c);
+    } else {
+        for (unsigned c = part; c < a.chunks; c += a.swpr) one_pass(c);
     }
 }
 
@@ -494,7 +503,8 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
         // Rows per CTA: as many as fit in 48 KB, at most eight; rows above 12 KB are shared by two warps, above 24 KB
         // by four, so that a CTA still has several warps to work through its few wide rows.
         a.swpr = a.stage_bytes <= 12u * 1024u ? 1u : (a.stage_bytes <= 24u * 1024u ? 2u : 4u);
-        if (a.swpr > a.chunks) a.swpr = a.chunks;
+        while (a.swpr > a.chunks) a.swpr >>= 1;
+        a.swpr_shift = a.swpr == 4 ? 2u : (a.swpr == 2 ? 1u : 0u);
         unsigned rpc = 8 / a.swpr;
         while (rpc > 1 && 128u + rpc * a.stage_bytes > 48u * 1024u) rpc -= (rpc > 4 ? 4 : (rpc > 2 ? 2 : 1));
         const unsigned swpc = rpc * a.swpr;  // warps per CTA
