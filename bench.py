@@ -72,6 +72,29 @@ def embed_dim_ok(cfg):
     return cfg.hidden % 32 == 0
 
 
+def bind_to_gpu_cpus(cuda_index: int) -> int:
+    """Restricts this process to the host CPUs NVML reports as local to the GPU (process-local affinity, read-only NVML
+    query), so that the pinned staging buffers it then allocates land on the GPU's NUMA node. Returns how many CPUs it
+    was bound to, 0 if nothing was changed."""
+    try:
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        props = torch.cuda.get_device_properties(cuda_index)
+        bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        local = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus = local & allowed
+        if cpus and cpus != allowed:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return 0
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
@@ -226,6 +249,7 @@ def ours(args, cfg, rank, world, local_rank):
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    bound_cpus = bind_to_gpu_cpus(local_rank)  # before any pinned allocation: host buffers on the GPU's NUMA node
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ctx = L.Context(local_rank)
@@ -419,7 +443,7 @@ def ours(args, cfg, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": {L.F32: "f32", L.F16: "f16", L.BF16: "bf16"}[cfg.dtype] + " storage, f32 arithmetic", "data": "synthetic",
-            "config": workload_config(cfg, T, args),
+            "config": dict(workload_config(cfg, T, args), host_cpus_bound_to_gpu=bound_cpus),
             "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9, "step_algorithmic_bytes": int(step_bytes),
             "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
             "roofline": roof, "clocks": clocks, "e2e": e2e,
