@@ -1,8 +1,10 @@
 /*
  * lokal_cuda.h -- C ABI of the B200 (sm_100a) implementation of lokal's fused
  * per-token layer ops: residual-add + RMSNorm (incl. per-head qk-norm), RoPE of
- * q/k with the bias fold, SiLU(gate)*up, and embedding gather with GGUF
- * Q8_0 / Q4_K row dequantisation.
+ * q/k with the bias fold, SiLU(gate)*up, and embedding gather with GGUF row
+ * dequantisation (every block type the reference decodes) -- plus the steps
+ * either side of that path: K/V staging into the cache, the gated-deltanet
+ * per-row ops, and a GGUF container reader.
  *
  * This is the boundary a `-b cuda` backend of the reference binds through FFI:
  * plain pointers and sizes, no C++ or framework types. Each entry point names
@@ -259,8 +261,8 @@ LOKAL_API int lokal_cuda_swiglu(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const 
  * prefill's Source::Ids arm (src/gpu/metal.rs:3160-3184), the dense lookup
  * (src/model.rs:200-202) and the GPU twin `embed` (src/gpu/kernels.metal:30);
  * row addressing and range check of LowMemSource::read_rows
- * (src/lowmem/mod.rs:654-668); decode = gguf::dequant_row_ref Q8_0 / Q4_K /
- * F16 / F32 arms (src/gguf/dequant.rs:191-239, 462-483), bit for bit.
+ * (src/lowmem/mod.rs:654-668); decode = gguf::dequant_row_ref, every arm
+ * (src/gguf/dequant.rs:191-535), bit for bit; BF16 tables in addition.
  *   out[i][0..dim) = dequant(table row ids[i])
  * table: device bytes, vocab rows of row_bytes(type, dim), 16-byte aligned.
  * ids: device u32[n]. out: `out_dtype` F32, or F16 / BF16 (the exact f32 value

@@ -465,7 +465,7 @@ int lokal_cuda_host_dequant_row(lokal_cuda_ctx* ctx, int ggml_type, const uint8_
     LOKAL_ENTER(ctx);
     if (!src || !out) return ctx->fail(LOKAL_ERR_BAD_ARG, "host_dequant_row: null pointer");
     const size_t be = lokal_cuda_blk_elems(ggml_type);
-    if (be == 0) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "host_dequant_row: ggml type %d is not F32/F16/BF16/Q8_0/Q4_K", ggml_type);
+    if (be == 0) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "host_dequant_row: ggml type %d is not a float type, a Q*_0 / Q*_K block type or an i-quant", ggml_type);
     if (n % be != 0 || src_len != lokal_cuda_row_bytes(ggml_type, n))
         return ctx->fail(LOKAL_ERR_BAD_ARG, "host_dequant_row: src/out size mismatch (%zu bytes for %zu elements of type %d)", src_len, n, ggml_type);
     if (n == 0) return LOKAL_OK;

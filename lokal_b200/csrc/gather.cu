@@ -5,12 +5,14 @@
 // src/lowmem/mod.rs:654-668) and expands it with gguf::dequant_row_ref
 // (src/gguf/dequant.rs:191-239 F32/F16/Q8_0, :462-483 Q4_K, scale unpack
 // :141-150; :204-230 Q4_0/Q5_0, :396-425 IQ4_NL/IQ4_XS, :426-461 Q2_K/Q3_K,
-// :484-535 Q5_K/Q6_K). Results here are bit-identical to that: int -> f32 and
-// f16 -> f32 conversions are exact, and every product and difference of the
-// reference's expressions (d1*q - m1, (d*sc)*q ...) is computed with
-// __fmul_rn / __fsub_rn, so each is rounded once and never contracted into an
-// FMA. Q8_0 and Q4_K have vector decoders; the other block types decode one
-// element at a time from the staged row with the same arithmetic.
+// :484-535 Q5_K/Q6_K, :255-394 the codebook types). Results here are
+// bit-identical to that: int -> f32 and f16 -> f32 conversions are exact, and
+// every product and difference of the reference's expressions (d1*q - m1,
+// (d*sc)*q ...) is computed with __fmul_rn / __fsub_rn or their packed f32x2
+// twins, so each is rounded once and never contracted into an FMA. Every block
+// type has a vector decoder for the staged kernel (four elements per 32-bit
+// word of quants) and an element decoder for the kernel that takes any
+// alignment.
 //
 // Kernel shape (quantised tables): one warp per token row, persistent over a
 // grid-stride list of rows. Lane 0 stages the raw row into shared memory with

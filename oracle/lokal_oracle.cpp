@@ -7,11 +7,16 @@
 // benchmark's CPU-baseline leg load this library.
 //
 // Parity status:
-//   * GGUF Q8_0 / Q4_K dequant, block-size table, embedding gather: PINNED by
-//     the reference's own known-answer vectors (src/gguf/dequant.rs:567-577,
-//     683-730, 768-780) and by a second, independently written per-element
-//     decoder in this file (the index form of src/gpu/kernels.metal:77-81,
-//     108-116, 889-904).
+//   * GGUF dequant, block-size table, embedding gather: Q8_0, Q4_K, Q4_0, Q5_0,
+//     Q2_K, Q3_K, Q5_K, Q6_K PINNED by the reference's own known-answer vectors
+//     (src/gguf/dequant.rs:567-577, 579-766, 768-780); Q8_0 / Q4_K also by a
+//     second, independently written per-element decoder in this file (the index
+//     form of src/gpu/kernels.metal:77-81, 108-116, 889-904). IQ4_NL, IQ4_XS and
+//     the seven codebook types have no hand vector in the reference: they are
+//     pinned by agreeing bit for bit with independent numpy decoders (tests/).
+//   * deltanet siblings (l2_norm, f64-mean rmsnorm, gated_output_norm,
+//     attn_out_gate): pinned by src/deltanet_ref.rs:226-235, 306-329; sigmoid
+//     shares the libm caveat below.
 //   * rmsnorm / dot: pinned by src/math.rs:86-108 (dot tail vector, all-3s row).
 //   * RoPE and SiLU: PARITY UNPINNED at the libm boundary. The reference calls
 //     the platform libm (powf, sinf, cosf, expf) through Rust std and holds no

@@ -6,7 +6,7 @@ tables to lokal_cuda_set_iq_grid. The tests need real values, so this script rea
 reference's data file (run where the reference tree is present), checks lengths and the wrapping checksums the
 reference's own test holds (src/lowmem/iq_grids.rs:584-603), and stores them as a binary fixture.
 
-    python tests/golden/make_iq_grids.py [path/to/reference]
+    python tests/golden/make_iq_grids.py path/to/reference
 """
 import os
 import re
@@ -31,7 +31,9 @@ def wrapping_sum(a):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    ref = sys.argv[1]
     text = open(os.path.join(ref, "src", "lowmem", "iq_grids.rs")).read()
     out = {}
     for name, (key, dtype, n, checksum) in TABLES.items():
