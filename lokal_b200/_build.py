@@ -24,6 +24,7 @@ NVCC_FLAGS = [
     "-fmad=false",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "--shared",
+    "--threads", "0",  # the sources compile in parallel
 ]
 
 

@@ -30,6 +30,11 @@ constexpr unsigned kMaxRot = 1024;
 #endif
 constexpr int kRopeInFlight = LOKAL_ROPE_IN_FLIGHT;
 
+#ifndef LOKAL_ROPE_STAGED_UNROLL
+#define LOKAL_ROPE_STAGED_UNROLL 2  // head-group passes of the staged kernel interleaved by the compiler
+#endif
+constexpr int kRopeStagedUnroll = LOKAL_ROPE_STAGED_UNROLL;
+
 #ifndef LOKAL_ROPE_MIN_CTAS
 #define LOKAL_ROPE_MIN_CTAS 3  // resident 256-thread CTAs per SM the fast kernel is compiled for (caps registers at 80)
 #endif
@@ -383,7 +388,7 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
         r.pass(a, slot, live, lo, hi);
     };
     if (!shared_row) {
-#pragma unroll 2
+#pragma unroll kRopeStagedUnroll
         for (unsigned c = 0; c < a.chunks; c++) one_pass(c);
     } else {
         for (unsigned c = part; c < a.chunks; c += a.swpr) one_pass(c);
