@@ -117,3 +117,44 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("lm_dequant_oracle", ""), f"{f} mentions the oracle"
+
+
+def test_header_is_plain_c_and_links_from_c(tmp_path):
+    """The boundary is a C ABI: a C99 translation unit includes the header, links the library and calls the
+    host-only entry points (no GPU needed), the way a cgo / bindgen / FFI consumer would."""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    capi.load()
+    src = tmp_path / "use_abi.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <string.h>
+#include "lokal_cuda.h"
+int main(void) {
+    lokal_kv_layout lay;
+    lokal_qk_rope_params p;
+    size_t row0 = 0, count = 0;
+    memset(&p, 0, sizeof p);
+    if (lokal_cuda_blk_bytes(LOKAL_Q6_K) != 210 || lokal_cuda_row_bytes(LOKAL_Q8_0, 896) != 952) return 1;
+    if (lokal_cuda_window_cfg(1024, 4, 512, &lay) != LOKAL_OK || lay.ring != 1536 || lokal_cuda_window_slot_of(&lay, 5) != 129) return 2;
+    if (lokal_cuda_shard_rows(8192, 8, 3, &row0, &count) != LOKAL_OK || row0 != 3072 || count != 1024) return 3;
+    if (lokal_cuda_stream_sync(NULL, NULL) != LOKAL_ERR_BAD_ARG) return 4;
+    {
+        lokal_gguf* g = NULL;
+        char err[256];
+        if (lokal_gguf_open("/nonexistent.gguf", &g, err, sizeof err) != LOKAL_ERR_IO || g != NULL || !strstr(err, "cannot open")) return 5;
+    }
+    printf("%s %zu\n", lokal_cuda_version(), sizeof p);
+    return 0;
+}
+''')
+    exe = tmp_path / "use_abi"
+    libdir = os.path.dirname(capi.library_path())
+    subprocess.run([cc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-llokal_cuda", f"-Wl,-rpath,{libdir}"], check=True, capture_output=True, text=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, (res.returncode, res.stdout, res.stderr)
+    assert "sm_100a" in res.stdout and res.stdout.split()[-1] == str(C.sizeof(capi.QkRopeParams))
