@@ -478,9 +478,11 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     a.chunks = (slots + hpw - 1) / hpw;
     // Warps per row: one warp walks all head groups of a row (the row's cos/sin are read once). Measured on B200
     // this beat splitting a row over several warps even for 8192-row batches; few rows spread over more warps.
+    // Below about 12 rows per SM a row is split over several warps of the register kernel (measured: at 2048 rows of
+    // the 0.5B / 0.6B shapes one staged warp per row is 20-35 % faster, at 1024 rows and fewer the split wins).
     unsigned wpr = 1;
     const unsigned long long want_warps = static_cast<unsigned long long>(ctx->sm_count) * 16;
-    if (a.rows < want_warps) {
+    if (a.rows < static_cast<unsigned long long>(ctx->sm_count) * 12) {
         wpr = static_cast<unsigned>((want_warps + a.rows - 1) / a.rows);
         if (wpr > a.chunks) wpr = a.chunks;
     }
