@@ -219,8 +219,10 @@ cudaError_t launch_vec(const NormArgs& a, unsigned tpr, unsigned vpt, cudaStream
         grid = dim3(static_cast<unsigned>(a.rows));
         block = dim3(tpr);
     } else {
-        block = dim3(256);
-        grid = dim3(ceil_div(a.rows, 8));
+        long wpc = tune_env("LOKAL_CUDA_NORM_WARPS", 8);  // rows (warps) per CTA in warp mode
+        if (wpc != 1 && wpc != 2 && wpc != 4 && wpc != 8) wpc = 8;
+        block = dim3(static_cast<unsigned>(wpc) * 32u);
+        grid = dim3(ceil_div(a.rows, static_cast<size_t>(wpc)));
     }
     switch (vpt) {
         case 1: launch_k(norm_rows_kernel<T, 1, CTA_MODE, WSAME>, grid, block, 0, s, a); break;
