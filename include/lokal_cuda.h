@@ -214,7 +214,13 @@ LOKAL_API int lokal_cuda_qk_rope(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const
 /* Same op with the reference's own argument list (pos0 or per-row positions
  * plus theta): the table is built into scratch memory owned by the context
  * (grown on demand with cudaMalloc) and consumed by the same launch sequence.
- * Calls on one context that overlap on the device share that scratch. */
+ * Calls from several streams of one context are safe: each waits, on the
+ * device, until the previous call's rope kernel has consumed the shared table
+ * (so these short sections run one after another; sessions that want no such
+ * coupling build their own table and call lokal_cuda_qk_rope). A call made
+ * while `s` is being captured into a graph cannot take part in that hand-over:
+ * keep other callers of this entry point off the context while such a graph
+ * runs. */
 LOKAL_API int lokal_cuda_qk_rope_pos(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_qk_rope_params* p,
                                      float theta, const int32_t* positions, int64_t pos0);
 

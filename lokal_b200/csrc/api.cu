@@ -112,6 +112,7 @@ void lokal_cuda_destroy(lokal_cuda_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+    if (ctx->scratch_event) cudaEventDestroy(ctx->scratch_event);
     if (ctx->err_word) cudaFree(ctx->err_word);
     if (ctx->err_word_host) cudaFreeHost(ctx->err_word_host);
     if (ctx->scratch) cudaFree(ctx->scratch);
@@ -334,12 +335,29 @@ int lokal_cuda_qk_rope_pos(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal
     std::lock_guard<std::mutex> g(ctx->mu);
     int rc = ensure_scratch(ctx, static_cast<size_t>(p->rows) * p->rot_dim * sizeof(float));
     if (rc != LOKAL_OK) return rc;
+    // The table lives in scratch shared by every stream of the context. Sessions on different streams may call
+    // this concurrently, so each call first waits (on the device, in its own stream) for the previous call's rope
+    // kernel to have consumed the table, and leaves an event behind for the next one. A stream under graph capture
+    // cannot take part in that hand-over: a captured call relies on its caller to keep other users of this entry
+    // point off the context while the graph runs (lokal_cuda_qk_rope with the caller's own table has no such limit).
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    LOKAL_CUDA_TRY(ctx, cudaStreamIsCapturing(as_stream(s), &cap));
+    const bool ordered = cap == cudaStreamCaptureStatusNone;
+    if (ordered) {
+        if (!ctx->scratch_event) LOKAL_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->scratch_event, cudaEventDisableTiming));
+        if (ctx->scratch_event_recorded) LOKAL_CUDA_TRY(ctx, cudaStreamWaitEvent(as_stream(s), ctx->scratch_event, 0));
+    }
     float* table = static_cast<float*>(ctx->scratch);
     rc = lokal::launch_rope_table(ctx, as_stream(s), theta, p->rot_dim, positions, pos0, p->rows, table);
     if (rc != LOKAL_OK) return rc;
     lokal_qk_rope_params q = *p;
     q.cos_sin = table;
-    return lokal::launch_qk_rope(ctx, as_stream(s), q);
+    rc = lokal::launch_qk_rope(ctx, as_stream(s), q);
+    if (ordered) {
+        LOKAL_CUDA_TRY(ctx, cudaEventRecord(ctx->scratch_event, as_stream(s)));
+        ctx->scratch_event_recorded = true;
+    }
+    return rc;
 }
 
 int lokal_cuda_swiglu(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* gate, const void* up, void* out, void* out_h,

@@ -43,6 +43,8 @@ struct lokal_cuda_ctx {
     void* staging = nullptr;  // pinned host
     size_t staging_bytes = 0;
     cudaStream_t host_stream = nullptr;
+    cudaEvent_t scratch_event = nullptr;  // recorded after the last stream-ordered use of `scratch` (qk_rope_pos)
+    bool scratch_event_recorded = false;
     void* iq_grids[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // device copies of the caller's i-quant codebooks
     std::mutex mu;  // guards scratch growth and the host-slice calls
     mutable std::mutex err_mu;
