@@ -62,8 +62,11 @@ __device__ __forceinline__ void store_h_copy(void* base, int h_dtype, size_t ele
 // usual case); otherwise through the type-switching loader. Arithmetic is packed f32x2 throughout: the same bits
 // as scalar round-to-nearest operations at half the instruction count (the kernel is as much issue-bound as
 // memory-bound: two loads and two stores per thread against some hundred instructions).
+#ifndef LOKAL_NORM_WARP_MIN_CTAS
+#define LOKAL_NORM_WARP_MIN_CTAS 1  // resident 256-thread CTAs per SM the warp-per-row shape is compiled for
+#endif
 template <typename T, int VPT, bool CTA_MODE, bool WSAME>
-__global__ void __launch_bounds__(CTA_MODE ? 1024 : 256) norm_rows_kernel(const NormArgs a) {
+__global__ void __launch_bounds__(CTA_MODE ? 1024 : 256, CTA_MODE ? 1 : LOKAL_NORM_WARP_MIN_CTAS) norm_rows_kernel(const NormArgs a) {
     pdl_launch();
     constexpr int N = VecOf<T>::N, P = N / 2;
     const unsigned tpr = CTA_MODE ? blockDim.x : 32u;
