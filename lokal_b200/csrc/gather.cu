@@ -287,12 +287,14 @@ __device__ __forceinline__ float dequant_any_elem(const Rd& rd, const void* grid
 // word. The values and the order of the rounded f32 operations are those of dequant_elem above, arm by arm;
 // integers become floats through byte_plus_2p23, products and sums go through the packed f32x2 instructions.
 // `lut` is the IQ4 codebook as 16 floats in shared memory (one bank each, so a warp's lookups never conflict).
-template <int QT, int EPL>
+// AT_BLOCK (32-element block types only): `row` already points at the block and e < 32 is the offset inside it; the
+// kernel then advances the pointer by a constant per step instead of recomputing (e >> 5) * block_bytes.
+template <int QT, int EPL, bool AT_BLOCK = false>
 __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned e, const float* lut, float2 (&y)[EPL / 2]) {
     constexpr int W = EPL / 4;
     constexpr float k2p23 = 8388608.0f;
     if constexpr (QT == LOKAL_Q8_0) {
-        const unsigned char* b = row + (e >> 5) * 34;
+        const unsigned char* b = AT_BLOCK ? row : row + (e >> 5) * 34;
         const float2 dd = both(lds_f16(b)), nb = both(-(k2p23 + 128.0f));
 #pragma unroll
         for (int w = 0; w < W; w++) {
@@ -303,7 +305,7 @@ __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned 
         }
     } else if constexpr (QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL || QT == LOKAL_Q5_0) {
         constexpr unsigned BB = QT == LOKAL_Q5_0 ? 22 : 18, QS = QT == LOKAL_Q5_0 ? 6 : 2;
-        const unsigned char* b = row + (e >> 5) * BB;
+        const unsigned char* b = AT_BLOCK ? row : row + (e >> 5) * BB;
         const unsigned j = e & 31, shift = (j & 16) ? 4u : 0u;
         const float2 dd = both(lds_f16(b));
         unsigned qh = 0;
@@ -622,11 +624,23 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
             for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) store_out16<OutT>(orow + e, z);
         } else {
             const unsigned char* row = stage_ptr(s) + ((state >> (8 + 4 * s)) & 15u);
-            for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
-                float2 y[EPL / 2];
-                if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
-                else decode_block<QT, EPL>(row, e, lut, y);
-                store_out16<OutT>(orow + e, y);
+            constexpr unsigned kSmallBlock = QT == LOKAL_Q8_0 ? 34u : (QT == LOKAL_Q5_0 ? 22u : ((QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL) ? 18u : 0u));
+            if constexpr (kSmallBlock != 0) {
+                // 32-element blocks: a lane's offset inside its block never changes, and every step moves it EPL blocks on
+                const unsigned char* bp = row + ((lane * EPL) >> 5) * kSmallBlock;
+                const unsigned in_block = (lane * EPL) & 31u;
+                for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL, bp += EPL * kSmallBlock) {
+                    float2 y[EPL / 2];
+                    decode_block<QT, EPL, true>(bp, in_block, lut, y);
+                    store_out16<OutT>(orow + e, y);
+                }
+            } else {
+                for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
+                    float2 y[EPL / 2];
+                    if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
+                    else decode_block<QT, EPL>(row, e, lut, y);
+                    store_out16<OutT>(orow + e, y);
+                }
             }
         }
         __syncwarp();  // every lane is done with stage s before it is refilled
