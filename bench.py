@@ -11,7 +11,11 @@ attention between them are out of scope, so their outputs are synthetic tensors,
 (several GB per step, far larger than L2). `value` times the step with inputs resident on the device (one CUDA graph
 per step); `e2e` times the same step through lokal_cuda_pass_run_host with all inputs in pinned host memory and the
 result copied back. Rows are sharded over GPUs with no collective on the path (weak scaling: every GPU gets a full
-batch). Rank 0 prints ONE JSON line.
+batch). Rank 0 prints ONE JSON line. `roofline.kernels` carries each kernel timed alone and, beside it, the driver's
+device-to-device copy of the same number of bytes launched the same way (`d2d_copy_same_bytes_us`).
+
+Other workloads: `--workload c4` (65,536 Zipf ids through every GGUF block type; `--only q8_0_f16,q4_k_f32` picks
+variants) and `--workload rows` (the neighbouring per-row ops and K/V staging).
 
 --impl reference times the reference's own CPU algorithm for the same step (the C++ restatement in oracle/, all host
 threads, f32 as the reference computes) on a bounded sample of the rows.
@@ -408,7 +412,40 @@ def ours(args, cfg, rank, world, local_rank):
             kern[name] = {"us_per_launch": 1e3 * avg, "us_best": 1e3 * min(times), "launches_timed": NL * len(times),
                           "bytes_per_launch": int(alg[name]), "gbs": alg[name] / (avg * 1e-3) / 1e9,
                           "warm_single_launch_us": 1e3 * float(np.median(singles))}
-        del xs, xn, inner, gout
+        # Calibration beside each figure: the driver's own device-to-device copy moving the same number of bytes
+        # (half read, half written), launched the same way (one graph of back-to-back copies over distinct memory).
+        # A kernel this short cannot be held to the bandwidth of a seconds-long copy; this is the size-matched bar.
+        src_flat, dst_flat = u.view(-1).view(torch.uint8), inner.view(-1).view(torch.uint8)
+        cs = torch.cuda.Stream(device=dev)
+        for name in ("add_rmsnorm", "qk_rope", "swiglu"):
+            chunk = (int(alg[name]) // 2) & ~255
+            n_copies = min(NL, src_flat.numel() // chunk)
+            if n_copies < 1:
+                continue
+            with torch.cuda.stream(cs):
+                def copies():
+                    for i in range(n_copies):
+                        dst_flat[i * chunk:(i + 1) * chunk].copy_(src_flat[i * chunk:(i + 1) * chunk], non_blocking=True)
+                copies()
+                cs.synchronize()
+                cg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(cg, stream=cs):
+                    copies()
+                ct = []
+                for rep in range(6):
+                    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a0.record(cs)
+                    cg.replay()
+                    a1.record(cs)
+                    cs.synchronize()
+                    if rep:
+                        ct.append(a0.elapsed_time(a1) / n_copies)
+                del cg
+            copy_us = 1e3 * float(np.mean(ct))
+            kern[name]["d2d_copy_same_bytes_us"] = copy_us
+            kern[name]["d2d_copy_same_bytes_gbs"] = 2 * chunk / (copy_us * 1e-6) / 1e9
+            kern[name]["speed_vs_d2d_copy"] = copy_us / kern[name]["us_per_launch"]
+        del xs, xn, inner, gout, src_flat, dst_flat
     torch.cuda.synchronize()
 
     # ---- end to end: host inputs in pinned memory, result back on the host ----
@@ -618,6 +655,8 @@ def gather_workload(args, rank, world, local_rank):
         if ty not in (L.Q8_0, L.Q4_K):
             dim = synth.C4_DIM_Q8 if synth.QUANT_GEOMETRY[ty][0] == 32 else synth.C4_DIM_Q4K
             variants.append((synth.QUANT_NAMES[ty] + "_f32", ty, dim, L.F32))
+    if args.only:  # a subset of the variants, e.g. for a profiler capture of one kernel
+        variants = [v for v in variants if v[0] in args.only.split(",")] or variants[:1]
     tables, kern = {}, {}
     O.build()
     threads = O.hardware_threads()
@@ -662,6 +701,9 @@ def gather_workload(args, rank, world, local_rank):
         kern[name]["bit_exact_vs_oracle_first_2048_rows"] = bool(np.array_equal(got.view(np.uint32), ref.view(np.uint32)))
         del outs
     # end to end: host ids in, host f32 rows out (Q8_0 -> f32, the configuration's first variant)
+    if (L.Q8_0, synth.C4_DIM_Q8) not in tables:
+        h8 = synth.q8_0_table(vocab, synth.C4_DIM_Q8, synth.C4_SEED + L.Q8_0)
+        tables[(L.Q8_0, synth.C4_DIM_Q8)] = (h8, torch.from_numpy(h8).to(dev))
     host, table = tables[(L.Q8_0, synth.C4_DIM_Q8)]
     ctx.host_embed_gather(table, L.Q8_0, vocab, synth.C4_DIM_Q8, ids_np)
     t0 = time.perf_counter()
@@ -678,7 +720,7 @@ def gather_workload(args, rank, world, local_rank):
         t0 = time.perf_counter()
         O.embed_gather(host, L.Q8_0, vocab, synth.C4_DIM_Q8, ids_np, threads=t)
         cpu[t] = n / (time.perf_counter() - t0)
-    first = kern["q8_0_f32"]
+    first = kern.get("q8_0_f32") or next(iter(kern.values()))
     line = {
         "metric": "embedding gather + GGUF row dequant, tokens/s", "value": first["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
         "steps": len(times) * reps_per_graph, "warmup": max(args.warmup, 3), "ms_per_step": first["us_per_launch"] * 1e-3,
@@ -804,6 +846,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures under a profiler)")
     ap.add_argument("--rows", type=int, default=0, help="override the token rows per GPU")
+    ap.add_argument("--only", default="", help="c4: comma-separated variant names to run (e.g. q8_0_f16)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
