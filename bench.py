@@ -821,6 +821,33 @@ def row_ops_workload(args, rank, world, local_rank):
     timed("kv_rows_windowed", T * 4, lambda b: ctx.kv_rows(idx, layout=lay, rows=T, pos0=20000, slot0=0, stream=stream))
     timed("kv_stage_f32_to_f16", T * (kvd * 6 + 4), lambda b: ctx.kv_stage(fresh[b], cache[b], src_dtype=L.F32, dst_dtype=L.F16, rows=T, width=kvd,
                                                                             dst_rows=idx, stream=stream))
+    del fresh, cache
+    # the deltanet conv over the whole chunk (10240 channels, 4 taps, window rolled at the end) and its gate scalars
+    CH, KC = 2 * HK * S + HV * S, 4
+    cx, cout = rnd(nbuf, T, CH), torch.empty(nbuf, T, CH, device=dev, dtype=torch.float32)
+    cstate, cw = rnd(CH, KC - 1), 0.5 * rnd(CH, KC)
+    timed("ssm_conv_chunk_f32", 2 * T * CH * 4, lambda b: ctx.ssm_conv(cstate, cx[b], cw, cout[b], channels=CH, d_conv=KC, n_tokens=T, stream=stream))
+    ref_out, _ = O.ssm_conv(np.ones((256, KC - 1), np.float32), cx[0, :8, :256].cpu().numpy(), cw[:256].cpu().numpy(), KC)
+    small = torch.empty(8, 256, device=dev, dtype=torch.float32)
+    ctx.ssm_conv(torch.ones(256, KC - 1, device=dev), cx[0, :8, :256].contiguous(), cw[:256].contiguous(), small, channels=256, d_conv=KC, n_tokens=8,
+                 roll=False, stream=stream)
+    ctx.stream_sync(stream)
+    kern["ssm_conv_chunk_f32"]["max_abs_err_vs_oracle"] = float(np.abs(small.cpu().numpy() - ref_out).max())
+    del cx, cout
+    hx = torch.randn(nbuf, T, CH, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    hout = torch.empty_like(hx)
+    timed("ssm_conv_chunk_bf16", 2 * T * CH * 2, lambda b: ctx.ssm_conv(cstate, hx[b], cw, hout[b], channels=CH, d_conv=KC, n_tokens=T, dtype=L.BF16, stream=stream))
+    del hx, hout
+    al, bi = rnd(nbuf, T, HV), rnd(nbuf, T, HV)
+    ga, gb, aw, dtb = torch.empty(nbuf, T, HV, device=dev), torch.empty(nbuf, T, HV, device=dev), -torch.exp(rnd(HV)), rnd(HV)
+    timed("delta_gates_f32", 4 * T * HV * 4, lambda b: ctx.delta_gates(al[b], bi[b], aw, dtb, ga[b], gb[b], n_v_heads=HV, n_tokens=T, stream=stream))
+    # the weight-page conversion of the low-memory stage-in: 64 Mi bf16 values to f16
+    PN = 64 << 20
+    page = torch.randn(2, PN, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    pout = torch.empty(2, PN, device=dev, dtype=torch.float16)
+    clip = torch.zeros(1, device=dev, dtype=torch.int32)
+    timed("bf16_to_f16_page", 4 * PN, lambda b: ctx.bf16_to_f16_copy(page[b % 2], pout[b % 2], n=PN, clip_flag=clip, stream=stream))
+    kern["bf16_to_f16_page"]["equals_torch_conversion"] = bool(torch.equal(pout[0], page[0].to(torch.float16)))
     first = kern["gated_output_norm_f32"]
     line = {
         "metric": "gated output norm rows/s", "value": T * HV / (first["us_per_launch"] * 1e-6), "unit": "rows/s", "n_gpus": 1,

@@ -351,6 +351,33 @@ LOKAL_API int lokal_cuda_attn_out_gate(lokal_cuda_ctx* ctx, lokal_cuda_stream s,
 LOKAL_API int lokal_cuda_split_q_gate(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* src, void* q, void* gate, size_t rows,
                                       size_t n_heads, size_t head_dim, int dtype);
 
+/* delta_gates (src/deltanet_ref.rs:48-58, 82-84; src/gpu/kernels.metal:3995-4015), one value per V head and token:
+ *   g[t][h]    = a[h] * softplus(alpha[t][h] + dt_bias[h])     softplus(x) = x > 20 ? x : log(1 + exp(x))
+ *   beta[t][h] = 1 / (1 + exp(-beta_in[t][h]))
+ * All f32, [n_tokens][n_v_heads]; a and dt_bias are [n_v_heads]. g may be alpha and beta may be beta_in. */
+LOKAL_API int lokal_cuda_delta_gates(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const float* alpha, const float* beta_in,
+                                     const float* a, const float* dt_bias, float* g, float* beta, size_t n_v_heads,
+                                     size_t n_tokens);
+
+/* Depthwise causal conv over the token axis, SiLU inside: conv_step (src/deltanet_ref.rs:91-112) applied to
+ * n_tokens rows in turn; one launch does what ssm_conv_decode / ssm_conv_prefill + ssm_conv_roll do
+ * (src/gpu/kernels.metal:3626-3665, 4039-4093).
+ *   acc = sum_{j<k-1} window[j] * w[c][j]  +  x[t][c] * w[c][k-1]      (f32, separate multiply and add, in this order)
+ *   out[t][c] = acc * (1 / (1 + exp(-acc)))
+ * window = the k-1 inputs before token t: rows of x, or entries of `state` for the first tokens.
+ * state: f32 [channels][d_conv-1], oldest first. With roll != 0 it is replaced, after every token has read it, by the
+ * window that follows the last token (the decode form always rolls; a prefill chunk rolls once at its end).
+ * x, out: [n_tokens][channels] in `dtype` (F32 / F16 / BF16), out must not be x. w: f32 [channels][d_conv].
+ * d_conv 1..8 (the reference refuses more taps). */
+LOKAL_API int lokal_cuda_ssm_conv(lokal_cuda_ctx* ctx, lokal_cuda_stream s, float* state, const void* x, const float* w,
+                                  void* out, size_t channels, size_t d_conv, size_t n_tokens, int dtype, int roll);
+
+/* bf16_to_f16_copy (src/gpu/kernels.metal:3572-3588), the weight-page conversion of the low-memory stage-in:
+ * bf16 bits widened exactly to f32, narrowed to f16 with round-to-nearest-even. clip_flag (device u32, may be
+ * NULL) is OR-ed with 1 when a finite value leaves the f16 range; the caller clears it. */
+LOKAL_API int lokal_cuda_bf16_to_f16_copy(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* src_bf16, void* dst_f16,
+                                          size_t n, uint32_t* clip_flag);
+
 /* ---- GGUF container reader -------------------------------------------------------
  * GgufFile (src/gguf/container.rs:152-384): v2/v3, little-endian, mapped read-only.
  * Host only. Enough to find token_embd.weight, norm weights and biases

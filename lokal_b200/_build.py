@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "liblokal_cuda.so")
-SOURCES = ["api.cu", "norm.cu", "rope.cu", "swiglu.cu", "gather.cu", "pass.cu", "kvstage.cu", "deltanet_rows.cu", "gguf_file.cu"]
+SOURCES = ["api.cu", "norm.cu", "rope.cu", "swiglu.cu", "gather.cu", "pass.cu", "kvstage.cu", "deltanet_rows.cu", "deltanet_tokens.cu", "gguf_file.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(HERE, "..", "include", "lokal_cuda.h")]
 
 NVCC_FLAGS = [

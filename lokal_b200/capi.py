@@ -135,6 +135,9 @@ SIGNATURES = {
     "lokal_cuda_gated_output_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _i]),
     "lokal_cuda_attn_out_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i]),
     "lokal_cuda_split_q_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
+    "lokal_cuda_delta_gates": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz]),
+    "lokal_cuda_ssm_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i, _i]),
+    "lokal_cuda_bf16_to_f16_copy": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "lokal_gguf_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p), C.c_char_p, _sz]),
     "lokal_gguf_close": (None, [_vp]),
     "lokal_gguf_last_error": (C.c_char_p, [_vp]),

@@ -236,6 +236,20 @@ class Context:
         """[q | gate] per head -> compact q and gate."""
         self._check(self._lib.lokal_cuda_split_q_gate(self._h, stream, _ptr(src), _ptr(q), _ptr(gate), rows, n_heads, head_dim, dtype))
 
+    def delta_gates(self, alpha, beta_in, a, dt_bias, g, beta, *, n_v_heads, n_tokens, stream=None):
+        """deltanet_ref::delta_gate / sigmoid per (token, V head): g = a * softplus(alpha + dt_bias), beta = sigmoid(beta_in)."""
+        self._check(self._lib.lokal_cuda_delta_gates(self._h, stream, _ptr(alpha), _ptr(beta_in), _ptr(a), _ptr(dt_bias), _ptr(g), _ptr(beta),
+                                                     n_v_heads, n_tokens))
+
+    def ssm_conv(self, state, x, w, out, *, channels, d_conv, n_tokens, dtype=F32, roll=True, stream=None):
+        """deltanet_ref::conv_step over n_tokens rows: depthwise causal conv + SiLU; `state` rolls when roll is set."""
+        self._check(self._lib.lokal_cuda_ssm_conv(self._h, stream, _ptr(state), _ptr(x), _ptr(w), _ptr(out), channels, d_conv, n_tokens, dtype,
+                                                  1 if roll else 0))
+
+    def bf16_to_f16_copy(self, src, dst, *, n, clip_flag=None, stream=None):
+        """bf16 bits -> f16 (nearest even); clip_flag (device u32) is OR-ed with 1 when a finite value overflows."""
+        self._check(self._lib.lokal_cuda_bf16_to_f16_copy(self._h, stream, _ptr(src), _ptr(dst), n, _ptr(clip_flag)))
+
     # -- host-slice mirrors of the reference's CPU signatures ----------------------
     def host_rmsnorm(self, x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
         """math::rmsnorm(x, weight, eps) -> new vector; x may be [dim] or [rows, dim]."""

@@ -368,6 +368,54 @@ ORACLE_API void lokal_ref_split_q_gate(const float* src, float* q, float* gate, 
         }
 }
 
+// softplus with ggml's shortcut (src/deltanet_ref.rs:48-50): x > 20 returns x unchanged.
+static inline float ref_softplus(float x) { return x > 20.0f ? x : std::log(1.0f + std::exp(x)); }
+ORACLE_API float lokal_ref_softplus(float x) { return ref_softplus(x); }
+
+// delta_gates (src/deltanet_ref.rs:82-84 per scalar; the batched addressing of src/gpu/kernels.metal:3995-4015):
+//   g[t][h] = a[h] * softplus(alpha[t][h] + dt_bias[h]);   beta[t][h] = sigmoid(beta_in[t][h])
+ORACLE_API void lokal_ref_delta_gates(const float* alpha, const float* beta_in, const float* a, const float* dt_bias, float* g,
+                                      float* beta, size_t n_v_heads, size_t n_tokens) {
+    for (size_t t = 0; t < n_tokens; t++)
+        for (size_t h = 0; h < n_v_heads; h++) {
+            const size_t i = t * n_v_heads + h;
+            g[i] = a[h] * ref_softplus(alpha[i] + dt_bias[h]);
+            beta[i] = ref_sigmoid(beta_in[i]);
+        }
+}
+
+// conv_step (src/deltanet_ref.rs:91-112) applied to n tokens in turn: depthwise causal conv over the rolling window
+// [state.., x] with separate multiply and add per tap, SiLU inside as x * sigmoid(x), the window rolled after the dot.
+// state: [channels][d_conv-1] oldest first (updated); x, out: [n][channels]; kernel: [channels][d_conv].
+ORACLE_API void lokal_ref_ssm_conv(float* state, const float* x, const float* kernel, float* out, size_t channels, size_t d_conv,
+                                   size_t n_tokens) {
+    const size_t k = d_conv;
+    for (size_t t = 0; t < n_tokens; t++)
+        for (size_t c = 0; c < channels; c++) {
+            float* st = state + c * (k - 1);
+            float acc = 0.0f;
+            for (size_t j = 0; j + 1 < k; j++) acc += st[j] * kernel[c * k + j];
+            const float xv = x[t * channels + c];
+            acc += xv * kernel[c * k + (k - 1)];
+            out[t * channels + c] = ref_silu_deltanet(acc);
+            if (k >= 2) {
+                for (size_t j = 0; j + 2 < k; j++) st[j] = st[j + 1];
+                st[k - 2] = xv;
+            }
+        }
+}
+
+// bf16_to_f16_copy (src/gpu/kernels.metal:3572-3588): bf16 bits widened exactly, narrowed to f16 nearest-even; the flag
+// is raised when a finite value leaves the f16 range.
+ORACLE_API void lokal_ref_bf16_to_f16(const uint16_t* src, size_t n, uint16_t* dst, uint32_t* clip) {
+    for (size_t i = 0; i < n; i++) {
+        const float v = bf16_to_f32(src[i]);
+        const uint16_t h = f32_to_f16(v);
+        if ((h & 0x7fffu) == 0x7c00u && !std::isinf(v)) *clip = 1u;
+        dst[i] = h;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // GGUF block formats (src/gguf/dequant.rs:21-41, 81-119)
 // ---------------------------------------------------------------------------

@@ -67,6 +67,10 @@ def lib() -> C.CDLL:
             "lokal_ref_gated_output_norm": (None, [vp, vp, vp, sz, sz, f32]),
             "lokal_ref_attn_out_gate": (None, [vp, vp, sz]),
             "lokal_ref_split_q_gate": (None, [vp, vp, vp, sz, sz, sz]),
+            "lokal_ref_softplus": (f32, [f32]),
+            "lokal_ref_delta_gates": (None, [vp, vp, vp, vp, vp, vp, sz, sz]),
+            "lokal_ref_ssm_conv": (None, [vp, vp, vp, vp, sz, sz, sz]),
+            "lokal_ref_bf16_to_f16": (None, [vp, sz, vp, vp]),
             "lokal_ref_set_iq_grid": (C.c_int, [C.c_int, vp, sz]),
             "lokal_ref_blk_elems": (sz, [u32]),
             "lokal_ref_blk_bytes": (sz, [u32]),
@@ -240,6 +244,39 @@ def split_q_gate(src, rows: int, heads: int, head_dim: int):
     gate = np.empty_like(q)
     lib().lokal_ref_split_q_gate(_p(src), _p(q), _p(gate), rows, heads, head_dim)
     return q, gate
+
+
+def softplus(x: float) -> float:
+    return float(lib().lokal_ref_softplus(x))
+
+
+def delta_gates(alpha, beta_in, a, dt_bias):
+    """alpha, beta_in: [n, H_v]; a, dt_bias: [H_v] -> (g, beta), both [n, H_v]."""
+    alpha, beta_in, a, dt_bias = _f32c(alpha), _f32c(beta_in), _f32c(a), _f32c(dt_bias)
+    assert alpha.shape == beta_in.shape and alpha.shape[-1] == a.size == dt_bias.size
+    g, beta = np.empty_like(alpha), np.empty_like(alpha)
+    lib().lokal_ref_delta_gates(_p(alpha), _p(beta_in), _p(a), _p(dt_bias), _p(g), _p(beta), a.size, alpha.size // a.size)
+    return g, beta
+
+
+def ssm_conv(state, x, kernel, d_conv: int):
+    """conv_step over the rows of x in turn. state: [C, d_conv-1]; x: [n, C]; kernel: [C, d_conv].
+    Returns (out [n, C], state after the last token)."""
+    state, x, kernel = _f32c(state).copy(), _f32c(x), _f32c(kernel)
+    n, ch = x.shape
+    assert state.size == ch * (d_conv - 1) and kernel.size == ch * d_conv
+    out = np.empty_like(x)
+    lib().lokal_ref_ssm_conv(_p(state), _p(x), _p(kernel), _p(out), ch, d_conv, n)
+    return out, state
+
+
+def bf16_to_f16(bits):
+    """bf16 bit patterns -> (f16 bit patterns, clip flag)."""
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    out = np.empty_like(bits)
+    clip = np.zeros(1, np.uint32)
+    lib().lokal_ref_bf16_to_f16(_p(bits), bits.size, _p(out), _p(clip))
+    return out, int(clip[0])
 
 
 # ---- gguf dequant ------------------------------------------------------------
