@@ -8,6 +8,8 @@
 // bf16_to_f16_copy (src/gpu/kernels.metal:3572-3588).
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace lokal {
 namespace {
 
@@ -58,7 +60,7 @@ struct ConvArgs {
     int write_state;   // only with a single token chunk per channel: the thread that read the window writes it back
 };
 
-// A thread owns N neighbouring channels and a run of tokens, and slides the window of the last k-1 inputs through
+// A thread owns N (four, or one) neighbouring channels and a run of tokens, and slides the window of the last k-1 inputs through
 // registers, so every input is read once (plus k-1 rows of overlap per run). The window is kept right-aligned in
 // KMAX-1 slots so that a tap count known only at run time still indexes registers statically. Channels are held in
 // pairs and the taps use the packed f32x2 multiply and add (each lane rounds as the scalar instruction does, and a
@@ -79,11 +81,27 @@ __global__ void __launch_bounds__(kConvThreads) ssm_conv_kernel(const ConvArgs a
     const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
     T* __restrict__ out = reinterpret_cast<T*>(a.out);
 
-    auto load_row = [&](unsigned t, float2 (&v)[P]) {
+    // a row's slice as loaded, before widening: one element, or four channels (16 bytes of f32, 8 bytes of a 16-bit type)
+    using Raw = typename std::conditional<N == 1, T, typename std::conditional<sizeof(T) == 4, uint4, uint2>::type>::type;
+    auto load_raw = [&](unsigned t) -> Raw {
         const T* p = x + static_cast<unsigned long long>(t) * C + c0;
-        if constexpr (N == 1) v[0] = make_float2(to_f32<T>(*p), 0.0f);
-        else unpack16p<T>(ld_stream(p), v);
+        if constexpr (N == 1) return *p;
+        else if constexpr (sizeof(T) == 4) return ld_stream(p);
+        else return *reinterpret_cast<const uint2*>(p);
     };
+    auto widen = [](const Raw& r, float2 (&v)[P]) {
+        if constexpr (N == 1) {
+            v[0] = make_float2(to_f32<T>(r), 0.0f);
+        } else if constexpr (sizeof(T) == 4) {
+            unpack16p<T>(r, v);
+        } else {
+            float2 four[4];
+            unpack16p<T>(make_uint4(r.x, r.y, 0u, 0u), four);
+            v[0] = four[0];
+            v[1] = four[1];
+        }
+    };
+    auto load_row = [&](unsigned t, float2 (&v)[P]) { widen(load_raw(t), v); };
     auto chan = [&](const float* base, unsigned stride, int pair, unsigned idx) {  // the two channels of a pair at base[c*stride + idx]
         const unsigned long long c = c0 + 2 * pair;
         return make_float2(base[c * stride + idx], N == 1 ? 0.0f : base[(c + (N == 1 ? 0 : 1)) * stride + idx]);
@@ -131,8 +149,15 @@ __global__ void __launch_bounds__(kConvThreads) ssm_conv_kernel(const ConvArgs a
             o[p].y = N == 1 ? 0.0f : silu(acc.y);
         }
         T* q = out + static_cast<unsigned long long>(t) * C + c0;
-        if constexpr (N == 1) *q = from_f32<T>(o[0].x);
-        else st_stream(q, pack16p<T>(o));
+        if constexpr (N == 1) {
+            *q = from_f32<T>(o[0].x);
+        } else if constexpr (sizeof(T) == 4) {
+            st_stream(q, pack16p<T>(o));
+        } else {
+            const float2 four[4] = {o[0], o[1], make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+            const uint4 w = pack16p<T>(four);
+            *reinterpret_cast<uint2*>(q) = make_uint2(w.x, w.y);
+        }
 #pragma unroll
         for (int s = 0; s + 1 < KMAX - 1; s++) {
 #pragma unroll
@@ -144,16 +169,33 @@ __global__ void __launch_bounds__(kConvThreads) ssm_conv_kernel(const ConvArgs a
         }
     };
 
-    // Whole batches of kBatch tokens run without a branch: all loads of a batch are issued before the first one is
-    // used, and the arithmetic of its tokens can be interleaved. The last tokens of a run go one at a time.
+    // Whole batches of kBatch tokens run without a branch, and the loads of the next batch are issued (and held as
+    // loaded, not widened) before the current one is worked on, so a warp always has loads in flight while it
+    // computes. The last tokens of a run go one at a time.
     constexpr int kBatch = KT == 0 ? 2 : (sizeof(T) == 2 ? 2 * LOKAL_CONV_BATCH : LOKAL_CONV_BATCH);  // run-time tap counts hold 8 slots: short batches
     unsigned tb = t0;
-    for (; tb + kBatch <= t1; tb += kBatch) {
-        float2 xv[kBatch][P];
+    if (tb + kBatch <= t1) {
+        Raw cur[kBatch];
 #pragma unroll
-        for (int b = 0; b < kBatch; b++) load_row(tb + b, xv[b]);
+        for (int b = 0; b < kBatch; b++) cur[b] = load_raw(tb + b);
+        for (;;) {
+            const bool more = tb + 2 * kBatch <= t1;
+            Raw nxt[kBatch];
+            if (more) {
 #pragma unroll
-        for (int b = 0; b < kBatch; b++) one_token(tb + b, xv[b]);
+                for (int b = 0; b < kBatch; b++) nxt[b] = load_raw(tb + kBatch + b);
+            }
+#pragma unroll
+            for (int b = 0; b < kBatch; b++) {
+                float2 xr[P];
+                widen(cur[b], xr);
+                one_token(tb + b, xr);
+            }
+            tb += kBatch;
+            if (!more) break;
+#pragma unroll
+            for (int b = 0; b < kBatch; b++) cur[b] = nxt[b];
+        }
     }
     for (; tb < t1; tb++) {
         float2 xr[P];
@@ -201,27 +243,53 @@ __global__ void __launch_bounds__(256) ssm_conv_roll_kernel(const ConvArgs a) {
     }
 }
 
+// CTAs of `kernel` that fit on one SM (asked once per kernel).
+inline unsigned resident_ctas(void (*kernel)(const ConvArgs)) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, static_cast<int>(kConvThreads), 0) != cudaSuccess || n < 1) n = 1;
+    return static_cast<unsigned>(n);
+}
+
+// Tokens per thread. Long runs amortise the k-1 rows of overlap that every run re-reads; the grid should fill a whole
+// number of waves (a last wave that is a third full costs as much as a full one); short chunks should still fill the
+// GPU. The cost of a candidate is its number of waves times the rows a thread touches.
+inline unsigned pick_tokens_per_thread(unsigned n_tokens, unsigned ctas_x, unsigned slots, unsigned d_conv) {
+    const unsigned hi = LOKAL_CONV_TOKENS * 2, lo = 4;
+    if (n_tokens <= lo) return n_tokens;
+    unsigned best = lo;
+    double best_cost = 1e300;
+    for (unsigned tpt = lo; tpt <= hi && tpt <= n_tokens + 3; tpt++) {
+        const unsigned long long ctas = static_cast<unsigned long long>(ctas_x) * ((n_tokens + tpt - 1) / tpt);
+        const unsigned long long waves = (ctas + slots - 1) / slots;
+        // a wave that is not full still runs at the speed its CTAs can pull from memory: count at least half a wave
+        const double fill = static_cast<double>(ctas) / static_cast<double>(slots);
+        const double eff_waves = waves > 1 ? static_cast<double>(waves) : (fill < 0.5 ? 0.5 : 1.0);
+        const double cost = eff_waves * (tpt + 0.5 * (d_conv - 1));
+        if (cost < best_cost * 0.999) {
+            best_cost = cost;
+            best = tpt;
+        }
+    }
+    return best;
+}
+
 template <typename T>
 int launch_conv(lokal_cuda_ctx* ctx, cudaStream_t s, ConvArgs a, bool vec_ok, int roll) {
-    constexpr int N = VecOf<T>::N;
+    constexpr int N = 4;  // channels per thread on the vector path: 16 bytes of f32, 8 bytes of a 16-bit type
+    void (*kern)(const ConvArgs) = vec_ok ? (a.d_conv == 4 ? ssm_conv_kernel<T, N, 4> : ssm_conv_kernel<T, N, 0>)
+                                          : (a.d_conv == 4 ? ssm_conv_kernel<T, 1, 4> : ssm_conv_kernel<T, 1, 0>);
+    static unsigned per_sm[4] = {0, 0, 0, 0};  // per instantiation of this template, per variant
+    const int variant = (vec_ok ? 0 : 2) + (a.d_conv == 4 ? 0 : 1);
+    if (per_sm[variant] == 0) per_sm[variant] = resident_ctas(kern);
     const unsigned per_thread = vec_ok ? N : 1;
     const unsigned threads = a.channels / per_thread;
     const unsigned ctas_x = (threads + kConvThreads - 1) / kConvThreads;
-    // tokens per thread: long runs amortise the k-1 rows of overlap, short ones fill the GPU
-    unsigned tpt = LOKAL_CONV_TOKENS;
-    while (tpt > 4 && static_cast<unsigned long long>(ctas_x) * ((a.n_tokens + tpt - 1) / tpt) < 2ull * ctx->sm_count) tpt /= 2;
+    const unsigned tpt = pick_tokens_per_thread(a.n_tokens, ctas_x, per_sm[variant] * static_cast<unsigned>(ctx->sm_count), a.d_conv);
     const unsigned chunks = (a.n_tokens + tpt - 1) / tpt;
     if (chunks > 65535u) return ctx->fail(LOKAL_ERR_BAD_ARG, "ssm_conv: %u tokens are too many for one launch", a.n_tokens);
     a.tokens_per_thread = tpt;
     a.write_state = (roll && chunks == 1) ? 1 : 0;
-    const dim3 grid(ctas_x, chunks);
-    if (vec_ok) {
-        if (a.d_conv == 4) launch_k(ssm_conv_kernel<T, N, 4>, grid, kConvThreads, 0, s, a);
-        else launch_k(ssm_conv_kernel<T, N, 0>, grid, kConvThreads, 0, s, a);
-    } else {
-        if (a.d_conv == 4) launch_k(ssm_conv_kernel<T, 1, 4>, grid, kConvThreads, 0, s, a);
-        else launch_k(ssm_conv_kernel<T, 1, 0>, grid, kConvThreads, 0, s, a);
-    }
+    launch_k(kern, dim3(ctas_x, chunks), kConvThreads, 0, s, a);
     LOKAL_CHECK_LAUNCH(ctx, "ssm_conv_kernel");
     if (roll && chunks > 1 && a.d_conv > 1) {
         // every run of tokens has read the old window by the time this launch starts (stream order)
@@ -321,7 +389,8 @@ int lokal_cuda_ssm_conv(lokal_cuda_ctx* ctx, lokal_cuda_stream s, float* state, 
     a.channels = static_cast<unsigned>(channels);
     a.d_conv = static_cast<unsigned>(d_conv);
     a.n_tokens = static_cast<unsigned>(n_tokens);
-    const bool vec_ok = lokal::aligned_to(x, 16) && lokal::aligned_to(out, 16) && (channels * es) % 16 == 0;
+    const size_t vb = 4 * es;  // a thread's four channels
+    const bool vec_ok = lokal::aligned_to(x, vb) && lokal::aligned_to(out, vb) && (channels * es) % vb == 0;
     cudaStream_t st = static_cast<cudaStream_t>(s);
     switch (dtype) {
         case LOKAL_F32: return lokal::launch_conv<float>(ctx, st, a, vec_ok, roll);
