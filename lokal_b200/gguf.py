@@ -66,7 +66,7 @@ class GgufFile:
 
     def _wrap(self, t: GgufTensor) -> Tensor:
         buf = (C.c_uint8 * t.nbytes).from_address(t.data) if t.nbytes else (C.c_uint8 * 0)()
-        return Tensor(t.name.decode(), tuple(int(t.dims[i]) for i in range(t.n_dims)), int(t.ggml_type), int(t.data_offset),
+        return Tensor(t.name.decode(errors="replace"), tuple(int(t.dims[i]) for i in range(t.n_dims)), int(t.ggml_type), int(t.data_offset),
                       int(t.nbytes), np.frombuffer(buf, np.uint8))
 
     def tensors(self):

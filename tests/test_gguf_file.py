@@ -183,6 +183,59 @@ def test_metadata_accessors_and_tensor_bytes(tmp_path):
         assert emb.dims == (64, 64) and emb.nbytes == L.row_bytes(L.Q8_0, 64 * 64)
 
 
+def walk_everything(path):
+    """Open, then touch every accessor and every tensor's bytes; a damaged file may be refused (an error with a
+    message) or accepted, but what is accepted must be readable end to end."""
+    try:
+        g = GgufFile(path)
+    except L.LokalCudaError as e:
+        assert e.status in (E.ERR_FORMAT, E.ERR_IO, E.ERR_UNSUPPORTED) and e.message
+        return False
+    with g:
+        g.version, g.data_start
+        for t in g.tensors():
+            assert t.data.nbytes == t.nbytes
+            int(np.frombuffer(t.data, np.uint8).sum())  # every byte of the tensor is inside the mapping
+        for key in ("general.architecture", "qwen3.block_count", "tokenizer.ggml.tokens", "tokenizer.ggml.token_type",
+                    "recurrent_layers", "scores", "flag", "neg"):
+            for call in (g.get_usize, g.get_f32, g.get_str, g.get_arr_i64, g.get_arr_str):
+                try:
+                    call(key)
+                except L.LokalCudaError as e:
+                    assert e.status in (E.ERR_BAD_ARG, E.ERR_NOT_FOUND)
+    return True
+
+
+def test_damaged_headers_are_refused_or_read_safely(tmp_path):
+    """The reader's input is a file from outside. Every truncation of the header, every 8-byte field blown up to a huge
+    count, and 1500 seeded byte flips: the reader must answer with an error or a file it can walk, never read outside
+    the mapping (container.rs:248-288 bounds every tensor against the file length for the same reason)."""
+    p, _ = model_file(tmp_path, vocab=8, hidden=32, layers=1)
+    good = p.read_bytes()
+    with GgufFile(p) as g:
+        header = min(g.data_start + 64, len(good))  # the header and the first bytes of tensor data
+    q = tmp_path / "damaged.gguf"
+    assert walk_everything(p)
+    accepted = 0
+    for cut in range(0, header, 3):
+        q.write_bytes(good[:cut])
+        accepted += walk_everything(q)
+    for off in range(4, header - 8, 4):
+        for blow in (struct.pack("<Q", 0xFFFFFFFFFFFFFFFF), struct.pack("<Q", 1 << 40), struct.pack("<Q", 0x7FFFFFFF)):
+            bad = bytearray(good)
+            bad[off:off + 8] = blow
+            q.write_bytes(bytes(bad))
+            accepted += walk_everything(q)
+    rng = np.random.default_rng(2024)
+    for _ in range(1500):
+        bad = bytearray(good)
+        for _ in range(int(rng.integers(1, 4))):
+            bad[int(rng.integers(0, header))] = int(rng.integers(0, 256))
+        q.write_bytes(bytes(bad))
+        accepted += walk_everything(q)
+    assert accepted > 0  # some damage is harmless (a flipped byte inside a key name): those files must stay readable
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("embed_type", [L.Q8_0, L.Q6_K, L.Q4_K])
 def test_embedding_table_from_a_file_through_the_gather(tmp_path, ctx, dev, oracle, embed_type):
