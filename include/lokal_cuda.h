@@ -516,7 +516,9 @@ LOKAL_API int lokal_cuda_host_swiglu(lokal_cuda_ctx* ctx, const float* gate, con
  * mismatch, where the reference panics, returns LOKAL_ERR_BAD_ARG. */
 LOKAL_API int lokal_cuda_host_dequant_row(lokal_cuda_ctx* ctx, int ggml_type, const uint8_t* src, size_t src_len,
                                           float* out, size_t n);
-/* embed_gather with a DEVICE-resident table and host ids / host f32 output. */
+/* embed_gather with a DEVICE-resident table and host ids / host f32 output. ids and out may be ordinary memory
+ * (copied through pinned staging; a large result is pulled by several worker threads so that DMA and the CPU copy
+ * overlap) or page-locked memory from lokal_cuda_host_alloc / cudaHostAlloc, which the copy engines reach directly. */
 LOKAL_API int lokal_cuda_host_embed_gather(lokal_cuda_ctx* ctx, const void* table_dev, int ggml_type, size_t vocab,
                                            size_t dim, const uint32_t* ids, size_t n, float* out);
 

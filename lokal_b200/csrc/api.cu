@@ -2,8 +2,11 @@
 // the op entry points (thin validation + launch) and the host-slice mirrors of
 // the reference's CPU signatures. See include/lokal_cuda.h for the contract of
 // each function and the reference interface it replaces.
+#include <atomic>
 #include <cstring>
 #include <new>
+#include <thread>
+#include <vector>
 
 #include "common.cuh"
 
@@ -40,6 +43,61 @@ int ensure_staging(lokal_cuda_ctx* ctx, size_t bytes) {
     ctx->staging_bytes = 0;
     LOKAL_CUDA_TRY(ctx, cudaHostAlloc(&ctx->staging, want, cudaHostAllocDefault));
     ctx->staging_bytes = want;
+    return LOKAL_OK;
+}
+
+// Page-locked host memory that CUDA knows (cudaHostAlloc / cudaHostRegister): a copy engine can reach it directly.
+bool is_pinned_host(const void* p) {
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeHost;
+}
+
+// Device memory -> ordinary (pageable) host memory, for results too large to bounce through one staging copy and one
+// single-threaded memcpy: a few workers, each with its own stream and its own slice of the pinned staging block, pull
+// 4 MB chunks in turn, so the DMA of one chunk overlaps the CPU copy (and the page faults of a fresh destination) of
+// the others. `s` is the stream the producer kernel ran on.
+int d2h_pageable(lokal_cuda_ctx* ctx, cudaStream_t s, const char* dev, char* out, size_t bytes) {
+    constexpr size_t kChunk = 4u << 20;
+    const size_t chunks = (bytes + kChunk - 1) / kChunk;
+    unsigned hw = std::thread::hardware_concurrency();
+    unsigned workers = hw >= 16 ? 8 : (hw >= 4 ? hw / 2 : 1);
+    if (workers > chunks) workers = static_cast<unsigned>(chunks);
+    int rc = ensure_staging(ctx, workers * kChunk);
+    if (rc != LOKAL_OK) return rc;
+    if (!ctx->copy_ready) LOKAL_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->copy_ready, cudaEventDisableTiming));
+    for (unsigned w = 0; w < workers; w++)
+        if (!ctx->copy_streams[w]) LOKAL_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_streams[w], cudaStreamNonBlocking));
+    LOKAL_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_ready, s));
+    std::atomic<size_t> next{0};
+    std::atomic<int> first_error{static_cast<int>(cudaSuccess)};
+    auto work = [&](unsigned w) {
+        cudaError_t e = cudaSetDevice(ctx->device);
+        cudaStream_t cs = ctx->copy_streams[w];
+        char* slot = static_cast<char*>(ctx->staging) + w * kChunk;
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, ctx->copy_ready, 0);
+        while (e == cudaSuccess) {
+            const size_t c = next.fetch_add(1);
+            if (c >= chunks) break;
+            const size_t off = c * kChunk, sz = bytes - off < kChunk ? bytes - off : kChunk;
+            e = cudaMemcpyAsync(slot, dev + off, sz, cudaMemcpyDeviceToHost, cs);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
+            if (e == cudaSuccess) std::memcpy(out + off, slot, sz);
+        }
+        if (e != cudaSuccess) {
+            int want = static_cast<int>(cudaSuccess);
+            first_error.compare_exchange_strong(want, static_cast<int>(e));
+        }
+    };
+    std::vector<std::thread> pool;
+    for (unsigned w = 1; w < workers; w++) pool.emplace_back(work, w);
+    work(0);
+    for (std::thread& t : pool) t.join();
+    const cudaError_t e = static_cast<cudaError_t>(first_error.load());
+    if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "device-to-host copy failed: %s", cudaGetErrorString(e));
     return LOKAL_OK;
 }
 
@@ -112,6 +170,9 @@ void lokal_cuda_destroy(lokal_cuda_ctx* ctx) {
     if (!ctx) return;
     DeviceGuard guard(ctx->device);
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+    for (cudaStream_t cs : ctx->copy_streams)
+        if (cs) cudaStreamDestroy(cs);
+    if (ctx->copy_ready) cudaEventDestroy(ctx->copy_ready);
     if (ctx->scratch_event) cudaEventDestroy(ctx->scratch_event);
     if (ctx->err_word) cudaFree(ctx->err_word);
     if (ctx->err_word_host) cudaFreeHost(ctx->err_word_host);
@@ -512,19 +573,29 @@ int lokal_cuda_host_embed_gather(lokal_cuda_ctx* ctx, const void* table_dev, int
     std::lock_guard<std::mutex> g(ctx->mu);
     const size_t ib = (n * 4 + 255) & ~size_t(255), ob = n * dim * 4;
     int rc = ensure_scratch(ctx, ib + ob);
-    if (rc == LOKAL_OK) rc = ensure_staging(ctx, ib > ob ? ib : ob);
     if (rc != LOKAL_OK) return rc;
     cudaStream_t s = ctx->host_stream;
     char* d = static_cast<char*>(ctx->scratch);
-    std::memcpy(ctx->staging, ids, n * 4);
-    LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, ctx->staging, n * 4, cudaMemcpyHostToDevice, s));
+    // Page-locked caller buffers are reached by the copy engines directly; ordinary memory goes through pinned staging.
+    if (is_pinned_host(ids)) {
+        LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, ids, n * 4, cudaMemcpyHostToDevice, s));
+    } else {
+        rc = ensure_staging(ctx, ib);
+        if (rc != LOKAL_OK) return rc;
+        std::memcpy(ctx->staging, ids, n * 4);
+        LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, ctx->staging, n * 4, cudaMemcpyHostToDevice, s));
+    }
     rc = lokal::launch_gather(ctx, s, table_dev, ggml_type, vocab, dim, reinterpret_cast<const uint32_t*>(d), n, d + ib, LOKAL_F32);
     if (rc != LOKAL_OK) return rc;
-    LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->staging, d + ib, ob, cudaMemcpyDeviceToHost, s));
+    if (is_pinned_host(out)) {
+        LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(out, d + ib, ob, cudaMemcpyDeviceToHost, s));
+    } else {
+        LOKAL_CUDA_TRY(ctx, cudaStreamSynchronize(s));  // the staged ids have been consumed before staging is reused
+        rc = d2h_pageable(ctx, s, d + ib, reinterpret_cast<char*>(out), ob);
+        if (rc != LOKAL_OK) return rc;
+    }
     LOKAL_CUDA_TRY(ctx, cudaStreamSynchronize(s));
-    rc = read_error_word(ctx, s);
-    std::memcpy(out, ctx->staging, ob);
-    return rc;
+    return read_error_word(ctx, s);
 }
 
 }  // extern "C"

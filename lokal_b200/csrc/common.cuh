@@ -43,6 +43,8 @@ struct lokal_cuda_ctx {
     void* staging = nullptr;  // pinned host
     size_t staging_bytes = 0;
     cudaStream_t host_stream = nullptr;
+    cudaStream_t copy_streams[8] = {};  // device-to-host workers of the host-slice gather, created on first use
+    cudaEvent_t copy_ready = nullptr;
     cudaEvent_t scratch_event = nullptr;  // recorded after the last stream-ordered use of `scratch` (qk_rope_pos)
     bool scratch_event_recorded = false;
     void* iq_grids[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // device copies of the caller's i-quant codebooks

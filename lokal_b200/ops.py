@@ -284,9 +284,12 @@ class Context:
         self._check(self._lib.lokal_cuda_host_dequant_row(self._h, ggml_type, _ptr(src), src.size, _ptr(out), n))
         return out
 
-    def host_embed_gather(self, table_dev, ggml_type: int, vocab: int, dim: int, ids: np.ndarray) -> np.ndarray:
+    def host_embed_gather(self, table_dev, ggml_type: int, vocab: int, dim: int, ids: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
+        """Host ids in, host f32 rows out. `out` may be a caller-owned array (page-locked memory is written by DMA)."""
         ids = np.ascontiguousarray(ids, np.uint32)
-        out = np.empty((ids.size, dim), np.float32)
+        if out is None:
+            out = np.empty((ids.size, dim), np.float32)
+        assert out.dtype == np.float32 and out.flags.c_contiguous and out.size == ids.size * dim
         self._check(self._lib.lokal_cuda_host_embed_gather(self._h, _ptr(table_dev), ggml_type, vocab, dim, _ptr(ids),
                                                            ids.size, _ptr(out)))
         return out

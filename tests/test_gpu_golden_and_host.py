@@ -106,3 +106,28 @@ def test_host_embed_gather_mirror(ctx, dev, oracle):
     with pytest.raises(L.LokalCudaError) as e:
         ctx.host_embed_gather(dt, Q8_0, vocab, dim, np.array([1, vocab], np.uint32))
     assert e.value.status == L.capi.ERR_ID_RANGE
+
+
+def test_host_embed_gather_large_result_pageable_and_pinned(ctx, dev, oracle):
+    """A result of tens of MB: ordinary memory is filled by several worker threads pulling 4 MB chunks through pinned
+    staging, page-locked caller buffers are written by DMA. Both must be the oracle's rows bit for bit, tail included."""
+    import lokal_b200 as L
+    torch = dev.torch
+    vocab, dim, n = 2000, 896, 20011  # 71.7 MB of f32 rows, not a whole number of chunks
+    table = synth.q8_0_table(vocab, dim, 21)
+    ids = synth.token_ids_zipf(vocab, n, 22)
+    dt = dev.put(table)
+    want = oracle.embed_gather(table, Q8_0, vocab, dim, ids, threads=8)
+    synth.assert_bits_equal(ctx.host_embed_gather(dt, Q8_0, vocab, dim, ids), want, "pageable result")
+    pin_ids = torch.from_numpy(ids.view(np.int32)).pin_memory()
+    pin_out = torch.full((n + 1, dim), 7.0, dtype=torch.float32).pin_memory()
+    got = ctx.host_embed_gather(dt, Q8_0, vocab, dim, pin_ids.numpy().view(np.uint32), out=pin_out.numpy()[:n])
+    synth.assert_bits_equal(got, want, "pinned result")
+    assert (pin_out.numpy()[n] == 7.0).all(), "wrote past the caller's buffer"
+    # a small call afterwards still works (the staging block was regrown and is reused)
+    synth.assert_bits_equal(ctx.host_embed_gather(dt, Q8_0, vocab, dim, ids[:5]), want[:5], "small call after a large one")
+    with pytest.raises(L.LokalCudaError) as e:
+        bad = ids.copy()
+        bad[-1] = vocab
+        ctx.host_embed_gather(dt, Q8_0, vocab, dim, bad)
+    assert e.value.status == L.capi.ERR_ID_RANGE
