@@ -63,7 +63,10 @@ __device__ __forceinline__ float sigmoid_f32(float x) { return __frcp_rn(1.0f + 
 // per lane and issues every load of all of them before the first reduction. Measured at 128-wide f32 rows: four
 // rows per warp are slower than one (l2norm 52 vs 50 us, gated norm 168 vs 115 us for 8192 x 48 rows): the
 // registers they hold halve the resident warps and the f64 reductions of a warp's rows run one after another.
-constexpr int kRowsPerWarp = 1;
+#ifndef LOKAL_DELTANET_ROWS_PER_WARP
+#define LOKAL_DELTANET_ROWS_PER_WARP 1
+#endif
+constexpr int kRowsPerWarp = LOKAL_DELTANET_ROWS_PER_WARP;
 
 template <typename T, int VPT, int MODE>
 __global__ void __launch_bounds__(256) deltanet_rows_kernel(const RowNormArgs a) {
