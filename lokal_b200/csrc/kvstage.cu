@@ -56,31 +56,49 @@ __global__ void __launch_bounds__(256) kv_stage_kernel(const StageArgs a) {
     const unsigned long long orow = a.dst_rows ? static_cast<unsigned long long>(__ldg(a.dst_rows + r)) : r;
     D* dst = reinterpret_cast<D*>(a.dst) + orow * a.dst_stride;
     if (a.vec_ok) {
-        for (unsigned e = lane * 8; e < a.width; e += 256) {
-            float f[8];
-            if constexpr (sizeof(S) == 4) {
-                float t[4];
-                unpack16<float>(ld_stream(src + e), t);
+        // Up to four steps of a row (1024 elements per warp) are loaded before the first one is converted and stored,
+        // so a warp has the whole row of a usual KV width in flight at once.
+        constexpr int kSteps = 4;
+        constexpr int kVecs = sizeof(S) == 4 ? 2 : 1;  // 16-byte loads per lane step
+        for (unsigned e0 = lane * 8; e0 < a.width; e0 += 256 * kSteps) {
+            uint4 raw[kSteps][kVecs];
 #pragma unroll
-                for (int i = 0; i < 4; i++) f[i] = t[i];
-                unpack16<float>(ld_stream(src + e + 4), t);
+            for (int j = 0; j < kSteps; j++) {
+                const unsigned e = e0 + j * 256;
+                if (e < a.width) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) f[4 + i] = t[i];
-            } else {
-                float2 p[4];
-                unpack16p<S>(ld_stream(src + e), p);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    f[2 * i] = p[i].x;
-                    f[2 * i + 1] = p[i].y;
+                    for (int v = 0; v < kVecs; v++) raw[j][v] = ld_stream(src + e + v * 4);
                 }
             }
-            if constexpr (sizeof(D) == 4) {
-                const float lo[4] = {f[0], f[1], f[2], f[3]}, hi[4] = {f[4], f[5], f[6], f[7]};
-                st_stream(dst + e, pack16<float>(lo));
-                st_stream(dst + e + 4, pack16<float>(hi));
-            } else {
-                st_stream(dst + e, pack16<D>(f));
+#pragma unroll
+            for (int j = 0; j < kSteps; j++) {
+                const unsigned e = e0 + j * 256;
+                if (e >= a.width) break;
+                float f[8];
+                if constexpr (sizeof(S) == 4) {
+                    float t[4];
+                    unpack16<float>(raw[j][0], t);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) f[i] = t[i];
+                    unpack16<float>(raw[j][kVecs - 1], t);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) f[4 + i] = t[i];
+                } else {
+                    float2 p[4];
+                    unpack16p<S>(raw[j][0], p);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        f[2 * i] = p[i].x;
+                        f[2 * i + 1] = p[i].y;
+                    }
+                }
+                if constexpr (sizeof(D) == 4) {
+                    const float lo[4] = {f[0], f[1], f[2], f[3]}, hi[4] = {f[4], f[5], f[6], f[7]};
+                    st_stream(dst + e, pack16<float>(lo));
+                    st_stream(dst + e + 4, pack16<float>(hi));
+                } else {
+                    st_stream(dst + e, pack16<D>(f));
+                }
             }
         }
     } else {
