@@ -646,7 +646,7 @@ def gather_workload(args, rank, world, local_rank):
     ids = torch.from_numpy(ids_np.view(np.int32)).to(dev)
     stream = ctx.stream_create()
     tstream = torch.cuda.ExternalStream(stream, device=dev)
-    tdt = {L.F32: torch.float32, L.F16: torch.float16}
+    tdt = {L.F32: torch.float32, L.F16: torch.float16, L.BF16: torch.bfloat16}
     peak, peak_kind = measured_peak()
     variants = [("q8_0_f32", L.Q8_0, synth.C4_DIM_Q8, L.F32), ("q8_0_f16", L.Q8_0, synth.C4_DIM_Q8, L.F16),
                 ("q4_k_f32", L.Q4_K, synth.C4_DIM_Q4K, L.F32), ("q4_k_f16", L.Q4_K, synth.C4_DIM_Q4K, L.F16)]
@@ -655,6 +655,8 @@ def gather_workload(args, rank, world, local_rank):
         if ty not in (L.Q8_0, L.Q4_K):
             dim = synth.C4_DIM_Q8 if synth.QUANT_GEOMETRY[ty][0] == 32 else synth.C4_DIM_Q4K
             variants.append((synth.QUANT_NAMES[ty] + "_f32", ty, dim, L.F32))
+    # dense tables: the reference's own `embed` kernel reads an f16 table into f32 rows (src/gpu/kernels.metal:30)
+    variants += [("f16_table_f32", L.F16, synth.C4_DIM_Q8, L.F32), ("bf16_table_bf16", L.BF16, synth.C4_DIM_Q4K, L.BF16)]
     if args.only:  # a subset of the variants, e.g. for a profiler capture of one kernel
         variants = [v for v in variants if v[0] in args.only.split(",")] or variants[:1]
     tables, kern = {}, {}
@@ -667,7 +669,12 @@ def gather_workload(args, rank, world, local_rank):
     for name, ty, dim, odt in variants:
         if (ty, dim) not in tables:
             gen = {L.Q8_0: synth.q8_0_table, L.Q4_K: synth.q4_k_table}.get(ty)
-            host = gen(vocab, dim, synth.C4_SEED + ty) if gen else synth.quant_table(ty, vocab, dim, synth.C4_SEED + ty)
+            if ty in (L.F16, L.BF16):
+                dense = synth.f32_table(vocab, dim, synth.C4_SEED + ty)
+                host = dense.astype(np.float16).view(np.uint8).reshape(-1) if ty == L.F16 else \
+                    (synth.round_to(dense, L.BF16).view(np.uint32) >> 16).astype(np.uint16).view(np.uint8).reshape(-1)
+            else:
+                host = gen(vocab, dim, synth.C4_SEED + ty) if gen else synth.quant_table(ty, vocab, dim, synth.C4_SEED + ty)
             tables[(ty, dim)] = (host, torch.from_numpy(host).to(dev))
         host, table = tables[(ty, dim)]
         es = 4 if odt == L.F32 else 2
