@@ -17,6 +17,13 @@
 //   * deltanet siblings (l2_norm, f64-mean rmsnorm, gated_output_norm,
 //     attn_out_gate): pinned by src/deltanet_ref.rs:226-235, 306-329; sigmoid
 //     shares the libm caveat below.
+//   * deltanet per-token ops: softplus and the gate scalars pinned by
+//     src/deltanet_ref.rs:225-236 (the > 20 shortcut exactly, ln 2 at zero);
+//     conv_step by the hand vector and the rolled window of
+//     src/deltanet_ref.rs:289-303, and by agreeing bit for bit with a second,
+//     whole-chunk reading of the conv (tests/); the bf16 -> f16 page
+//     conversion by numpy's float16 over all 65,536 patterns. exp / log inside
+//     them share the libm caveat below.
 //   * rmsnorm / dot: pinned by src/math.rs:86-108 (dot tail vector, all-3s row).
 //   * RoPE and SiLU: PARITY UNPINNED at the libm boundary. The reference calls
 //     the platform libm (powf, sinf, cosf, expf) through Rust std and holds no
