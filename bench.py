@@ -10,9 +10,14 @@ for each layer qk-norm/bias + RoPE, two residual-add + RMSNorm, and SwiGLU (loka
 attention between them are out of scope, so their outputs are synthetic tensors, distinct per layer, resident in HBM
 (several GB per step, far larger than L2). `value` times the step with inputs resident on the device (one CUDA graph
 per step); `e2e` times the same step through lokal_cuda_pass_run_host with all inputs in pinned host memory and the
-result copied back. Rows are sharded over GPUs with no collective on the path (weak scaling: every GPU gets a full
-batch). Rank 0 prints ONE JSON line. `roofline.kernels` carries each kernel timed alone and, beside it, the driver's
-device-to-device copy of the same number of bytes launched the same way (`d2d_copy_same_bytes_us`).
+result copied back. The token rows of the batch are PARTITIONED over the GPUs with no collective on the path (strong
+scaling: at N GPUs every rank runs its contiguous share of the 8192 rows, as the configuration is stated);
+`--scaling weak` gives every GPU a full batch instead, and at N > 1 the weak figure is printed beside the strong one
+(`weak_tokens_per_s`). The timed region is `--blocks` blocks of K steps, each block bracketed by a barrier and timed
+with CUDA events on the launching stream, maximum over ranks per block; `value` is the median block. Rank 0 prints
+ONE JSON line. `roofline.kernels` carries each kernel timed alone and, beside it, the driver's device-to-device copy
+of the same number of bytes launched the same way (`d2d_copy_same_bytes_us`). At N = 1 the line also carries
+`configs`: the other benchmark configurations (C1-C3 steps, C4 gathers) measured briefly in the same run.
 
 Other workloads: `--workload c4` (65,536 Zipf ids through every GGUF block type; `--only q8_0_f16,q4_k_f32` picks
 variants) and `--workload rows` (the neighbouring per-row ops and K/V staging).
@@ -51,15 +56,18 @@ def env_int(name, default):
 
 
 def ncu_traffic(workload: str, kernel: str):
-    """DRAM bytes per launch of `kernel` from the committed ncu capture of this workload (profiles/), or None."""
+    """(DRAM bytes per launch of `kernel`, where and when they were captured) from the committed ncu capture of this
+    workload (profiles/ncu_traffic.json), or (None, None)."""
     p = os.path.join(ROOT, "profiles", "ncu_traffic.json")
     try:
         t = json.load(open(p))
         if t.get("workload") == workload:
-            return t["dram_bytes_per_launch"].get(kernel)
+            stamp = {"source": t.get("source"), "commit": t.get("captured_at_commit"),
+                     "kernel": (t.get("kernel_names") or {}).get(kernel)}
+            return t["dram_bytes_per_launch"].get(kernel), stamp
     except Exception:
         pass
-    return None
+    return None, None
 
 
 def measured_peak():
@@ -108,6 +116,8 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
         self._halt = threading.Event()
+        self._active = threading.Event()  # samples are taken only inside timed regions (see timed())
+        self._active.set()
         try:
             import pynvml
             import torch
@@ -130,6 +140,9 @@ class ClockSampler(threading.Thread):
         if not self.ok:
             return
         while not self._halt.is_set():
+            if not self._active.is_set():
+                self._active.wait(0.05)
+                continue
             try:
                 self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
                 try:
@@ -141,10 +154,17 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._halt.wait(0.002)  # the timed region is tens of milliseconds: sample every ~2 ms
+            self._halt.wait(0.001)  # the timed regions are tens of milliseconds: sample every millisecond or so
+
+    def pause(self):
+        self._active.clear()
+
+    def resume(self):
+        self._active.set()
 
     def finish(self):
         self._halt.set()
+        self._active.set()
         if self.is_alive():
             self.join(2)
         if not self.samples:
@@ -198,13 +218,22 @@ def cpu_step_fn(cfg, rows, table, vocab, seed=1):
     return run
 
 
+def shard_of(cfg, args, rank, world):
+    """(first row, rows) of this rank's share: a contiguous block of the batch (strong), or a whole batch (weak)."""
+    if args.scaling == "strong":
+        per = (cfg.rows + world - 1) // world  # the same split as lokal_cuda_shard_rows
+        r0 = min(cfg.rows, per * rank)
+        return r0, min(cfg.rows, r0 + per) - r0
+    return rank * cfg.rows, cfg.rows
+
+
 def reference_arm(args, cfg, rank, world):
     if rank != 0:
         return
     from oracle import lokal_oracle as O
     O.build()
     threads = O.hardware_threads()
-    vocab = min(cfg.vocab, 32768)  # the table only feeds one row per token; a smaller table keeps set-up short
+    vocab = cfg.vocab  # the full table, as the GPU arm
     table = synth.q8_0_table(vocab, cfg.hidden, cfg.seed)
     # calibrate on a small probe, then size the per-step sample for about 2 s of wall time
     probe_rows = min(cfg.rows, 4 * threads)
@@ -219,13 +248,14 @@ def reference_arm(args, cfg, rank, world):
     times = [step(threads) for _ in range(args.steps)]
     total = float(sum(times))
     value = rows * args.steps / total
-    sample = (f"{rows} of {cfg.rows} token rows per step, all {cfg.layers} layers, f32, {threads} threads "
-              f"(token-parallel; per-layer inputs cycle over 2 distinct layers of data)")
+    sample = (f"{rows} of {cfg.rows} token rows per step, all {cfg.layers} layers, f32, {threads} threads (token-parallel), "
+              f"Q8_0 table {vocab}x{cfg.hidden}; layer_period 2: the per-layer inputs cycle over 2 distinct layers of data "
+              f"({2 * rows * (cfg.q_dim + cfg.kv_dim + 2 * cfg.hidden + 2 * cfg.inter) * 4 / 1e6:.0f} MB, beyond the host caches)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, cfg.rows, args),
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, shard_of(cfg, args, 0, max(1, args.gpus))[1], args),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -233,16 +263,141 @@ def reference_arm(args, cfg, rank, world):
 
 
 def workload_config(cfg, rows_per_gpu, args):
-    return {"workload": cfg.name, "rows_per_gpu": rows_per_gpu, "layers": cfg.layers, "hidden": cfg.hidden,
+    """The same dictionary in both arms (the CPU arm's sampling is described in its cpu_baseline.sample)."""
+    return {"workload": cfg.name, "rows": cfg.rows, "rows_per_gpu": rows_per_gpu, "layers": cfg.layers, "hidden": cfg.hidden,
             "intermediate": cfg.inter, "q_heads": cfg.n_q_heads, "kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
             "qk_norm": cfg.qk_norm, "qk_bias": cfg.qk_bias, "embed_table": f"Q8_0 {cfg.vocab}x{cfg.hidden}",
-            "sharding": f"token rows over {args.gpus} GPU(s), no collective on the path",
-            "l2": "per-layer inputs and outputs are distinct buffers, several GB per step, far larger than the 126 MB L2"}
+            "sharding": f"token rows over {args.gpus} GPU(s) ({args.scaling} scaling), no collective on the path",
+            "l2": "inputs larger than L2: per-layer inputs and outputs are distinct buffers, never reused inside a step "
+                  "(GPU arm: every layer has its own, several GB per full batch; CPU arm: see cpu_baseline.sample)"}
 
 
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+
+class StepBench:
+    """One GPU's share of a layer-pass workload: weights, device-resident synthetic inputs (distinct per layer), the
+    pass object and one CUDA graph per schedule ("encode everything, submit once")."""
+
+    def __init__(self, L, ctx, cfg, T, r0, rank, dev, stream):
+        import torch
+        self.L, self.ctx, self.cfg, self.T, self.r0, self.dev, self.stream = L, ctx, cfg, T, r0, dev, stream
+        self.tdt = {L.F32: torch.float32, L.F16: torch.float16, L.BF16: torch.bfloat16}[cfg.dtype]
+        self.es = 2 if cfg.dtype != L.F32 else 4
+        H, I, QD, KD, NL = cfg.hidden, cfg.inter, cfg.q_dim, cfg.kv_dim, cfg.layers
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(cfg.seed + rank)
+        self.rn = lambda *shape, s=1.0: (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * s).to(self.tdt)
+        rn = self.rn
+        wrng = np.random.default_rng(cfg.seed)
+        wnp = lambda *shape, s=0.1, one=True: synth.round_to((1.0 if one else 0.0) + wrng.standard_normal(shape, dtype=np.float32) * np.float32(s), cfg.dtype)
+        as_bits = lambda a: (torch.from_numpy(a).to(self.tdt).contiguous())
+        self.table = synth.q8_0_table(cfg.vocab, H, cfg.seed)
+        self.weights = dict(norm_w=as_bits(wnp(NL, 2, H)), final_w=as_bits(wnp(H)))
+        if cfg.qk_bias:
+            self.weights.update(q_bias=as_bits(wnp(NL, QD, one=False)), k_bias=as_bits(wnp(NL, KD, one=False)))
+        if cfg.qk_norm:
+            self.weights.update(q_norm_w=as_bits(wnp(NL, cfg.head_dim)), k_norm_w=as_bits(wnp(NL, cfg.head_dim)))
+        self.common = dict(max_rows=T, layers=NL, hidden=H, inter=I, n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads,
+                           head_dim=cfg.head_dim, eps=cfg.eps, theta=cfg.theta, dtype=cfg.dtype, w_dtype=cfg.dtype,
+                           embed_type=L.Q8_0, vocab=cfg.vocab, embed_table=self.table, **self.weights)
+        self.pass_dev = L.LayerPass(ctx, slots=NL, **self.common)  # every layer's outputs go to their own buffers
+        self.q, self.k = rn(NL, T, QD), rn(NL, T, KD)
+        self.da, self.dm = rn(NL, T, H), rn(NL, T, H)
+        self.g, self.u = rn(NL, T, I, s=2.0), rn(NL, T, I, s=2.0)
+        self.ids_np = synth.token_ids_zipf(cfg.vocab, T, cfg.seed + rank)
+        self.ids = torch.from_numpy(self.ids_np.astype(np.int64)).to(dev).to(torch.int32)  # same bits as u32 for ids < 2^31
+        self.pos = None
+        if cfg.decode_positions:
+            self.pos = torch.randint(0, cfg.decode_positions, (T,), generator=gen, device=dev, dtype=torch.int32)
+        self.out = torch.empty(T, H, dtype=self.tdt, device=dev)
+        self.inp = L.LayerPass.inputs(ids=self.ids, rows=T, q=self.q, k=self.k, delta_att=self.da, delta_mlp=self.dm, gate=self.g,
+                                      up=self.u, positions=self.pos, pos0=r0, q_layer_stride=T * QD, k_layer_stride=T * KD,
+                                      delta_layer_stride=T * H, mlp_layer_stride=T * I)
+        torch.cuda.synchronize()
+        self.graphs = {}
+
+    def graph(self, schedule):
+        if schedule not in self.graphs:
+            self.pass_dev.set_schedule(schedule)
+            self.ctx.graph_begin(self.stream)
+            self.pass_dev.run_device(self.inp, self.out, stream=self.stream)
+            self.graphs[schedule] = self.ctx.graph_end(self.stream)
+            self.launches_per_step = self.pass_dev.launches
+        return self.graphs[schedule]
+
+    def step_bytes(self):
+        cfg, T, es = self.cfg, self.T, self.es
+        rb = self.L.row_bytes(self.L.Q8_0, cfg.hidden)
+        uniq = int(np.unique(self.ids_np).size)
+        gather = T * (4 + cfg.hidden * es) + uniq * rb
+        per_token_layer = 2 * 4 * cfg.hidden * es + (2 * (cfg.q_dim + cfg.kv_dim) * es + cfg.head_dim * 4) + 3 * cfg.inter * es
+        return cfg.layers * per_token_layer * T + gather + 2 * cfg.hidden * es * T + cfg.head_dim * 4 * T, gather
+
+    def time_blocks(self, schedule, steps, blocks, warmup, barrier, sampler=None):
+        """`blocks` timed blocks of `steps` graph launches, each between a barrier and a stream sync, timed with CUDA
+        events on the launching stream. Returns the per-block milliseconds of this rank."""
+        import torch
+        g = self.graph(schedule)
+        ts = torch.cuda.ExternalStream(self.stream, device=self.dev)
+        for _ in range(max(warmup, 3)):
+            self.ctx.graph_launch(g, self.stream)
+        self.ctx.stream_sync(self.stream)
+        out = []
+        for _ in range(blocks):
+            barrier()
+            if sampler:
+                sampler.resume()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ts)
+            for _ in range(steps):
+                self.ctx.graph_launch(g, self.stream)
+            e1.record(ts)
+            self.ctx.stream_sync(self.stream)
+            if sampler:
+                sampler.pause()
+            out.append(e0.elapsed_time(e1))
+        barrier()
+        return out
+
+    def close(self):
+        for g in self.graphs.values():
+            self.ctx.graph_destroy(g)
+        self.graphs = {}
+        self.pass_dev.close()
+
+
+def max_over_ranks(values, world, dev):
+    if world == 1:
+        return [float(v) for v in values]
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(values, device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def quick_configs(L, ctx, dev, stream, sampler, peak):
+    """The other benchmark configurations, briefly, for the default line: a C1 / C2 / C3 step (device-resident
+    inputs, one graph, median of 5 blocks of 20 steps) and the four C4 gathers the configuration names."""
+    import torch
+    out = {}
+    nobar = lambda: torch.cuda.synchronize()
+    for key in ("c1", "c2", "c3"):
+        cfg = synth.CONFIGS[key]
+        sb = StepBench(L, ctx, cfg, cfg.rows, 0, 0, dev, stream)
+        ms = float(np.median(sb.time_blocks(L.capi.PASS_SCHEDULE_AUTO, 20, 5, 3, nobar, sampler))) / 20
+        nbytes, _ = sb.step_bytes()
+        out[key] = {"workload": cfg.name, "rows": cfg.rows, "ms_per_step": ms, "tokens_per_s": cfg.rows / (ms * 1e-3),
+                    "launches_per_step": int(sb.launches_per_step), "step_hbm_gbs": nbytes / (ms * 1e-3) / 1e9,
+                    "step_frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+        sb.close()
+        del sb
+        torch.cuda.empty_cache()
+    out["c4"] = gather_variants(L, ctx, dev, stream, sampler, peak, ["q8_0_f32", "q8_0_f16", "q4_k_f32", "q4_k_f16"], warmup=3, reps=5)[0]
+    return out
+
 
 def ours(args, cfg, rank, world, local_rank):
     import torch
@@ -257,57 +412,11 @@ def ours(args, cfg, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ctx = L.Context(local_rank)
-    tdt = {L.F32: torch.float32, L.F16: torch.float16, L.BF16: torch.bfloat16}[cfg.dtype]
-    es = 2 if cfg.dtype != L.F32 else 4
-    T, H, I, QD, KD, NL = cfg.rows, cfg.hidden, cfg.inter, cfg.q_dim, cfg.kv_dim, cfg.layers
-    if args.scaling == "strong":
-        r0, T = L.shard_rows(cfg.rows, world, rank)
-    else:
-        r0 = rank * T  # weak scaling: rank r owns rows [r*T, (r+1)*T) of a world*T-row job
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(cfg.seed + rank)
-    rn = lambda *shape, s=1.0: (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * s).to(tdt)
-
-    # weights (host, uploaded once by the pass)
-    wrng = np.random.default_rng(cfg.seed)
-    wnp = lambda *shape, s=0.1, one=True: synth.round_to((1.0 if one else 0.0) + wrng.standard_normal(shape, dtype=np.float32) * np.float32(s), cfg.dtype)
-    as_bits = lambda a: (torch.from_numpy(a).to(tdt).contiguous())
-    vocab = cfg.vocab
-    table = synth.q8_0_table(vocab, H, cfg.seed)
-    weights = dict(norm_w=as_bits(wnp(NL, 2, H)), final_w=as_bits(wnp(H)))
-    if cfg.qk_bias:
-        weights.update(q_bias=as_bits(wnp(NL, QD, one=False)), k_bias=as_bits(wnp(NL, KD, one=False)))
-    if cfg.qk_norm:
-        weights.update(q_norm_w=as_bits(wnp(NL, cfg.head_dim)), k_norm_w=as_bits(wnp(NL, cfg.head_dim)))
-    common = dict(max_rows=T, layers=NL, hidden=H, inter=I, n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads,
-                  head_dim=cfg.head_dim, eps=cfg.eps, theta=cfg.theta, dtype=cfg.dtype, w_dtype=cfg.dtype,
-                  embed_type=L.Q8_0, vocab=vocab, embed_table=table, **weights)
-    pass_dev = L.LayerPass(ctx, slots=NL, **common)    # every layer's outputs go to their own buffers
-
-    # device-resident synthetic activations, distinct per layer
-    q = rn(NL, T, QD)
-    k = rn(NL, T, KD)
-    da = rn(NL, T, H)
-    dm = rn(NL, T, H)
-    g = rn(NL, T, I, s=2.0)
-    u = rn(NL, T, I, s=2.0)
-    ids_np = synth.token_ids_zipf(vocab, T, cfg.seed + rank)
-    ids = torch.from_numpy(ids_np.astype(np.int64)).to(dev).to(torch.int32)  # same bits as u32 for ids < 2^31
-    pos = None
-    if cfg.decode_positions:
-        pos = torch.randint(0, cfg.decode_positions, (T,), generator=gen, device=dev, dtype=torch.int32)
-    out = torch.empty(T, H, dtype=tdt, device=dev)
-    inp = L.LayerPass.inputs(ids=ids, rows=T, q=q, k=k, delta_att=da, delta_mlp=dm, gate=g, up=u, positions=pos, pos0=r0,
-                             q_layer_stride=T * QD, k_layer_stride=T * KD, delta_layer_stride=T * H, mlp_layer_stride=T * I)
-    torch.cuda.synchronize()
-
+    r0, T = shard_of(cfg, args, rank, world)
+    assert T > 0, "more GPUs than token rows"
+    H, I, QD, KD, NL = cfg.hidden, cfg.inter, cfg.q_dim, cfg.kv_dim, cfg.layers
     stream = ctx.stream_create()
     tstream = torch.cuda.ExternalStream(stream, device=dev)
-    # one CUDA graph per step ("encode everything, submit once")
-    ctx.graph_begin(stream)
-    pass_dev.run_device(inp, out, stream=stream)
-    graph = ctx.graph_end(stream)
-    launches_per_step = pass_dev.launches
 
     def barrier():
         torch.cuda.synchronize()
@@ -315,42 +424,28 @@ def ours(args, cfg, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        ctx.graph_launch(graph, stream)
-    ctx.stream_sync(stream)
-    barrier()
+    sb = StepBench(L, ctx, cfg, T, r0, rank, dev, stream)
+    tdt, es = sb.tdt, sb.es
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
+        sampler.pause()
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(tstream)
-    for _ in range(args.steps):
-        ctx.graph_launch(graph, stream)
-    e1.record(tstream)
-    ctx.stream_sync(stream)
-    barrier()
-    clocks = sampler.finish() if sampler else None
-    ms_total = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    total_rows = T * world
-    value = total_rows / (ms_step * 1e-3)
+    step_bytes, gather_bytes = sb.step_bytes()
 
     # ---- per-kernel timing on this GPU (rank 0 reports): L launches over distinct per-layer buffers ----
-    rb = L.row_bytes(L.Q8_0, H)
-    uniq = int(np.unique(ids_np).size)
+    rn, q, k, da, dm, g, u, ids, pos = sb.rn, sb.q, sb.k, sb.da, sb.dm, sb.g, sb.u, sb.ids, sb.pos
+    weights, table, vocab = sb.weights, sb.table, cfg.vocab
     alg = {
         "add_rmsnorm": 4 * H * es * T,
         "qk_rope": (2 * (QD + KD) * es + cfg.head_dim * 4) * T,
         "swiglu": 3 * I * es * T,
-        "embed_gather": T * (4 + H * es) + uniq * rb,
+        "embed_gather": gather_bytes,
     }
-    per_token_layer = 2 * 4 * H * es + (2 * (QD + KD) * es + cfg.head_dim * 4) + 3 * I * es
-    step_bytes = NL * per_token_layer * T + alg["embed_gather"] + 2 * H * es * T + cfg.head_dim * 4 * T
     kern = {}
+    ksampler = ClockSampler(local_rank) if rank == 0 else None  # clocks while the kernels are timed alone
+    if ksampler:
+        ksampler.pause()
+        ksampler.start()
     if rank == 0:
         xs = rn(NL, T, H)
         xn = torch.empty(NL, T, H, dtype=tdt, device=dev)
@@ -389,6 +484,8 @@ def ours(args, cfg, rank, world, local_rank):
             kg = ctx.graph_end(stream)
             times = []
             for rep in range(6):
+                if rep == 1:
+                    ksampler.resume()
                 a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a0.record(tstream)
                 ctx.graph_launch(kg, stream)
@@ -396,6 +493,7 @@ def ours(args, cfg, rank, world, local_rank):
                 ctx.stream_sync(stream)
                 if rep:  # first repetition is warm-up
                     times.append(a0.elapsed_time(a1) / NL)
+            ksampler.pause()
             ctx.graph_destroy(kg)
             avg = float(np.mean(times))
             # warm single launches, one at a time on layer 0's buffers (what survives of them in L2 is reused): not a
@@ -445,13 +543,31 @@ def ours(args, cfg, rank, world, local_rank):
             kern[name]["d2d_copy_same_bytes_us"] = copy_us
             kern[name]["d2d_copy_same_bytes_gbs"] = 2 * chunk / (copy_us * 1e-6) / 1e9
             kern[name]["speed_vs_d2d_copy"] = copy_us / kern[name]["us_per_launch"]
-        del xs, xn, inner, gout, src_flat, dst_flat
+        del xs, xn, inner, gout, src_flat, dst_flat, table_dev
     torch.cuda.synchronize()
+    kernel_clocks = ksampler.finish() if ksampler else None
+
+    SEQ, BR, AUTO = L.capi.PASS_SCHEDULE_SEQUENTIAL, L.capi.PASS_SCHEDULE_BRANCHES, L.capi.PASS_SCHEDULE_AUTO
+    sched = {"auto": AUTO, "sequential": SEQ, "branches": BR}[args.schedule]
+    # the headline: `blocks` blocks of K steps, maximum over ranks per block, median block
+    blocks_ms = max_over_ranks(sb.time_blocks(sched, args.steps, args.blocks, args.warmup, barrier, sampler), world, dev)
+    launches_per_step = sb.launches_per_step
+    clocks = sampler.finish() if sampler else None  # sampled inside the timed blocks only
+    ms_total = float(np.median(blocks_ms))
+    ms_step = ms_total / args.steps
+    total_rows = cfg.rows if args.scaling == "strong" else T * world
+    value = total_rows / (ms_step * 1e-3)
+    # the same step under each schedule (same kernels, same results; see lokal_cuda_pass_set_schedule)
+    by_schedule = {}
+    for name, sc in (("sequential", SEQ), ("branches", BR)):
+        ms = float(np.median(max_over_ranks(sb.time_blocks(sc, args.steps, 3, args.warmup, barrier), world, dev))) / args.steps
+        by_schedule[name] = {"ms_per_step": ms, "tokens_per_s": total_rows / (ms * 1e-3)}
 
     # ---- end to end: host inputs in pinned memory, result back on the host ----
     e2e = None
     if not args.no_e2e:
-        del pass_dev
+        common = sb.common
+        sb.close()
         pass_host = L.LayerPass(ctx, slots=min(3, NL), **common)
         pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
         hq, hk, hda, hdm, hg, hu = (pin(t) for t in (q, k, da, dm, g, u))
@@ -462,7 +578,7 @@ def ours(args, cfg, rank, world, local_rank):
                                  pos0=r0, q_layer_stride=T * QD, k_layer_stride=T * KD, delta_layer_stride=T * H,
                                  mlp_layer_stride=T * I)
         # the device arm rotated q/k in place on the device; the host copies above were taken after it, so both
-        # arms have seen the same kind of data. One untimed run, then a bitwise self-check of host vs device results.
+        # arms have seen the same kind of data. One untimed run first.
         pass_host.run_host(hin, hout)
         e2e_steps = max(2, min(args.steps, args.e2e_steps))
         barrier()
@@ -470,33 +586,67 @@ def ours(args, cfg, rank, world, local_rank):
         for _ in range(e2e_steps):
             pass_host.run_host(hin, hout)
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([dt], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t.item())
+        dt_own = time.perf_counter() - t0
+        dt = max_over_ranks([dt_own], world, dev)[0]
         h2d = T * 4 + (T * 4 if pos is not None else 0) + NL * T * (QD + KD + 2 * H + 2 * I) * es
+        # What bounds it: every rank ships its inputs over its own PCIe link, but the ranks of one box share the host's
+        # memory and PCIe root bandwidth; the per-GPU rate shows which of the two a run sat on.
         e2e = {"value": total_rows * e2e_steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(T * H * es), "steps": e2e_steps, "ms_per_step": 1e3 * dt / e2e_steps,
+               "h2d_gbs_per_gpu": h2d * e2e_steps / dt / 1e9, "h2d_gbs_all_gpus": world * h2d * e2e_steps / dt / 1e9,
+               "bound": "host-to-device copies (PCIe link per GPU; host memory / PCIe root shared by the ranks of a box)",
                "api": "lokal_cuda_pass_run_host (pinned host inputs, 3-slot layer ring, copies overlap kernels)"}
-        del pass_host
+        del pass_host, hq, hk, hda, hdm, hg, hu
+    else:
+        sb.close()
+    del q, k, da, dm, g, u
+    sb = None
+    torch.cuda.empty_cache()
+
+    # ---- at N > 1: the weak figure beside the strong one (every GPU runs a full batch of its own) ----
+    weak = None
+    if world > 1 and args.scaling == "strong" and not args.no_extras:
+        wb = StepBench(L, ctx, cfg, cfg.rows, rank * cfg.rows, rank, dev, stream)
+        wms = float(np.median(max_over_ranks(wb.time_blocks(AUTO, args.steps, 3, args.warmup, barrier), world, dev))) / args.steps
+        weak = {"tokens_per_s": cfg.rows * world / (wms * 1e-3), "ms_per_step": wms, "rows_per_gpu": cfg.rows}
+        wb.close()
+        del wb
+        torch.cuda.empty_cache()
 
     if rank == 0:
         peak, peak_kind = measured_peak()
+        configs = None
+        if world == 1 and not args.no_extras and args.workload == "c5" and not (args.layers or args.rows):
+            s2 = ClockSampler(local_rank)
+            s2.pause()
+            s2.start()
+            configs = quick_configs(L, ctx, dev, stream, s2, peak)
+            configs["clocks"] = s2.finish()
         dom = max(kern, key=lambda n: kern[n]["us_per_launch"] * (2 * NL if n == "add_rmsnorm" else (1 if n == "embed_gather" else NL)))
+        traffic, stamp = ncu_traffic(cfg.name, dom)
+        scale_t = T / cfg.rows  # the capture is of full-batch launches; traffic grows in proportion to the rows
         roof = {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}",
                 "unit": "GB/s", "frac": kern[dom]["gbs"] / peak, "frac_of_nominal_8000": kern[dom]["gbs"] / NOMINAL_HBM_GBS,
-                "traffic": ncu_traffic(cfg.name, dom),
+                "traffic": None if traffic is None else int(traffic * scale_t), "traffic_captured_at": stamp,
+                "clocks_while_kernels_timed_alone": kernel_clocks,
                 "kernels": {n: dict(v, frac=v["gbs"] / peak, frac_of_nominal_8000=v["gbs"] / NOMINAL_HBM_GBS) for n, v in kern.items()}}
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": {L.F32: "f32", L.F16: "f16", L.BF16: "bf16"}[cfg.dtype] + " storage, f32 arithmetic", "data": "synthetic",
-            "config": dict(workload_config(cfg, T, args), host_cpus_bound_to_gpu=bound_cpus),
+            "config": workload_config(cfg, T, args),
+            "blocks_ms_per_step": [b / args.steps for b in blocks_ms], "value_is": "median block of K steps, maximum over ranks per block",
+            "schedule": args.schedule, "by_schedule": by_schedule,
+            "host_cpus_bound_to_gpu": bound_cpus,
             "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9, "step_algorithmic_bytes": int(step_bytes),
             "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
             "roofline": roof, "clocks": clocks, "e2e": e2e,
         }
+        if weak:
+            line["weak_tokens_per_s"] = weak["tokens_per_s"]
+            line["weak"] = weak
+        if configs:
+            line["configs"] = configs
         if not args.no_cpu_baseline and world >= 1:
             line["cpu_baseline"] = cpu_baseline(cfg)
             line["parity"] = parity_gate(ctx, cfg, dev, stream, r0)
@@ -579,7 +729,7 @@ def cpu_baseline(cfg):
     from oracle import lokal_oracle as O
     O.build()
     threads = O.hardware_threads()
-    vocab = min(cfg.vocab, 32768)
+    vocab = cfg.vocab
     table = synth.q8_0_table(vocab, cfg.hidden, cfg.seed)
     probe_rows = min(cfg.rows, 4 * threads)
     probe = cpu_step_fn(cfg, probe_rows, table, vocab)
@@ -594,7 +744,8 @@ def cpu_baseline(cfg):
     one(1)
     t1 = one(1)
     return {"value": rows / float(np.median(times)), "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"{rows} of {cfg.rows} token rows, all {cfg.layers} layers, f32, median of 3 steps, {threads} token-parallel threads",
+            "sample": f"{rows} of {cfg.rows} token rows, all {cfg.layers} layers, f32, median of 3 steps, {threads} token-parallel threads, "
+                      f"Q8_0 table {vocab}x{cfg.hidden}, layer_period 2 (per-layer inputs cycle over 2 distinct layers of data)",
             "single_thread_value": max(1, rows // threads) / t1, "ops": cpu_ops(cfg, threads)}
 
 
@@ -628,26 +779,7 @@ def cpu_ops(cfg, threads, rows=None):
 # C4: embedding gather + GGUF row dequant on its own (65536 Zipf(1.1) ids over a 151936-row table)
 # ------------------------------------------------------------------------------------------------
 
-def gather_workload(args, rank, world, local_rank):
-    import torch
-
-    import lokal_b200 as L
-    from oracle import lokal_oracle as O
-
-    if rank != 0:
-        return
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    ctx = L.Context(local_rank)
-    vocab, n = synth.C4_VOCAB, synth.C4_IDS
-    ids_np = synth.token_ids_zipf(vocab, n, synth.C4_SEED)
-    uniq = int(np.unique(ids_np).size)
-    ids = torch.from_numpy(ids_np.view(np.int32)).to(dev)
-    stream = ctx.stream_create()
-    tstream = torch.cuda.ExternalStream(stream, device=dev)
-    tdt = {L.F32: torch.float32, L.F16: torch.float16, L.BF16: torch.bfloat16}
-    peak, peak_kind = measured_peak()
+def gather_variant_list(L):
     variants = [("q8_0_f32", L.Q8_0, synth.C4_DIM_Q8, L.F32), ("q8_0_f16", L.Q8_0, synth.C4_DIM_Q8, L.F16),
                 ("q4_k_f32", L.Q4_K, synth.C4_DIM_Q4K, L.F32), ("q4_k_f16", L.Q4_K, synth.C4_DIM_Q4K, L.F16)]
     # the other block types of the gather, f32 out: 32-element blocks at the Q8_0 width, 256-element ones at the Q4_K width
@@ -657,15 +789,29 @@ def gather_workload(args, rank, world, local_rank):
             variants.append((synth.QUANT_NAMES[ty] + "_f32", ty, dim, L.F32))
     # dense tables: the reference's own `embed` kernel reads an f16 table into f32 rows (src/gpu/kernels.metal:30)
     variants += [("f16_table_f32", L.F16, synth.C4_DIM_Q8, L.F32), ("bf16_table_bf16", L.BF16, synth.C4_DIM_Q4K, L.BF16)]
-    if args.only:  # a subset of the variants, e.g. for a profiler capture of one kernel
-        variants = [v for v in variants if v[0] in args.only.split(",")] or variants[:1]
-    tables, kern = {}, {}
+    return variants
+
+
+def gather_variants(L, ctx, dev, stream, sampler, peak, names, warmup, reps):
+    """Times the named C4 variants (65,536 Zipf ids, 151,936-row table), each as a graph of 16 launches over rotating
+    outputs, and checks the first 2048 rows of each bit for bit against the oracle. Returns (results, tables, ids)."""
+    import torch
+    from oracle import lokal_oracle as O
     O.build()
     threads = O.hardware_threads()
-    # the codebook types read the i-quant codebooks the caller hands over (the test fixture's copy of the format's tables)
-    grids = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests", "golden", "iq_grids.npz"))
-    ctx.set_iq_grids(grids)
-    O.set_iq_grids(grids)
+    vocab, n = synth.C4_VOCAB, synth.C4_IDS
+    ids_np = synth.token_ids_zipf(vocab, n, synth.C4_SEED)
+    uniq = int(np.unique(ids_np).size)
+    ids = torch.from_numpy(ids_np.view(np.int32)).to(dev)
+    tstream = torch.cuda.ExternalStream(stream, device=dev)
+    tdt = {L.F32: torch.float32, L.F16: torch.float16, L.BF16: torch.bfloat16}
+    variants = [v for v in gather_variant_list(L) if v[0] in names]
+    if any(v[1] in L.capi.GRID_TYPES for v in variants):
+        # the codebook types read the i-quant codebooks the caller hands over (the test fixture's copy of the format's tables)
+        grids = np.load(os.path.join(ROOT, "tests", "golden", "iq_grids.npz"))
+        ctx.set_iq_grids(grids)
+        O.set_iq_grids(grids)
+    tables, kern = {}, {}
     for name, ty, dim, odt in variants:
         if (ty, dim) not in tables:
             gen = {L.Q8_0: synth.q8_0_table, L.Q4_K: synth.q4_k_table}.get(ty)
@@ -686,27 +832,62 @@ def gather_workload(args, rank, world, local_rank):
             ctx.embed_gather(table, ids, outs[r % nbuf], ggml_type=ty, vocab=vocab, dim=dim, n=n, out_dtype=odt, stream=stream)
         g = ctx.graph_end(stream)
         times = []
-        for rep in range(max(args.warmup, 3) + max(3, min(args.steps, 10))):
+        for rep in range(warmup + reps):
+            if sampler and rep == warmup:
+                sampler.resume()
             a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a0.record(tstream)
             ctx.graph_launch(g, stream)
             a1.record(tstream)
             ctx.stream_sync(stream)
-            if rep >= max(args.warmup, 3):
+            if rep >= warmup:
                 times.append(a0.elapsed_time(a1) / reps_per_graph)
+        if sampler:
+            sampler.pause()
         ctx.graph_destroy(g)
         rb = L.row_bytes(ty, dim)
         alg = n * (4 + dim * es) + uniq * rb
         ms = float(np.mean(times))
         kern[name] = {"us_per_launch": 1e3 * ms, "tokens_per_s": n / (ms * 1e-3), "bytes_per_launch": int(alg),
                       "bytes_not_deduplicated": int(n * (rb + 4 + dim * es)), "gbs": alg / (ms * 1e-3) / 1e9,
-                      "frac": alg / (ms * 1e-3) / 1e9 / peak, "frac_of_nominal_8000": alg / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS}
+                      "frac": alg / (ms * 1e-3) / 1e9 / peak, "frac_of_nominal_8000": alg / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
+                      "launches_timed": len(times) * reps_per_graph}
         # bit-exact spot check against the oracle on the first 2048 ids, every run
         want = O.embed_gather(host, ty, vocab, dim, ids_np[:2048], threads=threads)
         got = outs[0][:2048].to(torch.float32).cpu().numpy()
         ref = want if odt == L.F32 else synth.round_to(want, odt)
         kern[name]["bit_exact_vs_oracle_first_2048_rows"] = bool(np.array_equal(got.view(np.uint32), ref.view(np.uint32)))
         del outs
+    return kern, tables, ids_np
+
+
+def gather_workload(args, rank, world, local_rank):
+    import torch
+
+    import lokal_b200 as L
+    from oracle import lokal_oracle as O
+
+    if rank != 0:
+        return
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = L.Context(local_rank)
+    vocab, n = synth.C4_VOCAB, synth.C4_IDS
+    stream = ctx.stream_create()
+    peak, peak_kind = measured_peak()
+    names = [v[0] for v in gather_variant_list(L)]
+    if args.only:  # a subset of the variants, e.g. for a profiler capture of one kernel
+        names = [v for v in names if v in args.only.split(",")] or names[:1]
+    sampler = ClockSampler(local_rank)
+    sampler.pause()
+    sampler.start()
+    warmup, reps = max(args.warmup, 3), max(3, min(args.steps, 10))
+    kern, tables, ids_np = gather_variants(L, ctx, dev, stream, sampler, peak, names, warmup, reps)
+    clocks = sampler.finish()
+    uniq = int(np.unique(ids_np).size)
+    threads = O.hardware_threads()
+    times, reps_per_graph = [0] * reps, 16
     # end to end: host ids in, host f32 rows out (Q8_0 -> f32, the configuration's first variant)
     if (L.Q8_0, synth.C4_DIM_Q8) not in tables:
         h8 = synth.q8_0_table(vocab, synth.C4_DIM_Q8, synth.C4_SEED + L.Q8_0)
@@ -747,10 +928,10 @@ def gather_workload(args, rank, world, local_rank):
         "config": {"workload": "gguf-gather-zipf65536", "vocab": vocab, "ids": n, "unique_ids": uniq,
                    "tables": "Q8_0 151936x896; Q4_K 151936x1024 (a 896-wide Q4_K row cannot exist: 256-element super-blocks)",
                    "l2": "outputs rotate over 8 buffers (up to 2.1 GB) between reuses"},
-        "gpu_launches": len(times) * reps_per_graph,
+        "gpu_launches": sum(v["launches_timed"] for v in kern.values()),
         "roofline": {"bound": "hbm", "kernel": "gather_quant_staged_kernel<Q8_0,f32>", "achieved": first["gbs"], "peak": peak,
                      "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": first["frac"], "traffic": None, "kernels": kern},
-        "e2e": e2e,
+        "clocks": clocks, "e2e": e2e,
         "cpu_baseline": {"value": cpu[threads], "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": f"all {n} ids, Q8_0 896-wide rows to f32", "single_thread_value": cpu[1]},
     }
@@ -779,6 +960,9 @@ def row_ops_workload(args, rank, world, local_rank):
     nbuf, reps = 6, 12
     rnd = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.float32)
     kern = {}
+    sampler = ClockSampler(local_rank)  # samples inside the timed loops only
+    sampler.pause()
+    sampler.start()
 
     def timed(name, alg_bytes, launch):
         ctx.graph_begin(stream)
@@ -787,6 +971,8 @@ def row_ops_workload(args, rank, world, local_rank):
         g = ctx.graph_end(stream)
         times = []
         for rep in range(max(args.warmup, 3) + max(3, min(args.steps, 10))):
+            if rep == max(args.warmup, 3):
+                sampler.resume()
             a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a0.record(tstream)
             ctx.graph_launch(g, stream)
@@ -794,6 +980,7 @@ def row_ops_workload(args, rank, world, local_rank):
             ctx.stream_sync(stream)
             if rep >= max(args.warmup, 3):
                 times.append(a0.elapsed_time(a1) / reps)
+        sampler.pause()
         ctx.graph_destroy(g)
         ms = float(np.mean(times))
         kern[name] = {"us_per_launch": 1e3 * ms, "bytes_per_launch": int(alg_bytes), "gbs": alg_bytes / (ms * 1e-3) / 1e9,
@@ -877,6 +1064,7 @@ def row_ops_workload(args, rank, world, local_rank):
         "gpu_launches": sum(k["launches_timed"] for k in kern.values()),
         "roofline": {"bound": "hbm", "kernel": "deltanet_rows_kernel<f32,1,gated>", "achieved": first["gbs"], "peak": peak,
                      "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": first["frac"], "traffic": None, "kernels": kern},
+        "clocks": sampler.finish(),
     }
     print(json.dumps(line), flush=True)
 
@@ -888,7 +1076,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(synth.CONFIGS) + ["c4", "rows"], default="c5")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
+                    help="strong: the batch's token rows are partitioned over the GPUs (the configuration as stated); weak: a full batch per GPU")
+    ap.add_argument("--blocks", type=int, default=5, help="timed blocks of --steps steps; value is the median block")
+    ap.add_argument("--schedule", choices=["auto", "sequential", "branches"], default="auto",
+                    help="how the pass orders the kernels of a step (lokal_cuda_pass_set_schedule)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the weak figure (N > 1) and the other configs (N = 1)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures under a profiler)")
     ap.add_argument("--rows", type=int, default=0, help="override the token rows per GPU")

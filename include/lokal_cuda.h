@@ -501,6 +501,19 @@ LOKAL_API int lokal_cuda_pass_run_host(lokal_cuda_ctx* ctx, lokal_cuda_pass* pas
 LOKAL_API int lokal_cuda_pass_output(lokal_cuda_ctx* ctx, lokal_cuda_pass* pass, uint32_t layer, int which, void** dptr);
 /* Kernels launched by the last run on this pass. */
 LOKAL_API uint64_t lokal_cuda_pass_launches(const lokal_cuda_pass* pass);
+/* How lokal_cuda_pass_run_device orders the kernels of a step. The reference encodes a step into one command
+ * buffer and submits once (src/gpu/metal.rs:2679-2681); its order is the order of Model::forward. Here all inputs
+ * of a step are given up front, so the data flow has three independent families: the residual-add + RMSNorm chain
+ * (through x), the q/k rotations (q, k and the table), and SwiGLU (gate, up, inner).
+ *   SEQUENTIAL  one stream, the order of Model::forward (src/model.rs:207-255)
+ *   BRANCHES    the three families on parallel branches forked from and joined into `s` (graph edges under capture),
+ *               the norm chain at the highest stream priority; same kernels, same results bit for bit, and the ramp
+ *               and drain of one family's kernels is covered by the others
+ *   AUTO        the library's choice (the default): BRANCHES, the shorter one at every batch size measured */
+#define LOKAL_PASS_SCHEDULE_AUTO 0
+#define LOKAL_PASS_SCHEDULE_SEQUENTIAL 1
+#define LOKAL_PASS_SCHEDULE_BRANCHES 3
+LOKAL_API int lokal_cuda_pass_set_schedule(lokal_cuda_ctx* ctx, lokal_cuda_pass* pass, int schedule);
 
 /* ---- Host-slice mirrors of the reference's CPU signatures ---------------------
  * Inputs and outputs are HOST memory; each call stages through buffers owned

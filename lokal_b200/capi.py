@@ -20,6 +20,9 @@ IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M = 16, 17, 18, 19, 21, 22, 2
 GRID_TYPES = (IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M)
 GRID_ORDER = ("iq2xxs", "iq2xs", "iq2s", "iq3xxs", "iq3s", "iq1s")  # index = lokal_iq_grid
 
+# lokal_cuda_pass_set_schedule
+PASS_SCHEDULE_AUTO, PASS_SCHEDULE_SEQUENTIAL, PASS_SCHEDULE_BRANCHES = 0, 1, 3
+
 # lokal_status
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_CUDA, ERR_ID_RANGE, ERR_TIMEOUT, ERR_NO_DEVICE = range(8)
 ERR_IO, ERR_FORMAT, ERR_NOT_FOUND = 8, 9, 10
@@ -161,6 +164,7 @@ SIGNATURES = {
     "lokal_cuda_pass_run_host": (_i, [_vp, _vp, C.POINTER(PassInputs), _vp]),
     "lokal_cuda_pass_output": (_i, [_vp, _vp, _u32, _i, _pp]),
     "lokal_cuda_pass_launches": (C.c_uint64, [_vp]),
+    "lokal_cuda_pass_set_schedule": (_i, [_vp, _vp, _i]),
     "lokal_cuda_host_rmsnorm": (_i, [_vp, _vp, _vp, _f, _sz, _sz, _vp]),
     "lokal_cuda_host_rope": (_i, [_vp, _vp, _sz, _sz, _sz, _f]),
     "lokal_cuda_host_swiglu": (_i, [_vp, _vp, _vp, _sz, _vp]),

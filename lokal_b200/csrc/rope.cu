@@ -185,7 +185,10 @@ struct RopeRow {
 
     // One pass: the head in slot `slot` (this lane group's head), raw halves in lo / hi. Every lane of the warp
     // must call this together (the reduction shuffles); lanes with live == false contribute zeros and store nothing.
-    __device__ __forceinline__ void pass(const QkArgs& a, unsigned slot, bool live, const uint4& lo, const uint4& hi) const {
+    // wra / wrb, when given, are this lane's norm weights for its two vectors, already in registers (the flat kernel);
+    // otherwise they are read from the staged copy in shared memory.
+    __device__ __forceinline__ void pass(const QkArgs& a, unsigned slot, bool live, const uint4& lo, const uint4& hi,
+                                         const float2* wra = nullptr, const float2* wrb = nullptr) const {
         const bool is_q = slot < a.n_q;
         float2 va[P], vb[P];
         if (live) {
@@ -231,10 +234,18 @@ struct RopeRow {
             const float* w = w_s + (is_q ? 0 : HD) + sub * 4;  // ones where a kind has no norm weights
 #pragma unroll
             for (int j = 0; j < N / 4; j++) {
-                const float4 wa = *reinterpret_cast<const float4*>(w + j * LPH * 4);
-                const float4 wb = *reinterpret_cast<const float4*>(w + HALF + j * LPH * 4);
-                const float2 wa0 = make_float2(wa.x, wa.y), wa1 = make_float2(wa.z, wa.w);
-                const float2 wb0 = make_float2(wb.x, wb.y), wb1 = make_float2(wb.z, wb.w);
+                float2 wa0, wa1, wb0, wb1;
+                if (wra) {
+                    wa0 = wra[2 * j];
+                    wa1 = wra[2 * j + 1];
+                    wb0 = wrb[2 * j];
+                    wb1 = wrb[2 * j + 1];
+                } else {
+                    const float4 wa = *reinterpret_cast<const float4*>(w + j * LPH * 4);
+                    const float4 wb = *reinterpret_cast<const float4*>(w + HALF + j * LPH * 4);
+                    wa0 = make_float2(wa.x, wa.y), wa1 = make_float2(wa.z, wa.w);
+                    wb0 = make_float2(wb.x, wb.y), wb1 = make_float2(wb.z, wb.w);
+                }
                 if (sizeof(T) == 2) {  // scale applied after the rotation
                     va[2 * j] = mul2(va[2 * j], wa0);
                     va[2 * j + 1] = mul2(va[2 * j + 1], wa1);
@@ -325,6 +336,57 @@ __global__ void __launch_bounds__(256, LOKAL_ROPE_MIN_CTAS) qk_rope_kernel(const
             for (int i = 0; i < kRopeInFlight; i++) fetch(c + i, lo[i], hi[i]);
         }
     }
+}
+
+// Flat variant for short launches (few rows per SM): one warp per (row, head group), one pass each, nothing staged and
+// no barrier. Every load of the warp (its two data vectors per lane, the row's cos/sin, the norm weights) is issued
+// before the first is consumed, and the whole launch is resident at once, so the kernel lasts one memory round trip
+// plus the arithmetic of a single pass. Same RopeRow arithmetic and results as the other two.
+template <typename T, int HD, int ROT, bool NORM, bool BIAS>
+__global__ void __launch_bounds__(256) qk_rope_flat_kernel(const QkArgs a) {
+    pdl_launch();
+    using R = RopeRow<T, HD, ROT, NORM, BIAS>;
+    constexpr int N = R::N, P = R::P;
+    const unsigned long long warp = (static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const unsigned long long row = warp / a.chunks;
+    if (row >= a.rows) return;  // whole warps leave together; there is no barrier below
+    const unsigned c = static_cast<unsigned>(warp % a.chunks);
+    const unsigned lane = threadIdx.x & 31u;
+    const unsigned sub = lane % R::LPH, slot = c * R::HPW + lane / R::LPH;
+    const bool live = slot < a.n_q + a.n_kv, is_q = slot < a.n_q;
+    const unsigned lo_off = R::lo_of(sub), hi_off = R::hi_of(sub);
+    const T* src = (is_q ? reinterpret_cast<const T*>(a.q) + row * a.q_stride + static_cast<size_t>(slot) * HD
+                         : reinterpret_cast<const T*>(a.k) + row * a.k_stride + static_cast<size_t>(slot - a.n_q) * HD) + lo_off;
+    if (a.prefetch && live) {  // one request per 128-byte line, while the kernel before this one drains
+        if ((reinterpret_cast<uintptr_t>(src) & 127u) == 0) prefetch_l2(src);
+        if ((reinterpret_cast<uintptr_t>(src + (hi_off - lo_off)) & 127u) == 0) prefetch_l2(src + (hi_off - lo_off));
+    }
+    pdl_wait();
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+    if (live) {
+        lo = ld_stream(src);
+        hi = ld_stream(src + (hi_off - lo_off));
+    }
+    float2 wa[P], wb[P];
+    if (NORM) {
+        const void* nw = is_q ? a.q_norm_w : a.k_norm_w;
+        if (nw && live) {
+            float fa[N], fb[N];
+            load_w<N>(nw, a.w_dtype, lo_off, a.w_vec_ok, fa);
+            load_w<N>(nw, a.w_dtype, hi_off, a.w_vec_ok, fb);
+#pragma unroll
+            for (int i = 0; i < P; i++) {
+                wa[i] = make_float2(fa[2 * i], fa[2 * i + 1]);
+                wb[i] = make_float2(fb[2 * i], fb[2 * i + 1]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < P; i++) wa[i] = wb[i] = make_float2(1.0f, 1.0f);
+        }
+    }
+    R r;
+    r.init(a, row, lane, nullptr);
+    r.pass(a, slot, live, lo, hi, NORM ? wa : nullptr, NORM ? wb : nullptr);
 }
 
 // Staged variant: one lane brings the whole row (its q heads, then its k heads) into shared memory with two bulk
@@ -488,6 +550,36 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     }
     const long forced = tune_env("LOKAL_CUDA_ROPE_WPR", 0);
     if (forced >= 1 && forced <= static_cast<long>(a.chunks)) wpr = static_cast<unsigned>(forced);
+    const bool norm = a.q_norm_w || a.k_norm_w, bias = a.q_bias || a.k_bias;
+    a.prefetch = prefetch_enabled();
+    // Few rows: the flat kernel, a warp per (row, head group). It takes over from the split register kernel wherever
+    // that one was used for want of rows (measured at 1024 rows of 24 heads of 128, bf16: see the launch notes in
+    // the kernel's header comment); LOKAL_CUDA_ROPE_FLAT=0 / 1 forces the choice.
+    const long flat_env = tune_env("LOKAL_CUDA_ROPE_FLAT", -1);
+    const bool flat = flat_env >= 0 ? flat_env != 0 : (wpr > 1 && forced == 0);
+    if (flat) {
+        const unsigned long long fwarps = a.rows * a.chunks;
+        const unsigned long long fblocks = (fwarps + 7) / 8;
+        if (fblocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many rows for one launch");
+        const unsigned fgrid = static_cast<unsigned>(fblocks);
+#define LOKAL_ROPE_LAUNCH_FLAT(HD_, ROT_)                                                          \
+    do {                                                                                           \
+        if (norm && bias) launch_k(qk_rope_flat_kernel<T, HD_, ROT_, true, true>, fgrid, 256, 0, s, a);  \
+        else if (norm) launch_k(qk_rope_flat_kernel<T, HD_, ROT_, true, false>, fgrid, 256, 0, s, a);    \
+        else if (bias) launch_k(qk_rope_flat_kernel<T, HD_, ROT_, false, true>, fgrid, 256, 0, s, a);    \
+        else launch_k(qk_rope_flat_kernel<T, HD_, ROT_, false, false>, fgrid, 256, 0, s, a);             \
+    } while (0)
+        switch (geom) {
+            case 64u * 1024u + 64u: LOKAL_ROPE_LAUNCH_FLAT(64, 64); break;
+            case 128u * 1024u + 128u: LOKAL_ROPE_LAUNCH_FLAT(128, 128); break;
+            case 128u * 1024u + 64u: LOKAL_ROPE_LAUNCH_FLAT(128, 64); break;
+            case 256u * 1024u + 64u: LOKAL_ROPE_LAUNCH_FLAT(256, 64); break;
+            default: LOKAL_ROPE_LAUNCH_FLAT(256, 256); break;
+        }
+#undef LOKAL_ROPE_LAUNCH_FLAT
+        LOKAL_CHECK_LAUNCH(ctx, "qk_rope_flat_kernel");
+        return LOKAL_OK;
+    }
     a.cpw = (a.chunks + wpr - 1) / wpr;
     a.wpr = (a.chunks + a.cpw - 1) / a.cpw;
     const unsigned long long warps = a.rows * a.wpr;
@@ -498,15 +590,16 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     const unsigned long long blocks = (warps + wpc - 1) / wpc;
     if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: too many rows for one launch");
     const unsigned grid = static_cast<unsigned>(blocks);
-    const bool norm = a.q_norm_w || a.k_norm_w, bias = a.q_bias || a.k_bias;
     a.q_row_bytes = a.n_q * a.head_dim * static_cast<unsigned>(sizeof(T));
     a.k_row_bytes = a.n_kv * a.head_dim * static_cast<unsigned>(sizeof(T));
     a.stage_bytes = (a.q_row_bytes + a.k_row_bytes + 127u) & ~127u;
     a.err_word = ctx->err_word;
-    a.prefetch = prefetch_enabled();
     // Staged kernel: whole rows through shared memory by bulk copy. Needs one warp per row, row starts that are
     // 16-byte aligned (true on this path) and a row small enough that several warps' stages fit in shared memory.
-    const bool staged_ok = a.wpr == 1 && a.stage_bytes <= 47u * 1024u && tune_env("LOKAL_CUDA_ROPE_STAGED", 1) != 0;
+    // The 48 KB a kernel gets without opting in covers its static shared memory too (the staged norm weights).
+    const unsigned static_smem = norm ? 2u * a.head_dim * 4u : 16u;
+    const unsigned dyn_budget = 48u * 1024u - static_smem;
+    const bool staged_ok = a.wpr == 1 && 128u + a.stage_bytes <= dyn_budget && tune_env("LOKAL_CUDA_ROPE_STAGED", 1) != 0;
     if (staged_ok) {
         // Rows per CTA: as many as fit in 48 KB, at most eight; rows above 12 KB are shared by two warps, above 24 KB
         // by four, so that a CTA still has several warps to work through its few wide rows.
@@ -514,7 +607,7 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
         while (a.swpr > a.chunks) a.swpr >>= 1;
         a.swpr_shift = a.swpr == 4 ? 2u : (a.swpr == 2 ? 1u : 0u);
         unsigned rpc = 8 / a.swpr;
-        while (rpc > 1 && 128u + rpc * a.stage_bytes > 48u * 1024u) rpc -= (rpc > 4 ? 4 : (rpc > 2 ? 2 : 1));
+        while (rpc > 1 && 128u + rpc * a.stage_bytes > dyn_budget) rpc -= (rpc > 4 ? 4 : (rpc > 2 ? 2 : 1));
         const unsigned swpc = rpc * a.swpr;  // warps per CTA
         const unsigned sgrid = static_cast<unsigned>((a.rows + rpc - 1) / rpc);
         const size_t smem = 128u + static_cast<size_t>(rpc) * a.stage_bytes;

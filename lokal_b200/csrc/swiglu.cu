@@ -35,7 +35,7 @@ struct SwigluArgs {
     int prefetch;  // ask L2 for the tile before waiting for the previous kernel
 };
 
-constexpr int kSwigluUnroll = 4;
+constexpr int kSwigluMaxUnroll = 4;
 
 template <typename T>
 __device__ __forceinline__ void swiglu_store(const SwigluArgs& a, uint4* o, unsigned long long v, const uint4& gv, const uint4& uv) {
@@ -61,12 +61,12 @@ __device__ __forceinline__ void swiglu_store(const SwigluArgs& a, uint4* o, unsi
     }
 }
 
-template <typename T>
+template <typename T, int kSwigluUnroll>
 __global__ void __launch_bounds__(256) swiglu_kernel(const SwigluArgs a) {
     pdl_launch();
-    // Each CTA owns a contiguous tile of kSwigluUnroll * 256 vectors (16 KB per stream); a thread's vectors are
-    // 256 apart, so every load instruction of a warp is one 512-byte run. Many small CTAs: the machine drains
-    // evenly at the end of the kernel. All 64-bit address arithmetic is done once per CTA.
+    // Each CTA owns a contiguous tile of kSwigluUnroll * 256 vectors (16 KB per stream at four vectors per thread);
+    // a thread's vectors are 256 apart, so every load instruction of a warp is one 512-byte run. Many small CTAs:
+    // the machine drains evenly at the end of the kernel. All 64-bit address arithmetic is done once per CTA.
     constexpr unsigned kTile = 256u * kSwigluUnroll;
     const unsigned long long tile0 = static_cast<unsigned long long>(blockIdx.x) * kTile;
     const uint4* g = reinterpret_cast<const uint4*>(a.gate) + tile0 + threadIdx.x;
@@ -129,10 +129,20 @@ int launch_typed(lokal_cuda_ctx* ctx, cudaStream_t s, SwigluArgs a, bool aligned
     constexpr unsigned N = VecOf<T>::N;
     a.nvec = aligned ? a.n / N : 0;
     if (a.nvec) {
-        const unsigned long long per_cta = 256ull * kSwigluUnroll;
+        // Vectors per thread: four while that still gives every SM eight CTAs (a long launch: fewer, fatter CTAs cost
+        // fewer instructions per byte); a short launch takes two or one, so that all of its loads are in flight at
+        // once across the whole machine instead of queueing behind a few CTAs per SM.
+        int unroll = kSwigluMaxUnroll;
+        const unsigned long long want_ctas = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
+        while (unroll > 1 && (a.nvec + 256ull * unroll - 1) / (256ull * unroll) < want_ctas) unroll >>= 1;
+        const long forced = tune_env("LOKAL_CUDA_SWIGLU_UNROLL", 0);
+        if (forced == 1 || forced == 2 || forced == 4) unroll = static_cast<int>(forced);
+        const unsigned long long per_cta = 256ull * unroll;
         const unsigned long long blocks = (a.nvec + per_cta - 1) / per_cta;
         if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "swiglu: too many elements for one launch");
-        launch_k(swiglu_kernel<T>, static_cast<unsigned>(blocks), 256, 0, s, a);
+        if (unroll == 4) launch_k(swiglu_kernel<T, 4>, static_cast<unsigned>(blocks), 256, 0, s, a);
+        else if (unroll == 2) launch_k(swiglu_kernel<T, 2>, static_cast<unsigned>(blocks), 256, 0, s, a);
+        else launch_k(swiglu_kernel<T, 1>, static_cast<unsigned>(blocks), 256, 0, s, a);
         LOKAL_CHECK_LAUNCH(ctx, "swiglu_kernel");
     }
     const unsigned long long first = a.nvec * N;

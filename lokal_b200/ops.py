@@ -343,6 +343,10 @@ class LayerPass:
     def run_host(self, inputs: PassInputs, out_host):
         self.ctx._check(self.ctx._lib.lokal_cuda_pass_run_host(self.ctx._h, self._h, C.byref(inputs), _ptr(out_host)))
 
+    def set_schedule(self, schedule: int):
+        """capi.PASS_SCHEDULE_AUTO / _SEQUENTIAL / _BRANCHES: how run_device orders the kernels of a step."""
+        self.ctx._check(self.ctx._lib.lokal_cuda_pass_set_schedule(self.ctx._h, self._h, schedule))
+
     def output(self, layer: int, which: int) -> int:
         p = C.c_void_p()
         self.ctx._check(self.ctx._lib.lokal_cuda_pass_output(self.ctx._h, self._h, layer, which, C.byref(p)))

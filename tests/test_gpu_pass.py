@@ -176,6 +176,52 @@ def test_graph_replay_equals_direct_run(ctx, dev, oracle):
     p.close()
 
 
+@pytest.mark.parametrize("captured", [False, True])
+def test_branch_schedule_equals_sequential_bitwise(ctx, dev, captured):
+    """The three op families on parallel branches (forked from and joined into the caller's stream) give the bits of
+    the one-stream order, run directly or replayed from a captured graph, for every per-layer output."""
+    import lokal_b200 as L
+    cfg, a = make_case(BF16, rows=333, layers=6, qk_norm=True, hd=128)
+    outs = {}
+    for sched in (L.capi.PASS_SCHEDULE_SEQUENTIAL, L.capi.PASS_SCHEDULE_BRANCHES):
+        p = build_pass(ctx, dev, cfg, a)
+        p.set_schedule(sched)
+        t = inputs_on("dev", dev, cfg, a)
+        out = dev.empty((cfg.rows, cfg.hidden), BF16, fill=0.0)
+        s = ctx.stream_create()
+        if captured:
+            ctx.graph_begin(s)
+            p.run_device(pass_inputs(cfg, t, 11), out, stream=s)
+            g = ctx.graph_end(s)
+            for _ in range(2):  # q/k are rotated in place: the second replay rotates again, identically in both schedules
+                ctx.graph_launch(g, s)
+            ctx.stream_sync(s)
+            ctx.graph_destroy(g)
+        else:
+            p.run_device(pass_inputs(cfg, t, 11), out, stream=s)
+            ctx.stream_sync(s)
+        got = {"out": dev.get(out), "q": dev.get(t["q"]), "k": dev.get(t["k"])}
+        for l in range(cfg.layers):
+            for which in (0, 1, 2):
+                width = cfg.inter if which == 2 else cfg.hidden
+                raw = np.empty(cfg.rows * width, np.uint16)
+                ctx.memcpy_d2h(raw, p.output(l, which), raw.nbytes)
+                ctx.stream_sync()
+                got[(l, which)] = raw
+        outs[sched] = got
+        ctx.stream_destroy(s)
+        p.close()
+    a_, b_ = outs[L.capi.PASS_SCHEDULE_SEQUENTIAL], outs[L.capi.PASS_SCHEDULE_BRANCHES]
+    for key in a_:
+        assert np.array_equal(a_[key].view(np.uint8), b_[key].view(np.uint8)), f"schedules differ in {key}"
+    with pytest.raises(L.LokalCudaError):
+        p2 = build_pass(ctx, dev, cfg, a)
+        try:
+            p2.set_schedule(7)
+        finally:
+            p2.close()
+
+
 def test_refusals(ctx, dev):
     import lokal_b200 as L
     cfg, a = make_case(F32, layers=2)

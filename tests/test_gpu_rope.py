@@ -263,6 +263,30 @@ def test_large_batches_staged_kernel_equals_register_kernel(ctx, dev, oracle, na
         synth.check_half(k1, rk, f"{name} k", cfg.dtype, atol=ROPE_HALF_ATOL)
 
 
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c5"])
+@pytest.mark.parametrize("rows", [1, 37, 700])
+def test_small_batches_flat_kernel_equals_register_kernel(ctx, dev, oracle, name, rows, monkeypatch):
+    # Few rows take the flat kernel (a warp per row and head group, nothing staged); LOKAL_CUDA_ROPE_FLAT=0 keeps the
+    # register kernel with the row split over several warps. Same arithmetic: bit for bit the same, and within the bar.
+    cfg = synth.CONFIGS[name]
+    d = synth.layer_inputs(cfg, rows)
+    q1, k1 = run_qk(ctx, dev, cfg, d, rows, pos0=4000)
+    monkeypatch.setenv("LOKAL_CUDA_ROPE_FLAT", "0")
+    q0, k0 = run_qk(ctx, dev, cfg, d, rows, pos0=4000)
+    monkeypatch.delenv("LOKAL_CUDA_ROPE_FLAT")
+    synth.assert_bits_equal(q1, q0, "flat vs register kernel, q")
+    synth.assert_bits_equal(k1, k0, "flat vs register kernel, k")
+    rq, rk = oracle.qk_rope_rows(d["q"], d["k"], n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
+                                 theta=cfg.theta, eps=cfg.eps, q_bias=d.get("q_bias"), k_bias=d.get("k_bias"),
+                                 q_norm_w=d.get("q_norm_w"), k_norm_w=d.get("k_norm_w"), positions=d.get("positions"), pos0=4000)
+    if cfg.dtype == F32:
+        synth.check_f32(q1, rq, f"{name} q")
+        synth.check_f32(k1, rk, f"{name} k")
+    else:
+        synth.check_half(q1, rq, f"{name} q", cfg.dtype, atol=ROPE_HALF_ATOL)
+        synth.check_half(k1, rk, f"{name} k", cfg.dtype, atol=ROPE_HALF_ATOL)
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_qwen35_partial_rope_large_batch(ctx, dev, oracle, dtype, monkeypatch):
     # head_dim 256 with 64 rotated dims, 24 q heads and 4 kv heads, per-head norm: the lane-mapped kernels
