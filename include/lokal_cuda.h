@@ -55,7 +55,8 @@ typedef enum lokal_status {
     LOKAL_ERR_NO_DEVICE = 7,   /* no usable CUDA device */
     LOKAL_ERR_IO = 8,          /* a file could not be opened or mapped */
     LOKAL_ERR_FORMAT = 9,      /* a GGUF file is malformed, truncated or of an unsupported version */
-    LOKAL_ERR_NOT_FOUND = 10   /* a tensor name or metadata key is not in the file */
+    LOKAL_ERR_NOT_FOUND = 10,  /* a tensor name or metadata key is not in the file */
+    LOKAL_ERR_POS_RANGE = 11   /* a position was negative or beyond the KV cache (its row was not stored) */
 } lokal_status;
 
 /* GGUF tensor type ids (src/gguf/dequant.rs:21-41; BF16 = 30 per ggml.h).
@@ -217,10 +218,14 @@ LOKAL_API int lokal_cuda_qk_rope(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const
  * Calls from several streams of one context are safe: each waits, on the
  * device, until the previous call's rope kernel has consumed the shared table
  * (so these short sections run one after another; sessions that want no such
- * coupling build their own table and call lokal_cuda_qk_rope). A call made
- * while `s` is being captured into a graph cannot take part in that hand-over:
- * keep other callers of this entry point off the context while such a graph
- * runs. */
+ * coupling build their own table and call lokal_cuda_qk_rope). The block is
+ * used by this entry point only (the host-slice mirrors below have their own).
+ * A call made while `s` is being captured into a graph cannot take part in that
+ * hand-over: keep other callers of this entry point off the context while such
+ * a graph runs. Nor can it allocate: if the block is smaller than the call needs
+ * it returns LOKAL_ERR_BAD_ARG (make one uncaptured call of that size first). A
+ * block whose address a captured graph holds is kept until the context is
+ * destroyed, also when a later, larger call replaces it, so replays stay valid. */
 LOKAL_API int lokal_cuda_qk_rope_pos(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_qk_rope_params* p,
                                      float theta, const int32_t* positions, int64_t pos0);
 
@@ -313,7 +318,12 @@ LOKAL_API int lokal_cuda_window_write_spans(const lokal_kv_layout* layout, uint6
 
 /* Cache row of every token row, on the device:
  *   linear:   slot_r * max_seq + pos_r            windowed: slot_r * (sink_pad + ring) + slot_of(pos_r)
- * positions / slots: device int32[rows] / uint32[rows], or NULL for pos0 + r / slot0. */
+ * positions / slots: device int32[rows] / uint32[rows], or NULL for pos0 + r / slot0.
+ * A position the cache cannot hold (negative; >= max_seq in the linear layout, which would be a row of the next
+ * slot; a row index beyond 32 bits) gets LOKAL_KV_ROW_NONE: lokal_cuda_kv_stage and lokal_cuda_qk_rope store nothing
+ * for such a row, and the next lokal_cuda_stream_sync returns LOKAL_ERR_POS_RANGE. The slot count is the caller's:
+ * a slot beyond the cache is not detectable here. */
+#define LOKAL_KV_ROW_NONE 0xFFFFFFFFu
 LOKAL_API int lokal_cuda_kv_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_kv_layout* layout,
                                  const int32_t* positions, int64_t pos0, const uint32_t* slots, uint32_t slot0,
                                  size_t rows, uint32_t* rows_out);

@@ -25,12 +25,13 @@ PASS_SCHEDULE_AUTO, PASS_SCHEDULE_SEQUENTIAL, PASS_SCHEDULE_BRANCHES = 0, 1, 3
 
 # lokal_status
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_MISALIGNED, ERR_CUDA, ERR_ID_RANGE, ERR_TIMEOUT, ERR_NO_DEVICE = range(8)
-ERR_IO, ERR_FORMAT, ERR_NOT_FOUND = 8, 9, 10
+ERR_IO, ERR_FORMAT, ERR_NOT_FOUND, ERR_POS_RANGE = 8, 9, 10, 11
+KV_ROW_NONE = 0xFFFFFFFF
 STATUS_NAMES = {
     OK: "LOKAL_OK", ERR_BAD_ARG: "LOKAL_ERR_BAD_ARG", ERR_UNSUPPORTED: "LOKAL_ERR_UNSUPPORTED",
     ERR_MISALIGNED: "LOKAL_ERR_MISALIGNED", ERR_CUDA: "LOKAL_ERR_CUDA", ERR_ID_RANGE: "LOKAL_ERR_ID_RANGE",
     ERR_TIMEOUT: "LOKAL_ERR_TIMEOUT", ERR_NO_DEVICE: "LOKAL_ERR_NO_DEVICE", ERR_IO: "LOKAL_ERR_IO",
-    ERR_FORMAT: "LOKAL_ERR_FORMAT", ERR_NOT_FOUND: "LOKAL_ERR_NOT_FOUND",
+    ERR_FORMAT: "LOKAL_ERR_FORMAT", ERR_NOT_FOUND: "LOKAL_ERR_NOT_FOUND", ERR_POS_RANGE: "LOKAL_ERR_POS_RANGE",
 }
 
 

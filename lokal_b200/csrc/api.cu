@@ -18,18 +18,46 @@ constexpr const char* kVersion = "lokal_cuda 0.1 (sm_100a)";
 
 cudaStream_t as_stream(lokal_cuda_stream s) { return static_cast<cudaStream_t>(s); }
 
-// Grow-only device scratch / pinned staging owned by the context.
+// Grow-only device blocks / pinned staging owned by the context.
+//
+// The table block of lokal_cuda_qk_rope_pos is used in stream order on the callers' streams. Growing it drains the
+// device first (work already queued may still read the old block). A block whose address a captured graph holds is
+// never freed while the context lives: it is set aside and a new one takes its place, so replays stay valid.
 int ensure_scratch(lokal_cuda_ctx* ctx, size_t bytes) {
     if (bytes <= ctx->scratch_bytes) return LOKAL_OK;
     size_t want = ctx->scratch_bytes ? ctx->scratch_bytes : (1u << 20);
     while (want < bytes) want *= 2;
-    // Work already queued may still read the old block: drain before replacing it.
     LOKAL_CUDA_TRY(ctx, cudaDeviceSynchronize());
-    if (ctx->scratch) LOKAL_CUDA_TRY(ctx, cudaFree(ctx->scratch));
+    if (ctx->scratch) {
+        if (ctx->scratch_in_graph) {
+            if (ctx->n_retired >= 8)
+                return ctx->fail(LOKAL_ERR_UNSUPPORTED, "qk_rope_pos: the table block has been captured into graphs and outgrown eight times; "
+                                                         "size it once with the largest call before capturing");
+            ctx->retired_scratch[ctx->n_retired++] = ctx->scratch;
+        } else {
+            LOKAL_CUDA_TRY(ctx, cudaFree(ctx->scratch));
+        }
+    }
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;
+    ctx->scratch_in_graph = false;
     LOKAL_CUDA_TRY(ctx, cudaMalloc(&ctx->scratch, want));
     ctx->scratch_bytes = want;
+    return LOKAL_OK;
+}
+
+// The host-slice mirrors have a block of their own: they run on host_stream, one call at a time (ctx->mu), and must
+// not touch the table block, which kernels queued on other streams may still be reading.
+int ensure_host_scratch(lokal_cuda_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->host_scratch_bytes) return LOKAL_OK;
+    size_t want = ctx->host_scratch_bytes ? ctx->host_scratch_bytes : (1u << 20);
+    while (want < bytes) want *= 2;
+    LOKAL_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->host_stream));
+    if (ctx->host_scratch) LOKAL_CUDA_TRY(ctx, cudaFree(ctx->host_scratch));
+    ctx->host_scratch = nullptr;
+    ctx->host_scratch_bytes = 0;
+    LOKAL_CUDA_TRY(ctx, cudaMalloc(&ctx->host_scratch, want));
+    ctx->host_scratch_bytes = want;
     return LOKAL_OK;
 }
 
@@ -109,6 +137,8 @@ int read_error_word(lokal_cuda_ctx* ctx, cudaStream_t s) {
     LOKAL_CUDA_TRY(ctx, cudaMemsetAsync(ctx->err_word, 0, sizeof(unsigned), s));
     LOKAL_CUDA_TRY(ctx, cudaStreamSynchronize(s));
     if (bits & lokal::kErrTimeout) return ctx->fail(LOKAL_ERR_TIMEOUT, "a device-side wait on a staged copy gave up");
+    if (bits & lokal::kErrPosRange)
+        return ctx->fail(LOKAL_ERR_POS_RANGE, "a position was negative or beyond the KV cache (its row was not stored)");
     return ctx->fail(LOKAL_ERR_ID_RANGE, "a token id was out of range for the table (its row was zero-filled)");
 }
 
@@ -177,6 +207,8 @@ void lokal_cuda_destroy(lokal_cuda_ctx* ctx) {
     if (ctx->err_word) cudaFree(ctx->err_word);
     if (ctx->err_word_host) cudaFreeHost(ctx->err_word_host);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (int i = 0; i < ctx->n_retired; i++) cudaFree(ctx->retired_scratch[i]);
+    if (ctx->host_scratch) cudaFree(ctx->host_scratch);
     if (ctx->staging) cudaFreeHost(ctx->staging);
     for (void* g : ctx->iq_grids)
         if (g) cudaFree(g);
@@ -394,16 +426,26 @@ int lokal_cuda_qk_rope_pos(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal
     if (p->rot_dim == 0 || p->rows > (SIZE_MAX / 4) / (p->rot_dim ? p->rot_dim : 1))
         return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope_pos: rot_dim/rows out of range");
     std::lock_guard<std::mutex> g(ctx->mu);
-    int rc = ensure_scratch(ctx, static_cast<size_t>(p->rows) * p->rot_dim * sizeof(float));
-    if (rc != LOKAL_OK) return rc;
-    // The table lives in scratch shared by every stream of the context. Sessions on different streams may call
+    // The table lives in a block shared by every stream of the context. Sessions on different streams may call
     // this concurrently, so each call first waits (on the device, in its own stream) for the previous call's rope
     // kernel to have consumed the table, and leaves an event behind for the next one. A stream under graph capture
     // cannot take part in that hand-over: a captured call relies on its caller to keep other users of this entry
     // point off the context while the graph runs (lokal_cuda_qk_rope with the caller's own table has no such limit).
+    // Nor can a captured call allocate or drain the device: it must find the block large enough already.
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     LOKAL_CUDA_TRY(ctx, cudaStreamIsCapturing(as_stream(s), &cap));
     const bool ordered = cap == cudaStreamCaptureStatusNone;
+    const size_t table_bytes = static_cast<size_t>(p->rows) * p->rot_dim * sizeof(float);
+    if (!ordered) {
+        if (table_bytes > ctx->scratch_bytes)
+            return ctx->fail(LOKAL_ERR_BAD_ARG,
+                             "qk_rope_pos: the stream is being captured and the table block (%zu bytes) is smaller than this call needs "
+                             "(%zu): make one uncaptured call of this size first, or pass your own table to lokal_cuda_qk_rope",
+                             ctx->scratch_bytes, table_bytes);
+        ctx->scratch_in_graph = true;
+    }
+    int rc = ensure_scratch(ctx, table_bytes);
+    if (rc != LOKAL_OK) return rc;
     if (ordered) {
         if (!ctx->scratch_event) LOKAL_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->scratch_event, cudaEventDisableTiming));
         if (ctx->scratch_event_recorded) LOKAL_CUDA_TRY(ctx, cudaStreamWaitEvent(as_stream(s), ctx->scratch_event, 0));
@@ -465,12 +507,12 @@ int lokal_cuda_host_rmsnorm(lokal_cuda_ctx* ctx, const float* x, const float* w,
     std::lock_guard<std::mutex> g(ctx->mu);
     // device scratch: [w | x | y], each part starting on a 256-byte boundary
     const size_t xb = rows * dim * 4, wb = (dim * 4 + 255) & ~size_t(255), xb_al = (xb + 255) & ~size_t(255);
-    int rc = ensure_scratch(ctx, wb + xb_al + xb);
+    int rc = ensure_host_scratch(ctx, wb + xb_al + xb);
     if (rc == LOKAL_OK) rc = ensure_staging(ctx, wb + xb);
     if (rc != LOKAL_OK) return rc;
     cudaStream_t s = ctx->host_stream;
     char* st = static_cast<char*>(ctx->staging);
-    char* d = static_cast<char*>(ctx->scratch);
+    char* d = static_cast<char*>(ctx->host_scratch);
     std::memcpy(st, w, dim * 4);
     std::memcpy(st + wb, x, xb);
     LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, st, wb + xb, cudaMemcpyHostToDevice, s));
@@ -491,11 +533,11 @@ int lokal_cuda_host_rope(lokal_cuda_ctx* ctx, float* x, size_t n, size_t pos, si
     if (n == 0) return LOKAL_OK;
     std::lock_guard<std::mutex> g(ctx->mu);
     const size_t xb = (n * 4 + 255) & ~size_t(255), tb = head_dim * 4;
-    int rc = ensure_scratch(ctx, xb + tb + 256);
+    int rc = ensure_host_scratch(ctx, xb + tb + 256);
     if (rc == LOKAL_OK) rc = ensure_staging(ctx, xb);
     if (rc != LOKAL_OK) return rc;
     cudaStream_t s = ctx->host_stream;
-    char* d = static_cast<char*>(ctx->scratch);
+    char* d = static_cast<char*>(ctx->host_scratch);
     std::memcpy(ctx->staging, x, n * 4);
     LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, ctx->staging, n * 4, cudaMemcpyHostToDevice, s));
     float* table = reinterpret_cast<float*>(d + xb);
@@ -523,12 +565,12 @@ int lokal_cuda_host_swiglu(lokal_cuda_ctx* ctx, const float* gate, const float* 
     if (n == 0) return LOKAL_OK;
     std::lock_guard<std::mutex> g(ctx->mu);
     const size_t b = (n * 4 + 255) & ~size_t(255);
-    int rc = ensure_scratch(ctx, 2 * b);
+    int rc = ensure_host_scratch(ctx, 2 * b);
     if (rc == LOKAL_OK) rc = ensure_staging(ctx, 2 * b);
     if (rc != LOKAL_OK) return rc;
     cudaStream_t s = ctx->host_stream;
     char* st = static_cast<char*>(ctx->staging);
-    char* d = static_cast<char*>(ctx->scratch);
+    char* d = static_cast<char*>(ctx->host_scratch);
     std::memcpy(st, gate, n * 4);
     std::memcpy(st + b, up, n * 4);
     LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, st, 2 * b, cudaMemcpyHostToDevice, s));
@@ -550,11 +592,11 @@ int lokal_cuda_host_dequant_row(lokal_cuda_ctx* ctx, int ggml_type, const uint8_
     if (n == 0) return LOKAL_OK;
     std::lock_guard<std::mutex> g(ctx->mu);
     const size_t sb = (src_len + 255) & ~size_t(255);
-    int rc = ensure_scratch(ctx, sb + n * 4);
+    int rc = ensure_host_scratch(ctx, sb + n * 4);
     if (rc == LOKAL_OK) rc = ensure_staging(ctx, sb > n * 4 ? sb : n * 4);
     if (rc != LOKAL_OK) return rc;
     cudaStream_t s = ctx->host_stream;
-    char* d = static_cast<char*>(ctx->scratch);
+    char* d = static_cast<char*>(ctx->host_scratch);
     std::memcpy(ctx->staging, src, src_len);
     LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, ctx->staging, src_len, cudaMemcpyHostToDevice, s));
     rc = lokal::launch_gather(ctx, s, d, ggml_type, 1, n, nullptr, 1, d + sb, LOKAL_F32);
@@ -572,10 +614,10 @@ int lokal_cuda_host_embed_gather(lokal_cuda_ctx* ctx, const void* table_dev, int
     if (n == 0) return LOKAL_OK;
     std::lock_guard<std::mutex> g(ctx->mu);
     const size_t ib = (n * 4 + 255) & ~size_t(255), ob = n * dim * 4;
-    int rc = ensure_scratch(ctx, ib + ob);
+    int rc = ensure_host_scratch(ctx, ib + ob);
     if (rc != LOKAL_OK) return rc;
     cudaStream_t s = ctx->host_stream;
-    char* d = static_cast<char*>(ctx->scratch);
+    char* d = static_cast<char*>(ctx->host_scratch);
     // Page-locked caller buffers are reached by the copy engines directly; ordinary memory goes through pinned staging.
     if (is_pinned_host(ids)) {
         LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(d, ids, n * 4, cudaMemcpyHostToDevice, s));

@@ -18,6 +18,7 @@
 #include <cstdlib>
 #include <mutex>
 #include <set>
+#include <vector>
 #include <utility>
 #include <string>
 
@@ -28,7 +29,7 @@ namespace lokal {
 constexpr int kSmCountB200 = 148;
 
 // Device-side error word bits (read back by lokal_cuda_stream_sync).
-enum : unsigned { kErrIdRange = 1u, kErrTimeout = 2u };
+enum : unsigned { kErrIdRange = 1u, kErrTimeout = 2u, kErrPosRange = 4u };
 
 }  // namespace lokal
 
@@ -37,9 +38,15 @@ struct lokal_cuda_ctx {
     int sm_count = lokal::kSmCountB200;
     unsigned* err_word = nullptr;      // device, 4 bytes
     unsigned* err_word_host = nullptr; // pinned, 4 bytes
-    // scratch for calls that build their own cos/sin table or stage host slices
+    // cos/sin table of lokal_cuda_qk_rope_pos, used in stream order on the caller's streams
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
+    bool scratch_in_graph = false;         // a captured graph holds the block's address: it is retired, not freed, on growth
+    void* retired_scratch[8] = {};         // such blocks, freed with the context
+    int n_retired = 0;
+    // device block of the host-slice mirrors (lokal_cuda_host_*), used on host_stream only, under `mu`
+    void* host_scratch = nullptr;
+    size_t host_scratch_bytes = 0;
     void* staging = nullptr;  // pinned host
     size_t staging_bytes = 0;
     cudaStream_t host_stream = nullptr;
@@ -400,9 +407,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
+// Polls before a wait gives up. LOKAL_CUDA_WAIT_LIMIT (read per launch) lowers it and LOKAL_CUDA_TEST_EXTRA_TX makes a
+// staged copy announce more bytes than it delivers, so that a test can watch a wait run out and come back as
+// LOKAL_ERR_TIMEOUT; nothing else uses them.
 constexpr unsigned kWaitLimit = 1u << 20;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, unsigned parity) {
-    for (unsigned spin = 0; spin < kWaitLimit; spin++) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, unsigned parity, unsigned limit = kWaitLimit) {
+    for (unsigned spin = 0; spin < limit; spin++) {
         if (mbar_try_wait(mbar, parity)) return true;
     }
     return false;

@@ -22,7 +22,9 @@
 #include <cerrno>
 #include <cstdarg>
 #include <cstring>
+#include <exception>
 #include <map>
+#include <new>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -170,6 +172,16 @@ struct Cursor {
             err = fmt("GGUF array %s: %llu entries: corrupt length", key.c_str(), (unsigned long long)n);
             return false;
         }
+        // Nothing is reserved for entries the file cannot hold: every entry takes at least its scalar size (a string at
+        // least its 8-byte length), so a count beyond the bytes that are left is a damaged header, refused before any
+        // allocation is made for it.
+        static const unsigned char kMinBytes[13] = {1, 1, 2, 2, 4, 4, 4, 1, 8, 0, 8, 8, 8};
+        const size_t each = et <= 12 ? kMinBytes[et] : 0;
+        if (each != 0 && n > (len - p) / each) {
+            err = fmt("GGUF array %s: %llu entries of at least %zu bytes, %zu bytes left in the file", key.c_str(), (unsigned long long)n,
+                      each, len - p);
+            return false;
+        }
         if (et == 8) {
             v->kind = lokal_gguf::ARR_STR;
             v->arr_s.resize(static_cast<size_t>(n));
@@ -245,7 +257,25 @@ void fill_tensor(const lokal_gguf* g, const lokal_gguf::Info& i, lokal_gguf_tens
 
 extern "C" {
 
+static int gguf_open_impl(const char* path, lokal_gguf** out, char* err, size_t err_len, lokal_gguf** partial);
+
+// A damaged header must come back as an error code, never as an exception crossing the C boundary: allocation
+// failures (and anything else the containers may throw) are caught here and the half-built handle is released.
 int lokal_gguf_open(const char* path, lokal_gguf** out, char* err, size_t err_len) {
+    lokal_gguf* partial = nullptr;
+    try {
+        return gguf_open_impl(path, out, err, err_len, &partial);
+    } catch (const std::bad_alloc&) {
+        if (out) *out = nullptr;
+        return fail_open("out of memory while reading the GGUF header", err, err_len, partial, LOKAL_ERR_FORMAT);
+    } catch (const std::exception& e) {
+        if (out) *out = nullptr;
+        return fail_open(fmt("GGUF header could not be read: %s", e.what()), err, err_len, partial, LOKAL_ERR_FORMAT);
+    }
+}
+
+static int gguf_open_impl(const char* path, lokal_gguf** out, char* err, size_t err_len, lokal_gguf** partial) {
+    // every failure below releases the handle through fail_open and returns; `partial` is read on the exception path only
     if (!path || !out) return fail_open("lokal_gguf_open: path and out must be non-null", err, err_len, nullptr, LOKAL_ERR_BAD_ARG);
     *out = nullptr;
     const int fd = open(path, O_RDONLY);
@@ -258,7 +288,12 @@ int lokal_gguf_open(const char* path, lokal_gguf** out, char* err, size_t err_le
     void* m = mmap(nullptr, static_cast<size_t>(st.st_size), PROT_READ, MAP_PRIVATE, fd, 0);
     close(fd);
     if (m == MAP_FAILED) return fail_open(fmt("cannot map %s: %s", path, strerror(errno)), err, err_len, nullptr, LOKAL_ERR_IO);
-    lokal_gguf* g = new lokal_gguf();
+    lokal_gguf* g = new (std::nothrow) lokal_gguf();
+    if (!g) {
+        munmap(m, static_cast<size_t>(st.st_size));
+        return fail_open("out of memory", err, err_len, nullptr, LOKAL_ERR_IO);
+    }
+    *partial = g;
     g->map = static_cast<const unsigned char*>(m);
     g->len = static_cast<size_t>(st.st_size);
     Cursor rd{g->map, g->len};
@@ -344,9 +379,12 @@ int lokal_gguf_open(const char* path, lokal_gguf** out, char* err, size_t err_le
         unsigned __int128 elems = 1;
         for (auto d : r.ne) {
             elems *= d;
-            if (elems > (static_cast<unsigned __int128>(1) << 62)) return fail_open(fmt("tensor %s: element count overflow", r.name.c_str()), err, err_len, g, LOKAL_ERR_FORMAT);
+            if (elems >= (static_cast<unsigned __int128>(1) << 62)) return fail_open(fmt("tensor %s: element count overflow", r.name.c_str()), err, err_len, g, LOKAL_ERR_FORMAT);
         }
-        const uint64_t nbytes = lokal_cuda_row_bytes(r.type, static_cast<size_t>(elems));
+        // bytes in 128-bit arithmetic: elems / block elements * block bytes must itself fit the file
+        const unsigned __int128 wide = elems / lokal_cuda_blk_elems(r.type) * lokal_cuda_blk_bytes(r.type);
+        if (wide > g->len) return fail_open(fmt("tensor %s: its bytes run past the file", r.name.c_str()), err, err_len, g, LOKAL_ERR_FORMAT);
+        const uint64_t nbytes = static_cast<uint64_t>(wide);
         const uint64_t start = g->data_start + r.offset;
         if (start < g->data_start) return fail_open(fmt("tensor %s: offset overflow", r.name.c_str()), err, err_len, g, LOKAL_ERR_FORMAT);
         if (nbytes > g->len || start > g->len - nbytes)

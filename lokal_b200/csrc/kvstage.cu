@@ -23,17 +23,25 @@ struct RowsArgs {
     unsigned slot0;
     unsigned long long rows;
     uint32_t* out;
+    unsigned* err_word;
 };
 
+// A position the cache cannot hold (negative; at or beyond max_seq in the linear layout, where it would land in the
+// next slot's rows; a row index that does not fit 32 bits) gets LOKAL_KV_ROW_NONE, which every consumer of the index
+// array skips, and sets an error bit that the next synchronisation reports: one bad position from a scheduler is an
+// error code, never a store outside the cache.
 __global__ void __launch_bounds__(256) kv_rows_kernel(const RowsArgs a) {
     pdl_sync();
     const unsigned long long r = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (r >= a.rows) return;
-    const unsigned long long pos = a.positions ? static_cast<unsigned long long>(a.positions[r]) : static_cast<unsigned long long>(a.pos0) + r;
+    const long long spos = a.positions ? static_cast<long long>(a.positions[r]) : a.pos0 + static_cast<long long>(r);
+    const unsigned long long pos = static_cast<unsigned long long>(spos);
     const unsigned long long slot = a.slots ? a.slots[r] : a.slot0;
     const unsigned long long row = a.layout.ring ? slot * (a.layout.sink_pad + a.layout.ring) + slot_of(a.layout, pos)
                                                  : slot * a.layout.max_seq + pos;
-    a.out[r] = static_cast<uint32_t>(row);
+    const bool bad = spos < 0 || (a.layout.ring == 0 && pos >= a.layout.max_seq) || row >= LOKAL_KV_ROW_NONE;
+    if (bad) atomicOr(a.err_word, kErrPosRange);
+    a.out[r] = bad ? LOKAL_KV_ROW_NONE : static_cast<uint32_t>(row);
 }
 
 struct StageArgs {
@@ -54,6 +62,7 @@ __global__ void __launch_bounds__(256) kv_stage_kernel(const StageArgs a) {
     const unsigned lane = threadIdx.x & 31u;
     const S* src = reinterpret_cast<const S*>(a.src) + r * a.src_stride;
     const unsigned long long orow = a.dst_rows ? static_cast<unsigned long long>(__ldg(a.dst_rows + r)) : r;
+    if (a.dst_rows && orow == LOKAL_KV_ROW_NONE) return;  // a position lokal_cuda_kv_rows refused: nothing is stored
     D* dst = reinterpret_cast<D*>(a.dst) + orow * a.dst_stride;
     if (a.vec_ok) {
         // Up to four steps of a row (1024 elements per warp) are loaded before the first one is converted and stored,
@@ -174,7 +183,7 @@ int lokal_cuda_kv_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const lokal_kv_
     if (!lokal::aligned_to(rows_out, 4) || (positions && !lokal::aligned_to(positions, 4)) || (slots && !lokal::aligned_to(slots, 4)))
         return ctx->fail(LOKAL_ERR_MISALIGNED, "kv_rows: a pointer is not 4-byte aligned");
     if (rows == 0) return LOKAL_OK;
-    lokal::RowsArgs a{*layout, positions, pos0, slots, slot0, rows, rows_out};
+    lokal::RowsArgs a{*layout, positions, pos0, slots, slot0, rows, rows_out, ctx->err_word};
     const unsigned long long blocks = (rows + 255) / 256;
     if (blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "kv_rows: too many rows for one launch");
     lokal::launch_k(lokal::kv_rows_kernel, static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(s), a);

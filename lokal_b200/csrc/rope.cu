@@ -89,6 +89,8 @@ struct QkArgs {
     int prefetch;                       // ask L2 for the row before waiting for the previous kernel (staged kernel)
     unsigned swpr, swpr_shift;          // warps that share one staged row, a power of two, and its log2 (staged kernel)
     unsigned* err_word;
+    unsigned wait_limit;                // polls of the staged row's mbarrier before the kernel gives up (kWaitLimit)
+    unsigned extra_tx;                  // 0; a test sets it so that the row's barrier never completes and the wait runs out
 };
 
 // ---------------------------------------------------------------------------
@@ -131,6 +133,7 @@ struct RopeRow {
     unsigned sub, hsel, slots;
     unsigned lo_off, hi_off;  // element offsets inside a head of this lane's two vectors
     bool rot_lane;            // this lane holds a rotated pair (always, when ROT == HD)
+    bool k_skip;              // the row's cache row is LOKAL_KV_ROW_NONE: its k heads are not stored
 
     // The two vectors of lane `s` of a group: a rotated pair, or two consecutive vectors of the tail.
     static __device__ __forceinline__ unsigned lo_of(unsigned s) { return (FULL || s < RL) ? s * N : ROT + (s - RL) * 2 * N; }
@@ -165,9 +168,11 @@ struct RopeRow {
         const long long k_shift = static_cast<long long>(a.n_q) * HD;
         q_dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride + lo_off;
         k_dst = nullptr;
+        k_skip = false;
         if (a.n_kv) {
             const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(__ldg(a.k_out_rows + row)) : row;
-            k_dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride + lo_off - k_shift;
+            k_skip = a.k_out_rows && orow == LOKAL_KV_ROW_NONE;
+            k_dst = reinterpret_cast<T*>(a.k_out) + (k_skip ? 0ull : orow) * a.k_out_stride + lo_off - k_shift;
         }
     }
 
@@ -259,7 +264,7 @@ struct RopeRow {
                 }
             }
         }
-        if (live) {
+        if (live && !(k_skip && !is_q)) {
             float2 oa[P], ob[P];
 #pragma unroll
             for (int i = 0; i < P; i++) {
@@ -424,7 +429,7 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
         mbar_init(bar, 1);
         mbar_init_fence();
         if (valid) {
-            mbar_expect_tx(bar, a.q_row_bytes + a.k_row_bytes);
+            mbar_expect_tx(bar, a.q_row_bytes + a.k_row_bytes + a.extra_tx);
             if (a.q_row_bytes) bulk_copy_g2s(smem_addr(stage), reinterpret_cast<const T*>(a.q) + row * a.q_stride, a.q_row_bytes, bar);
             if (a.k_row_bytes) bulk_copy_g2s(smem_addr(stage + a.q_row_bytes), reinterpret_cast<const T*>(a.k) + row * a.k_stride, a.k_row_bytes, bar);
         }
@@ -434,9 +439,9 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
     if (NORM) R::stage_weights(a, w_s);
     __syncthreads();  // norm weights staged; every row's mbarrier initialised before anyone waits on it
     if (!valid) return;
-    if (!mbar_wait_bounded(bar, 0)) {
+    if (!mbar_wait_bounded(bar, 0, a.wait_limit)) {
         if (lane == 0) atomicOr(a.err_word, kErrTimeout);
-        mbar_wait_bounded(bar, 0);  // one more bounded chance for the copies in flight to land before leaving
+        mbar_wait_bounded(bar, 0, a.wait_limit);  // one more bounded chance for the copies in flight to land before leaving
         return;
     }
     const T* srow = reinterpret_cast<const T*>(stage) + r.lo_off;
@@ -481,6 +486,7 @@ __global__ void __launch_bounds__(256) qk_rope_generic_kernel(const QkArgs a) {
         dst = reinterpret_cast<T*>(a.q_out) + row * a.q_out_stride;
     } else {
         const unsigned long long orow = a.k_out_rows ? static_cast<unsigned long long>(a.k_out_rows[row]) : row;
+        if (a.k_out_rows && orow == LOKAL_KV_ROW_NONE) return;  // a position lokal_cuda_kv_rows refused (no shuffles follow a return of a whole warp)
         dst = reinterpret_cast<T*>(a.k_out) + orow * a.k_out_stride;
     }
     dst += static_cast<size_t>(head) * hd;
@@ -594,6 +600,8 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     a.k_row_bytes = a.n_kv * a.head_dim * static_cast<unsigned>(sizeof(T));
     a.stage_bytes = (a.q_row_bytes + a.k_row_bytes + 127u) & ~127u;
     a.err_word = ctx->err_word;
+    a.wait_limit = static_cast<unsigned>(tune_env("LOKAL_CUDA_WAIT_LIMIT", kWaitLimit));
+    a.extra_tx = static_cast<unsigned>(tune_env("LOKAL_CUDA_TEST_EXTRA_TX", 0)) & ~15u;
     // Staged kernel: whole rows through shared memory by bulk copy. Needs one warp per row, row starts that are
     // 16-byte aligned (true on this path) and a row small enough that several warps' stages fit in shared memory.
     // The 48 KB a kernel gets without opting in covers its static shared memory too (the staged norm weights).

@@ -236,6 +236,32 @@ def test_damaged_headers_are_refused_or_read_safely(tmp_path):
     assert accepted > 0  # some damage is harmless (a flipped byte inside a key name): those files must stay readable
 
 
+def test_tiny_headers_cannot_ask_for_huge_allocations(tmp_path):
+    """A 40-byte header that announces an array of 2^26 strings (or numbers) is refused before anything is reserved for
+    it: an array cannot have more entries than the bytes left in the file can hold. And a tensor of exactly 2^62 F32
+    elements, whose byte count wraps to zero in 64 bits, is an overflow, not an empty tensor."""
+    import resource
+    import time
+    for et, each in ((8, 8), (4, 4), (10, 8), (7, 1)):
+        n = 1 << 26
+        blob = gguf_bytes(3, [kv("tokenizer.ggml.tokens", 9, struct.pack("<IQ", et, n))], [], b"")
+        before = resource.getrusage(resource.RUSAGE_SELF).ru_maxrss
+        t0 = time.perf_counter()
+        e = open_err(tmp_path, blob)
+        assert e.status == E.ERR_FORMAT and "entries" in e.message and "left in the file" in e.message
+        assert time.perf_counter() - t0 < 0.5
+        assert resource.getrusage(resource.RUSAGE_SELF).ru_maxrss - before < 64 * 1024  # KiB: nowhere near the 0.5-2 GiB asked for
+    # an array that does fit is still read
+    ok = gguf_bytes(3, [kv("a", 9, struct.pack("<IQ", 4, 3) + struct.pack("<III", 7, 8, 9))], [], b"")
+    p = tmp_path / "ok.gguf"
+    p.write_bytes(ok)
+    with GgufFile(p) as g:
+        assert list(g.get_arr_i64("a")) == [7, 8, 9]
+    for ne in ([1 << 62], [1 << 31, 1 << 31], [1 << 20, 1 << 21, 1 << 21]):
+        e = open_err(tmp_path, gguf_bytes(3, [], [tensor_info("t", ne, 0, 0)], bytes(64)))
+        assert e.status == E.ERR_FORMAT and ("overflow" in e.message or "past the file" in e.message)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("embed_type", [L.Q8_0, L.Q6_K, L.Q4_K])
 def test_embedding_table_from_a_file_through_the_gather(tmp_path, ctx, dev, oracle, embed_type):

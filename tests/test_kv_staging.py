@@ -168,3 +168,55 @@ def test_stage_refusals(ctx, dev):
     with pytest.raises(L.LokalCudaError):
         ctx.kv_stage(None, a, src_dtype=F32, dst_dtype=F32, rows=4, width=8)
     ctx.kv_stage(a, a, src_dtype=F32, dst_dtype=F32, rows=0, width=8)
+
+
+@pytest.mark.gpu
+def test_bad_positions_are_refused_by_code_and_nothing_is_stored_for_them(ctx, dev, oracle):
+    """A negative position, or one at or beyond max_seq in the linear layout (which would land in the next slot's rows or
+    past the cache), gets LOKAL_KV_ROW_NONE from kv_rows; kv_stage and the rope's k output store nothing for such a row,
+    every other row lands where it belongs, and the next synchronisation returns LOKAL_ERR_POS_RANGE."""
+    import torch
+    max_seq, slots, width, rows = 64, 3, 128, 10
+    lay = L.KvLayout(max_seq=max_seq, sink=0, sink_pad=0, ring=0)
+    pos = np.array([0, 5, -1, 63, 64, 10, 1 << 30, 7, -(1 << 31), 20], np.int32)
+    slot = np.array([0, 1, 1, 2, 0, 2, 1, 0, 2, 1], np.uint32)
+    good = (pos >= 0) & (pos < max_seq)
+    idx = dev.empty((rows,), F32).view(torch.int32)
+    dpos, dslot = dev.put(pos), dev.put(slot.view(np.int32))
+    ctx.kv_rows(idx, layout=lay, rows=rows, positions=dpos, slots=dslot)
+    with pytest.raises(L.LokalCudaError) as e:
+        ctx.stream_sync()
+    assert e.value.status == L.capi.ERR_POS_RANGE
+    got = idx.cpu().numpy().view(np.uint32)
+    want = np.where(good, slot.astype(np.int64) * max_seq + pos, L.capi.KV_ROW_NONE).astype(np.uint32)
+    assert np.array_equal(got, want)
+    # staging: rows with the sentinel are skipped, the cache holds its fill value everywhere else
+    src = np.random.default_rng(1).standard_normal((rows, width), dtype=np.float32)
+    cache = dev.empty((slots * max_seq, width), F16, fill=3.0)
+    dsrc = dev.put(src)
+    ctx.kv_stage(dsrc, cache, src_dtype=F32, dst_dtype=F16, rows=rows, width=width, dst_rows=idx)
+    ctx.stream_sync()
+    out = dev.get(cache)
+    ref = np.full((slots * max_seq, width), 3.0, np.float32)
+    ref[want[good]] = synth.round_to(src[good], F16)
+    synth.assert_bits_equal(out, ref, "staged rows with refused positions")
+    # the rope's k output through the same index array
+    cfg = synth.LayerConfig("kvbad", F32, rows, 64, 64, 2, 2, 64, 100, 1e4, 1e-6, 1, seed=3)
+    d = synth.layer_inputs(cfg, rows)
+    table = dev.empty((rows, 64), F32, fill=0.0)
+    dgood = dev.put(np.where(good, pos, 0).astype(np.int32))
+    ctx.rope_table(table, theta=cfg.theta, rot_dim=64, rows=rows, positions=dgood)
+    kcache = dev.empty((slots * max_seq, width), F32, fill=3.0)
+    q, k = dev.put(d["q"]), dev.put(d["k"])
+    p = ctx.qk_rope_params(q=q, k=k, k_out=kcache, k_out_rows=idx, k_out_row_stride=width, rows=rows, n_q_heads=2,
+                           n_kv_heads=2, head_dim=64, eps=cfg.eps, cos_sin=table, q_dtype=F32, k_dtype=F32, w_dtype=F32)
+    ctx.qk_rope(p)
+    ctx.stream_sync()
+    rq, rk = oracle.qk_rope_rows(d["q"], d["k"], n_q_heads=2, n_kv_heads=2, head_dim=64, theta=cfg.theta, eps=cfg.eps,
+                                 positions=np.where(good, pos, 0).astype(np.int32))
+    kout = dev.get(kcache)
+    synth.check_f32(kout[want[good]], rk[good], "k rows with a valid position")
+    mask = np.ones(slots * max_seq, bool)
+    mask[want[good]] = False
+    assert (kout[mask] == 3.0).all(), "a refused position must not be stored anywhere"
+    synth.check_f32(dev.get(q), rq, "q is rotated for every row")

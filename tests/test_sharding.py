@@ -76,3 +76,29 @@ def test_two_rank_shards_concatenate_to_the_single_rank_result(n_rows):
             p.join(180)
             assert p.exitcode == 0
         assert ret["rows"] == n_rows and ret["equal"]
+
+
+def test_bench_partition_is_the_librarys_and_both_arms_print_the_same_config():
+    """bench.py splits the batch's rows over the ranks exactly as lokal_cuda_shard_rows does (strong scaling: the
+    configuration's 8192 rows are partitioned, never replicated), and the `config` object it prints is the same
+    dictionary in the GPU arm and in the CPU arm for every world size."""
+    import argparse
+    import importlib.util
+    import lokal_b200
+    sys.path.insert(0, HERE)
+    import synth
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    cfg = synth.C5
+    for world in (1, 2, 3, 4, 8):
+        args = argparse.Namespace(scaling="strong", gpus=world)
+        spans = [bench.shard_of(cfg, args, r, world) for r in range(world)]
+        assert spans == [lokal_b200.shard_rows(cfg.rows, world, r) for r in range(world)]
+        assert sum(c for _, c in spans) == cfg.rows
+        # what rank 0 of the GPU arm prints, and what the CPU arm (rank 0 only) prints
+        ours = bench.workload_config(cfg, spans[0][1], args)
+        ref = bench.workload_config(cfg, bench.shard_of(cfg, args, 0, max(1, args.gpus))[1], args)
+        assert ours == ref and ours["rows"] == 8192 and ours["rows_per_gpu"] == -(-8192 // world)
+        weak = argparse.Namespace(scaling="weak", gpus=world)
+        assert [bench.shard_of(cfg, weak, r, world) for r in range(world)] == [(r * cfg.rows, cfg.rows) for r in range(world)]
