@@ -47,13 +47,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return SO
     extra = os.environ.get("LOKAL_B200_NVCC_EXTRA", "").split()  # e.g. -DLOKAL_ROPE_MIN_CTAS=3 for experiments
+    tmp = SO + ".partial"  # the library appears under its name only when it is complete
     cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + \
-          [os.path.join(CSRC, s) for s in SOURCES] + ["-o", SO]
+          [os.path.join(CSRC, s) for s in SOURCES] + ["-o", tmp]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         sys.stderr.write(res.stderr)
     if res.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, SO)
     return SO
 
 

@@ -291,6 +291,34 @@ __device__ __forceinline__ float dequant_any_elem(const Rd& rd, const void* grid
 // `lut` is the IQ4 codebook as 16 floats in shared memory (one bank each, so a warp's lookups never conflict).
 // AT_BLOCK (32-element block types only): `row` already points at the block and e < 32 is the offset inside it; the
 // kernel then advances the pointer by a constant per step instead of recomputing (e >> 5) * block_bytes.
+// Q4_K / Q5_K in two halves, so that a caller can compute the scales once per row instead of once per step.
+// k45_scale_min: d1 = d * sc and -(dmin * m) of 32-element sub-block `sub` of the super-block at b (both f32 products
+// rounded once, as the reference computes them). k45_quants: EPL elements starting at element i of the super-block.
+__device__ __forceinline__ void k45_scale_min(const unsigned char* b, unsigned sub, float& d1, float& nm1) {
+    const unsigned dm = lds_u32(b);  // f16 d, f16 dmin
+    const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(dm & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(dm >> 16)));
+    unsigned sc, mn;
+    scale_min_k4(SharedBytes{b}, 4, sub, sc, mn);
+    d1 = __fmul_rn(d, static_cast<float>(sc));
+    nm1 = -__fmul_rn(dmin, static_cast<float>(mn));
+}
+template <int QT, int EPL>
+__device__ __forceinline__ void k45_quants(const unsigned char* b, unsigned i, float2 d1, float2 nm1, float2 (&y)[EPL / 2]) {
+    constexpr unsigned QS = QT == LOKAL_Q4_K ? 16 : 48;
+    constexpr float k2p23 = 8388608.0f;
+    const unsigned sub = i >> 5, l = i & 31, shift = (i & 32) ? 4u : 0u;
+#pragma unroll
+    for (int w = 0; w < EPL / 4; w++) {
+        unsigned four = (lds_u32(b + QS + (i >> 6) * 32 + l + 4 * w) >> shift) & 0x0F0F0F0Fu;
+        if constexpr (QT == LOKAL_Q5_K) four |= ((lds_u32(b + 16 + l + 4 * w) >> sub) & 0x01010101u) << 4;
+        float2 f0, f1;
+        bytes_to_pairs(four, both(-k2p23), f0, f1);
+        y[2 * w] = add2(mul2(d1, f0), nm1);
+        y[2 * w + 1] = add2(mul2(d1, f1), nm1);
+    }
+}
+
 template <int QT, int EPL, bool AT_BLOCK = false>
 __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned e, const float* lut, float2 (&y)[EPL / 2]) {
     constexpr int W = EPL / 4;
@@ -372,24 +400,11 @@ __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned 
             y[2 * w + 1] = mul2(dl, f1);
         }
     } else if constexpr (QT == LOKAL_Q4_K || QT == LOKAL_Q5_K) {
-        constexpr unsigned BB = QT == LOKAL_Q4_K ? 144 : 176, QS = QT == LOKAL_Q4_K ? 16 : 48;
+        constexpr unsigned BB = QT == LOKAL_Q4_K ? 144 : 176;
         const unsigned char* b = row + (e >> 8) * BB;
-        const unsigned i = e & 255, sub = i >> 5, l = i & 31, shift = (i & 32) ? 4u : 0u;
-        const unsigned dm = lds_u32(b);  // f16 d, f16 dmin
-        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(dm & 0xFFFF)));
-        const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(dm >> 16)));
-        unsigned sc, mn;
-        scale_min_k4(SharedBytes{b}, 4, sub, sc, mn);
-        const float2 d1 = both(__fmul_rn(d, static_cast<float>(sc))), nm1 = both(-__fmul_rn(dmin, static_cast<float>(mn)));
-#pragma unroll
-        for (int w = 0; w < W; w++) {
-            unsigned four = (lds_u32(b + QS + (i >> 6) * 32 + l + 4 * w) >> shift) & 0x0F0F0F0Fu;
-            if constexpr (QT == LOKAL_Q5_K) four |= ((lds_u32(b + 16 + l + 4 * w) >> sub) & 0x01010101u) << 4;
-            float2 f0, f1;
-            bytes_to_pairs(four, both(-k2p23), f0, f1);
-            y[2 * w] = add2(mul2(d1, f0), nm1);
-            y[2 * w + 1] = add2(mul2(d1, f1), nm1);
-        }
+        float d1, nm1;
+        k45_scale_min(b, (e & 255) >> 5, d1, nm1);
+        k45_quants<QT, EPL>(b, e & 255, both(d1), both(nm1), y);
     } else {  // LOKAL_Q6_K
         const unsigned char* b = row + (e >> 8) * 210;
         const unsigned i = e & 255, h = i >> 7, k = (i >> 5) & 3, l = i & 31, shift = (k & 2) ? 4u : 0u;
@@ -405,6 +420,49 @@ __device__ __forceinline__ void decode_block(const unsigned char* row, unsigned 
             y[2 * w + 1] = mul2(dsc, f1);
         }
     }
+}
+
+// Eight f16 outputs of a Q8_0 / Q4_0 / Q5_0 block without leaving half precision, bit-identical to rounding the f32
+// result. The reference computes f32(q) * f32(d) with q an integer of at most 8 bits and d an f16 (11 significant
+// bits): the product has at most 19 significant bits, so the f32 multiply is EXACT, and the f16 row is the
+// nearest-even rounding of that exact product. An IEEE f16 multiply of the same two numbers (q is exact in f16) is
+// the nearest-even rounding of the same exact product: the same bits, overflow to infinity and gradual underflow
+// included. The integer becomes an f16 the way it becomes an f32 elsewhere in this file: its byte is placed in the low
+// mantissa bits of 1024.0 (0x6400) and 1024 + bias is subtracted, both exact. 12 instructions per 8 outputs instead
+// of 20 plus the packs. `b` points at the block, `in_block` (0, 8, 16 or 24) is the first element.
+template <int QT>
+__device__ __forceinline__ uint4 decode_small_block_h8(const unsigned char* b, unsigned in_block) {
+    static_assert(QT == LOKAL_Q8_0 || QT == LOKAL_Q4_0 || QT == LOKAL_Q5_0, "types whose value is one exact product");
+    const unsigned short dbits = *reinterpret_cast<const unsigned short*>(b);
+    const __half2 dd = __half2half2(__ushort_as_half(dbits));
+    constexpr float kBias = QT == LOKAL_Q8_0 ? 1152.0f : (QT == LOKAL_Q5_0 ? 1040.0f : 1032.0f);  // 1024 + 128 / 16 / 8
+    const __half2 bias = __float2half2_rn(kBias);
+    unsigned word[2];
+    if constexpr (QT == LOKAL_Q8_0) {
+        word[0] = lds_u32_a2(b + 2 + in_block) ^ 0x80808080u;  // int8 -> biased uint8
+        word[1] = lds_u32_a2(b + 2 + in_block + 4) ^ 0x80808080u;
+    } else {
+        constexpr unsigned QS = QT == LOKAL_Q5_0 ? 6 : 2;
+        const unsigned shift = (in_block & 16) ? 4u : 0u;
+        word[0] = (lds_u32_a2(b + QS + (in_block & 15)) >> shift) & 0x0F0F0F0Fu;
+        word[1] = (lds_u32_a2(b + QS + (in_block & 15) + 4) >> shift) & 0x0F0F0F0Fu;
+        if constexpr (QT == LOKAL_Q5_0) {
+            const unsigned qh = lds_u32_a2(b + 2) >> in_block;  // bit k: fifth bit of element in_block + k
+            word[0] |= (((qh & 15u) * 0x00204081u) & 0x01010101u) << 4;
+            word[1] |= ((((qh >> 4) & 15u) * 0x00204081u) & 0x01010101u) << 4;
+        }
+    }
+    unsigned out[4];
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+        const unsigned lo = __byte_perm(word[w], 0x64646464u, 0x4140), hi = __byte_perm(word[w], 0x64646464u, 0x4342);
+        const __half2 q0 = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
+        const __half2 q1 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+        const __half2 y0 = __hmul2(q0, dd), y1 = __hmul2(q1, dd);
+        out[2 * w] = *reinterpret_cast<const unsigned*>(&y0);
+        out[2 * w + 1] = *reinterpret_cast<const unsigned*>(&y1);
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
 // Codebook types in the staged kernel. EPL consecutive elements are half a run (EPL = 4) or one run (EPL = 8): one
@@ -642,17 +700,44 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
                 // 32-element blocks: a lane's offset inside its block never changes, and every step moves it EPL blocks on
                 const unsigned char* bp = row + ((lane * EPL) >> 5) * kSmallBlock;
                 const unsigned in_block = (lane * EPL) & 31u;
+                constexpr bool kHalfPath = std::is_same<OutT, __half>::value && (QT == LOKAL_Q8_0 || QT == LOKAL_Q4_0 || QT == LOKAL_Q5_0);
                 for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL, bp += EPL * kSmallBlock) {
-                    float2 y[EPL / 2];
-                    decode_block<QT, EPL, true>(bp, in_block, lut, y);
-                    store_out16<OutT>(orow + e, y);
+                    if constexpr (kHalfPath) {
+                        st_stream(orow + e, decode_small_block_h8<QT>(bp, in_block));
+                    } else {
+                        float2 y[EPL / 2];
+                        decode_block<QT, EPL, true>(bp, in_block, lut, y);
+                        store_out16<OutT>(orow + e, y);
+                    }
                 }
             } else {
-                for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
-                    float2 y[EPL / 2];
-                    if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
-                    else decode_block<QT, EPL>(row, e, lut, y);
-                    store_out16<OutT>(orow + e, y);
+                bool done = false;
+                if constexpr (QT == LOKAL_Q4_K || QT == LOKAL_Q5_K) {
+                    // Rows of at most 32 sub-blocks (1024 elements): lane j works out the scale and min of sub-block j
+                    // once, and each step fetches the pair of its own sub-block with two shuffles instead of
+                    // recomputing them (the 6-bit unpacking and two products are a third of a step's instructions).
+                    // a.dim is a multiple of 256 and a step covers 128 or 256 elements, so all lanes take the same
+                    // number of steps and every shuffle is executed by the whole warp.
+                    if (a.dim <= 1024u) {
+                        constexpr unsigned BB = QT == LOKAL_Q4_K ? 144 : 176;
+                        float d1 = 0.0f, nm1 = 0.0f;
+                        if (lane * 32u < a.dim) k45_scale_min(row + (lane >> 3) * BB, lane & 7u, d1, nm1);
+                        for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
+                            const float d1s = __shfl_sync(0xffffffffu, d1, e >> 5), nm1s = __shfl_sync(0xffffffffu, nm1, e >> 5);
+                            float2 y[EPL / 2];
+                            k45_quants<QT, EPL>(row + (e >> 8) * BB, e & 255u, both(d1s), both(nm1s), y);
+                            store_out16<OutT>(orow + e, y);
+                        }
+                        done = true;
+                    }
+                }
+                if (!done) {
+                    for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
+                        float2 y[EPL / 2];
+                        if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
+                        else decode_block<QT, EPL>(row, e, lut, y);
+                        store_out16<OutT>(orow + e, y);
+                    }
                 }
             }
         }
@@ -694,185 +779,6 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
     } else {
         for (unsigned st = 0; i < a.n; i += total_warps, st = (st + 1 == NST) ? 0u : st + 1) {
             if (!step(i, st)) return;
-        }
-    }
-}
-
-// ---- batch kernel for quantised tables: a CTA stages and decodes R consecutive output rows at a time ----
-// The warp-per-row kernel above spends about half of its instructions on per-row bookkeeping (id fetch, window
-// arithmetic, copy issue, barrier wait, ring state), and a row whose vectors do not fill a whole number of warp steps
-// leaves lanes idle in its last step (896 elements = 3.5 steps of 8 per lane). Here that part is paid once per batch
-// of R rows: R lanes of warp 0 each fetch one id, work out one window and issue one bulk copy, all against ONE
-// mbarrier per stage (arrival count R, each lane announcing its own bytes); every thread waits once per batch; then
-// warp w decodes rows w, w + 8, ... of the batch with the warp-per-row kernel's row loop. (Dealing the batch's output
-// vectors round-robin to all 256 threads, which would also fill the last partial step of a row, was measured slower:
-// the per-vector row lookup and index arithmetic cost more instructions than the idle lanes.) A ring of NST stages: the copies of
-// batch b + NST - 1 are issued before batch b is decoded. A batch completes when its slowest row has landed, so the
-// ring has to be deep enough to cover the latency of a row that comes from HBM rather than L2. The decoders are the
-// same device functions the warp-per-row kernel calls, so the results are the same bits.
-constexpr unsigned kRowInvalid = 0xFFFFFFFFu;
-constexpr unsigned kBatchMaxRows = 16, kBatchMaxStages = 8;
-
-struct BatchArgs {
-    GatherArgs g;
-    unsigned rows_per_batch;   // R: 1, 2, 4, 8 or 16
-    unsigned stages;           // NST: 2 .. 8
-    unsigned slot_bytes;       // shared memory per staged row, multiple of 16, >= row window + 16
-    unsigned long long batches;
-};
-
-template <int QT, typename OutT>
-__global__ void __launch_bounds__(256) gather_quant_batch_kernel(const BatchArgs b) {
-    pdl_sync();
-    constexpr int EPL = VecOf<OutT>::N;
-    const GatherArgs& a = b.g;
-    extern __shared__ __align__(128) unsigned char smem[];
-    // layout: [8 mbarriers (64 B)] [row_off[stage][16] (512 B)] [pad to 1024] [stage 0: R slots] [stage 1: R slots] ...
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem);
-    unsigned* row_off = reinterpret_cast<unsigned*>(smem + 64);  // written by the producer lanes before they arrive
-    unsigned char* stages = smem + 1024;
-    const unsigned R = b.rows_per_batch, NST = b.stages, stage_bytes = R * b.slot_bytes;
-    const unsigned tid = threadIdx.x;
-    const bool producer = tid < R;  // lanes 0..R-1 of warp 0
-    if (tid == 0) {
-        for (unsigned st = 0; st < NST; st++) mbar_init(smem_addr(&bars[st]), R);
-        mbar_init_fence();
-    }
-    __shared__ float lut[16];  // the IQ4 codebook as floats; unused by the other block types
-    if constexpr (QT == LOKAL_IQ4_NL || QT == LOKAL_IQ4_XS) {
-        if (tid < 16) lut[tid] = iq4_value(tid);
-    }
-    __syncthreads();
-
-    auto id_of = [&](unsigned long long i) { return a.ids ? static_cast<unsigned long long>(__ldg(a.ids + i)) : i; };
-    // Producer lane `tid` brings row (batch, tid) into its slot of stage st. Every producer lane arrives exactly once
-    // per call, with or without bytes, so the stage's phase completes when all R rows are in.
-    auto issue = [&](unsigned long long row_i, unsigned long long id, unsigned st) {
-        const uint32_t bar = smem_addr(&bars[st]);
-        unsigned char* slot = stages + st * stage_bytes + tid * b.slot_bytes;
-        bool valid = row_i < a.n;  // false past the last row of the last batch
-        if (valid && id >= a.vocab) {
-            atomicOr(a.err_word, kErrIdRange);
-            valid = false;
-        }
-        if (!valid) {
-            row_off[st * kBatchMaxRows + tid] = kRowInvalid;
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-            return;
-        }
-        const unsigned long long start = id * a.row_bytes, end = start + a.row_bytes;
-        const unsigned long long w0 = start & ~15ull;
-        unsigned long long w1 = (end + 15ull) & ~15ull;
-        const unsigned long long whole = a.table_bytes & ~15ull;  // the bulk copy never reads past the table
-        if (w1 > whole) w1 = whole;
-        row_off[st * kBatchMaxRows + tid] = tid * b.slot_bytes + static_cast<unsigned>(start - w0);
-        if (end > w1) {  // the table's last bytes (its size is not a multiple of 16): at most 15 plain byte loads
-            const unsigned long long from = w1 > start ? w1 : start;
-            for (unsigned long long p = from; p < end; p++) slot[p - w0] = __ldg(a.table + p);
-        }
-        if (w1 > w0) {
-            const unsigned bytes = static_cast<unsigned>(w1 - w0);
-            mbar_expect_tx(bar, bytes + a.extra_tx);
-            bulk_copy_g2s(smem_addr(slot), a.table + w0, bytes, bar);
-        } else {
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-        }
-    };
-
-    const unsigned warp_in_cta = tid >> 5, lane = tid & 31u;
-    const unsigned long long stride = gridDim.x;
-    unsigned long long batch = blockIdx.x;
-    // prologue: this CTA's first NST - 1 batches in flight, and the ids of the kIdAhead batches after them on their
-    // way. An id is a load from HBM (the id list is read once); the copy that needs it is issued kIdAhead iterations
-    // after the load, so that its latency is never on the path of an iteration (with one iteration of lead it was:
-    // an iteration lasts well under a microsecond).
-    constexpr unsigned kIdAhead = 4;
-    unsigned long long id_q[kIdAhead];
-#pragma unroll
-    for (unsigned k = 0; k < kIdAhead; k++) id_q[k] = 0;
-    if (producer) {
-        unsigned long long bb = batch;
-        for (unsigned st = 0; st + 1 < NST; st++, bb += stride) {
-            if (bb < b.batches) {
-                const unsigned long long ri = bb * R + tid;
-                issue(ri, ri < a.n ? id_of(ri) : 0, st);
-            }
-        }
-#pragma unroll
-        for (unsigned k = 0; k < kIdAhead; k++, bb += stride) {
-            const unsigned long long rn = bb * R + tid;
-            if (bb < b.batches && rn < a.n) id_q[k] = id_of(rn);
-        }
-    }
-    const unsigned long long ahead = static_cast<unsigned long long>(NST - 1) * stride;
-    unsigned st = 0, ph = 0;  // stage and phase parity of the batch being decoded
-    for (; batch < b.batches; batch += stride) {
-        const unsigned st_fill = st == 0 ? NST - 1 : st - 1;  // decoded in the iteration before this one
-        if (producer && batch + ahead < b.batches) {
-            // every thread has passed the closing barrier of the iteration that decoded stage st_fill
-            issue((batch + ahead) * R + tid, id_q[0], st_fill);
-#pragma unroll
-            for (unsigned k = 0; k + 1 < kIdAhead; k++) id_q[k] = id_q[k + 1];
-            const unsigned long long bn = batch + ahead + kIdAhead * stride, rn = bn * R + tid;
-            if (bn < b.batches && rn < a.n) id_q[kIdAhead - 1] = id_of(rn);
-        }
-        const bool ok = mbar_wait_bounded(smem_addr(&bars[st]), ph, a.wait_limit);
-        if (ok) {
-            const unsigned long long row0 = batch * R;
-            const unsigned nrows = static_cast<unsigned>(a.n - row0 < R ? a.n - row0 : R);
-            const unsigned char* stage = stages + st * stage_bytes;
-            const unsigned* offs = row_off + st * kBatchMaxRows;
-            // warp w decodes rows w, w + 8, ... of the batch with the row loop of the warp-per-row kernel: constant
-            // strides, one 16-byte store per lane and step
-            for (unsigned r = warp_in_cta; r < nrows; r += 8) {
-                const unsigned off = offs[r];
-                OutT* orow = reinterpret_cast<OutT*>(a.out) + (row0 + r) * a.dim;
-                if (off == kRowInvalid) {
-                    float2 z[EPL / 2];
-#pragma unroll
-                    for (int k = 0; k < EPL / 2; k++) z[k] = make_float2(0.0f, 0.0f);
-                    for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) store_out16<OutT>(orow + e, z);
-                    continue;
-                }
-                const unsigned char* row = stage + off;
-                constexpr unsigned kSmallBlock = QT == LOKAL_Q8_0 ? 34u : (QT == LOKAL_Q5_0 ? 22u : ((QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL) ? 18u : 0u));
-                if constexpr (kSmallBlock != 0) {
-                    // 32-element blocks: a lane's offset inside its block never changes, and every step moves it EPL blocks on
-                    const unsigned char* bp = row + ((lane * EPL) >> 5) * kSmallBlock;
-                    const unsigned in_block = (lane * EPL) & 31u;
-                    for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL, bp += EPL * kSmallBlock) {
-                        float2 y[EPL / 2];
-                        decode_block<QT, EPL, true>(bp, in_block, lut, y);
-                        store_out16<OutT>(orow + e, y);
-                    }
-                } else {
-                    for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
-                        float2 y[EPL / 2];
-                        if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
-                        else decode_block<QT, EPL>(row, e, lut, y);
-                        store_out16<OutT>(orow + e, y);
-                    }
-                }
-            }
-        }
-        // closing barrier of the iteration: the stage may be refilled after it; it also carries the verdict of the wait
-        if (!__syncthreads_and(ok ? 1 : 0)) {
-            if (tid == 0) atomicOr(a.err_word, kErrTimeout);
-            // one more bounded chance for the copies still in flight to land before the CTA gives up its shared memory
-            unsigned s2 = st, p2 = ph;
-            unsigned long long b2 = batch;
-            for (unsigned k = 0; k < NST && b2 < b.batches; k++, b2 += stride) {
-                mbar_wait_bounded(smem_addr(&bars[s2]), p2, a.wait_limit);
-                if (++s2 == NST) {
-                    s2 = 0;
-                    p2 ^= 1u;
-                }
-            }
-            return;
-        }
-        if (++st == NST) {
-            st = 0;
-            ph ^= 1u;
         }
     }
 }
@@ -967,48 +873,6 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
             launch_k(gather_quant_plain_kernel<decltype(qt)::value, OutT>, static_cast<unsigned>(row_warps_blocks), 256, 0, s, a);
         });
         LOKAL_CHECK_LAUNCH(ctx, "gather_quant_plain_kernel");
-        return LOKAL_OK;
-    }
-    // Batch kernel: a ring of NST stages of R rows. Four stages of as many rows (a power of two up to 8) as keep the
-    // ring within 32 KB, so that four CTAs stay resident per SM; rows too wide for that take fewer stages.
-    // LOKAL_CUDA_GATHER_ROWS / LOKAL_CUDA_GATHER_STAGES force R / NST, LOKAL_CUDA_GATHER_KERNEL=warp keeps the
-    // warp-per-row kernel.
-    const unsigned slot_bytes = ((a.row_bytes + 15u) & ~15u) + 32u;
-    unsigned NST = 4, R = 8;
-    while (R > 1 && NST * R * slot_bytes > 32u * 1024u) R >>= 1;
-    while (NST > 2 && NST * R * slot_bytes > 64u * 1024u) NST--;
-    const long forced_r = tune_env("LOKAL_CUDA_GATHER_ROWS", 0);
-    if (forced_r == 1 || forced_r == 2 || forced_r == 4 || forced_r == 8 || forced_r == 16) R = static_cast<unsigned>(forced_r);
-    const long forced_st = tune_env("LOKAL_CUDA_GATHER_STAGES", 0);
-    if (forced_st >= 2 && forced_st <= static_cast<long>(kBatchMaxStages)) NST = static_cast<unsigned>(forced_st);
-    const size_t bsmem = 1024u + static_cast<size_t>(NST) * R * slot_bytes;
-    const char* which = getenv("LOKAL_CUDA_GATHER_KERNEL");
-    const bool use_batch = bsmem <= 200u * 1024u && !(which && which[0] == 'w');
-    if (use_batch) {
-        BatchArgs b{};
-        b.g = a;
-        b.rows_per_batch = R;
-        b.stages = NST;
-        b.slot_bytes = slot_bytes;
-        b.batches = (a.n + R - 1) / R;
-        void (*bk)(const BatchArgs) = nullptr;
-        for_quant_type(ggml_type, [&](auto qt) { bk = gather_quant_batch_kernel<decltype(qt)::value, OutT>; });
-        if (bsmem > 48u * 1024u) {
-            cudaError_t e = cudaFuncSetAttribute(bk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bsmem));
-            if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "embed_gather: cannot reserve %zu bytes of shared memory: %s", bsmem, cudaGetErrorString(e));
-        }
-        // Persistent grid: the CTAs that are resident at once, trimmed so that every CTA gets the same number of batches.
-        unsigned per_sm = static_cast<unsigned>((136u * 1024u) / (bsmem + 1024u));  // the library-wide 60 % shared-memory split
-        if (per_sm > 8) per_sm = 8;
-        if (per_sm < 1) per_sm = 1;
-        const long forced_ctas = tune_env("LOKAL_CUDA_GATHER_CTAS_PER_SM", 0);
-        if (forced_ctas >= 1 && forced_ctas <= 8) per_sm = static_cast<unsigned>(forced_ctas);
-        unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * per_sm;
-        if (cap > b.batches) cap = b.batches;
-        const unsigned long long per_cta = (b.batches + cap - 1) / cap;
-        const unsigned long long bgrid = (b.batches + per_cta - 1) / per_cta;
-        launch_k(bk, static_cast<unsigned>(bgrid), 256, bsmem, s, b);
-        LOKAL_CHECK_LAUNCH(ctx, "gather_quant_batch_kernel");
         return LOKAL_OK;
     }
     void (*kern)(const GatherArgs) = nullptr;

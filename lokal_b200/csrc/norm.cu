@@ -90,14 +90,19 @@ __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256, CTA_MODE ? 1 : LOKAL_NO
     }
     pdl_wait();
 
-    // All loads of the row are issued before any is consumed.
-    uint4 xv[VPT], dv[VPT];
+    // All loads of the row are issued before any is consumed; in the CTA-per-row shape so are the loads of the weights
+    // (of the rows' own type, the usual case), which do not depend on the reduction: left after it they would start
+    // only behind the barrier, a cache round trip on the critical path of a short launch. (The warp-per-row shape has
+    // no barrier, and four more vectors in registers would cost it a resident CTA per SM.)
+    constexpr bool kEarlyW = WSAME && CTA_MODE;
+    uint4 xv[VPT], dv[VPT], wv4[kEarlyW ? VPT : 1];
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const unsigned idx = t + j * tpr;
         if (idx < a.nvec) {
             xv[j] = ld_stream(xr + idx * N);
             if (dr) dv[j] = ld_stream(dr + idx * N);
+            if (kEarlyW) wv4[j] = ld_keep(reinterpret_cast<const T*>(a.w) + idx * N);
         }
     }
 
@@ -149,7 +154,9 @@ __global__ void __launch_bounds__(CTA_MODE ? 1024 : 256, CTA_MODE ? 1 : LOKAL_NO
         const unsigned idx = t + j * tpr;
         if (idx < a.nvec) {
             float2 w[P];
-            if (WSAME) {
+            if (kEarlyW) {
+                unpack16p<T>(wv4[j], w);
+            } else if (WSAME) {
                 unpack16p<T>(ld_keep(reinterpret_cast<const T*>(a.w) + idx * N), w);
             } else {
                 float wv[N];

@@ -206,3 +206,45 @@ def test_full_size_zipf_gather_q4_k(ctx, dev, oracle):
     ctx.embed_gather(dt, di, out, ggml_type=Q4_K, vocab=vocab, dim=dim, n=n)
     ctx.stream_sync()
     synth.assert_bits_equal(dev.get(out), want, "full-size Q4_K gather")
+
+
+@pytest.mark.parametrize("ty", [Q8_0, 2, 6])  # Q8_0, Q4_0, Q5_0: value = (integer) * (f16 scale), one exact product
+def test_f16_rows_of_single_product_types_over_every_scale_and_quant(ctx, dev, oracle, ty):
+    """f16 rows of Q8_0 / Q4_0 / Q5_0 tables are computed in half precision on the device, on the strength of an
+    exactness argument: integer (at most 8 bits) times f16 scale is exact in f32, so rounding it to f16 and multiplying
+    in f16 give the same bits. Checked here over EVERY f16 scale pattern (all 65,536, infinities and NaNs included) times
+    every quant value the block type can hold, against the f32 formula rounded once (numpy), and against the oracle."""
+    be, bb, _ = synth.QUANT_GEOMETRY[ty]
+    nq = 256 if ty == Q8_0 else (16 if ty == 2 else 32)
+    n_scales, per_row = 65536, 256 // 32  # 8 blocks per row: 256 elements
+    scales = np.arange(n_scales, dtype=np.uint16)
+    blocks = np.zeros((n_scales, per_row, bb), np.uint8)
+    blocks[:, :, 0:2] = scales.view(np.uint8).reshape(n_scales, 1, 2)
+    elem = np.arange(256).reshape(per_row, 32)  # element index -> which quant value it carries
+    if ty == Q8_0:
+        blocks[:, :, 2:] = elem.astype(np.uint8)[None]                     # all 256 int8 patterns
+        qv = elem.astype(np.uint8).view(np.int8).astype(np.float32)
+    else:
+        vals = (elem % nq).astype(np.uint8)                                 # 0..15 or 0..31, every value many times
+        qs = 2 if ty == 2 else 6
+        lo, hi = vals[:, :16], vals[:, 16:]
+        blocks[:, :, qs:qs + 16] = ((lo & 15) | ((hi & 15) << 4))[None]
+        if ty == 6:
+            bits = ((vals >> 4) & 1).astype(np.uint32)
+            qh = (bits << np.arange(32, dtype=np.uint32)[None, :]).sum(axis=1).astype(np.uint32)
+            blocks[:, :, 2:6] = qh.view(np.uint8).reshape(per_row, 4)[None]
+        qv = vals.astype(np.float32) - (8 if ty == 2 else 16)
+    table = blocks.reshape(-1)
+    got = dequant(ctx, dev, table, ty, n_scales, 256, F16)          # f32 view of the f16 rows
+    d = scales.view(np.float16).astype(np.float32)
+    with np.errstate(all="ignore"):
+        want = (qv.reshape(1, 256) * d.reshape(-1, 1)).astype(np.float16)   # exact f32 product, one rounding
+    got16 = got.astype(np.float16)
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got16), nan)
+    assert np.array_equal(got16.view(np.uint16)[~nan], want.view(np.uint16)[~nan])
+    assert nan.sum() > 0 and np.isinf(want).sum() > 0 and (want.view(np.uint16)[~nan] & 0x7C00 == 0).sum() > 1000  # NaN, inf, subnormals all occur
+    # and the oracle agrees on a slice (finite scales)
+    rows = slice(0x3000, 0x3040)
+    ref = synth.round_to(oracle.embed_gather(table[rows.start * per_row * bb:rows.stop * per_row * bb], ty, 64, 256, np.arange(64, dtype=np.uint32)), F16)
+    synth.assert_bits_equal(got[rows], ref, "oracle slice")
