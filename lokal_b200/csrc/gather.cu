@@ -722,11 +722,24 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
                         constexpr unsigned BB = QT == LOKAL_Q4_K ? 144 : 176;
                         float d1 = 0.0f, nm1 = 0.0f;
                         if (lane * 32u < a.dim) k45_scale_min(row + (lane >> 3) * BB, lane & 7u, d1, nm1);
-                        for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
-                            const float d1s = __shfl_sync(0xffffffffu, d1, e >> 5), nm1s = __shfl_sync(0xffffffffu, nm1, e >> 5);
-                            float2 y[EPL / 2];
-                            k45_quants<QT, EPL>(row + (e >> 8) * BB, e & 255u, both(d1s), both(nm1s), y);
-                            store_out16<OutT>(orow + e, y);
+                        if constexpr (EPL == 8) {
+                            // 16-bit rows: a step is one whole super-block, so a lane's place inside the super-block
+                            // (lane * 8) never changes: only the block pointer and the shuffle source move
+                            const unsigned char* bp = row;
+                            unsigned src_lane = lane >> 2;
+                            for (unsigned e = lane * EPL; e < a.dim; e += 256, bp += BB, src_lane += 8) {
+                                const float d1s = __shfl_sync(0xffffffffu, d1, src_lane), nm1s = __shfl_sync(0xffffffffu, nm1, src_lane);
+                                float2 y[EPL / 2];
+                                k45_quants<QT, EPL>(bp, lane * 8u, both(d1s), both(nm1s), y);
+                                store_out16<OutT>(orow + e, y);
+                            }
+                        } else {
+                            for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
+                                const float d1s = __shfl_sync(0xffffffffu, d1, e >> 5), nm1s = __shfl_sync(0xffffffffu, nm1, e >> 5);
+                                float2 y[EPL / 2];
+                                k45_quants<QT, EPL>(row + (e >> 8) * BB, e & 255u, both(d1s), both(nm1s), y);
+                                store_out16<OutT>(orow + e, y);
+                            }
                         }
                         done = true;
                     }
