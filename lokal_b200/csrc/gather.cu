@@ -894,10 +894,19 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "embed_gather: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    // Persistent grid: as many CTAs as stay resident (8 x 256 threads per SM, or what shared memory allows).
+    // Grid: 8 CTAs per SM for 16-bit rows, 24 for f32 rows (or what shared memory allows), each warp walking a
+    // grid-stride list of rows. That is more than are resident at once (a decoder of 48 registers holds five
+    // 256-thread CTAs per SM), and measured better than a grid of exactly the resident CTAs: later CTAs start as earlier
+    // ones finish and even out the tail (Q8_0 to f16 rows: 25.4 against 28.0 us). The f32 rows, which are bound by
+    // the store path rather than by instruction issue, gain from a finer grain still (Q8_0 / Q4_K / Q6_K to f32:
+    // 45.7 / 49.5 / 49.4 us at 8 CTAs per SM, 41.2 / 45.4 / 46.4 us at 24); the 16-bit rows, which are issue-bound,
+    // lose to the per-CTA prologue beyond 8. LOKAL_CUDA_GATHER_CTAS_PER_SM overrides.
+    const unsigned want_per_sm = sizeof(OutT) == 4 ? 24u : 8u;
     unsigned per_sm = static_cast<unsigned>((220u * 1024u) / (smem + 1024u));
-    if (per_sm > 8) per_sm = 8;
+    if (per_sm > 8) per_sm = want_per_sm;
     if (per_sm < 1) per_sm = 1;
+    const long forced_ctas = tune_env("LOKAL_CUDA_GATHER_CTAS_PER_SM", 0);
+    if (forced_ctas >= 1 && forced_ctas <= 64) per_sm = static_cast<unsigned>(forced_ctas);
     unsigned long long grid = static_cast<unsigned long long>(ctx->sm_count) * per_sm;
     if (grid > row_warps_blocks) grid = row_warps_blocks;
     launch_k(kern, static_cast<unsigned>(grid), warps * 32, smem, s, a);
