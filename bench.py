@@ -685,7 +685,7 @@ def parity_gate(ctx, cfg, dev, stream, pos0, rows=192):
     get = lambda t: t.to(torch.float32).cpu().numpy()
     result = {"rows": rows, "bar": "f32: max abs 1e-5; f16: 2e-3 relative; bf16: one bf16 rounding (2^-8) of an f32-accurate value"}
 
-    def judge(name, got, ref, atol):
+    def grade(name, got, ref, atol):
         got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
         err = np.abs(got - ref)
         if cfg.dtype == L.F32:
@@ -724,12 +724,12 @@ def parity_gate(ctx, cfg, dev, stream, pos0, rows=192):
     ctx.stream_sync(stream)
 
     rx, rxn = O.add_rmsnorm_rows(d["x"], d["delta"], d["w_norm"], cfg.eps)
-    judge("add_rmsnorm", get(xn), rxn, 1e-6)
+    grade("add_rmsnorm", get(xn), rxn, 1e-6)
     rq, rk = O.qk_rope_rows(d["q"], d["k"], n_q_heads=cfg.n_q_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, theta=cfg.theta,
                             eps=cfg.eps, q_bias=d.get("q_bias"), k_bias=d.get("k_bias"), q_norm_w=d.get("q_norm_w"),
                             k_norm_w=d.get("k_norm_w"), pos0=pos0)
-    judge("qk_rope", np.concatenate([get(q), get(k)], axis=1), np.concatenate([rq, rk], axis=1), 2e-6)
-    judge("swiglu", get(inner), O.swiglu(d["gate"], d["up"]), 1e-6)
+    grade("qk_rope", np.concatenate([get(q), get(k)], axis=1), np.concatenate([rq, rk], axis=1), 2e-6)
+    grade("swiglu", get(inner), O.swiglu(d["gate"], d["up"]), 1e-6)
     want = synth.round_to(O.embed_gather(table, L.Q8_0, vocab, cfg.hidden, ids), cfg.dtype)
     gg = get(gout)
     result["embed_gather"] = {"ok": bool(np.array_equal(gg.view(np.uint32), want.view(np.uint32))), "bit_exact": True}

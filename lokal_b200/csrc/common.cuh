@@ -488,7 +488,9 @@ int launch_norm(lokal_cuda_ctx* ctx, cudaStream_t s, void* x, const void* delta,
                 size_t rows, size_t dim, float eps, int dtype, int w_dtype, int h_dtype);
 int launch_rope_table(lokal_cuda_ctx* ctx, cudaStream_t s, float theta, uint32_t rot_dim, const int32_t* positions,
                       int64_t pos0, size_t rows, float* cos_sin);
-int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_params& p);
+// `shared_machine`: the caller runs other kernels beside this one (the branched schedule of the layer pass); a short
+// launch then takes its compact shape (one warp per row) instead of the one that is fastest alone.
+int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_params& p, bool shared_machine = false);
 int launch_swiglu(lokal_cuda_ctx* ctx, cudaStream_t s, const void* gate, const void* up, void* out, void* out_h,
                   size_t n, int dtype, int h_dtype);
 int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int ggml_type, size_t vocab, size_t dim,

@@ -82,8 +82,8 @@ const char* at(const void* base, size_t bytes) { return static_cast<const char*>
 // it is given: rotation of q/k (s_rope), SwiGLU (s_mlp), and the two residual-add + RMSNorm calls that carry the
 // residual stream from layer to layer (s_norm). With one stream for all three they are issued in the order of
 // Model::forward (src/model.rs:207-255).
-int layer_ops(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, cudaStream_t s_rope, cudaStream_t s_norm, cudaStream_t s_mlp, uint32_t l,
-              size_t rows, void* q, void* k, const void* delta_att, const void* delta_mlp, const void* gate, const void* up) {
+int layer_ops(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, cudaStream_t s_rope, cudaStream_t s_norm, cudaStream_t s_mlp, bool branched,
+              uint32_t l, size_t rows, void* q, void* k, const void* delta_att, const void* delta_mlp, const void* gate, const void* up) {
     const lokal_pass_config& c = P->cfg;
     const uint32_t slot = l % c.slots;
     const size_t hid_b = static_cast<size_t>(c.max_rows) * c.hidden * P->es;
@@ -105,7 +105,7 @@ int layer_ops(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, cudaStream_t s_rope, cuda
     rp.eps = c.eps;
     rp.q_dtype = rp.k_dtype = c.dtype;
     rp.w_dtype = c.w_dtype;
-    int rc = lokal::launch_qk_rope(ctx, s_rope, rp);
+    int rc = lokal::launch_qk_rope(ctx, s_rope, rp, branched);
     if (rc != LOKAL_OK) return rc;
     const void* w_post = at(P->norm_w, (static_cast<size_t>(l) * 2 + 1) * c.hidden * P->wes);
     rc = lokal::launch_norm(ctx, s_norm, P->x, delta_att, w_post, at(P->xn_att, slot * hid_b), nullptr, rows, c.hidden, c.eps,
@@ -285,7 +285,7 @@ int lokal_cuda_pass_run_device(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, lokal_cu
     }
     rc = step_head(ctx, P, s_norm, s_rope, in->ids, in->positions, in->pos0, in->rows);
     for (uint32_t l = 0; rc == LOKAL_OK && l < c.layers; l++) {
-        rc = layer_ops(ctx, P, s_rope, s_norm, s_mlp, l, in->rows, at(in->q, l * in->q_layer_stride * P->es), at(in->k, l * in->k_layer_stride * P->es),
+        rc = layer_ops(ctx, P, s_rope, s_norm, s_mlp, branches == LOKAL_PASS_SCHEDULE_BRANCHES, l, in->rows, at(in->q, l * in->q_layer_stride * P->es), at(in->k, l * in->k_layer_stride * P->es),
                        at(in->delta_att, l * in->delta_layer_stride * P->es), at(in->delta_mlp, l * in->delta_layer_stride * P->es),
                        at(in->gate, l * in->mlp_layer_stride * P->es), at(in->up, l * in->mlp_layer_stride * P->es));
     }
@@ -347,7 +347,7 @@ int lokal_cuda_pass_run_host(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, const loka
         LOKAL_CUDA_TRY(ctx, cudaMemcpyAsync(ddm, at(in->delta_mlp, l * in->delta_layer_stride * P->es), rows * c.hidden * P->es, cudaMemcpyHostToDevice, cs));
         LOKAL_CUDA_TRY(ctx, cudaEventRecord(P->filled[slot], cs));
         LOKAL_CUDA_TRY(ctx, cudaStreamWaitEvent(ks, P->filled[slot], 0));
-        rc = layer_ops(ctx, P, ks, ks, ks, l, rows, dq, dk, dda, ddm, dg, du);
+        rc = layer_ops(ctx, P, ks, ks, ks, false, l, rows, dq, dk, dda, ddm, dg, du);
         if (rc != LOKAL_OK) return rc;
         LOKAL_CUDA_TRY(ctx, cudaEventRecord(P->drained[slot], ks));
     }

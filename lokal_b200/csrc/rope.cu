@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(256) qk_rope_generic_kernel(const QkArgs a) {
 }
 
 template <typename T>
-int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
+int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok, bool shared_machine) {
     constexpr unsigned N = VecOf<T>::N;
     const unsigned slots = a.n_q + a.n_kv;
     if (slots == 0 || a.rows == 0) return LOKAL_OK;
@@ -550,7 +550,12 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     // the 0.5B / 0.6B shapes one staged warp per row is 20-35 % faster, at 1024 rows and fewer the split wins).
     unsigned wpr = 1;
     const unsigned long long want_warps = static_cast<unsigned long long>(ctx->sm_count) * 16;
-    if (a.rows < static_cast<unsigned long long>(ctx->sm_count) * 12) {
+    // When the caller runs other kernels beside this one, a short launch keeps one warp per row too: alone it is the
+    // slower shape, but it occupies a sixth of the thread slots of the flat kernel and leaves the machine to its
+    // neighbours (a 1024-row step of the branched layer pass: 0.268 against 0.289 ms).
+    // (Below about six rows per SM there are too few warps for that to pay: 512- and 256-row steps measured 3-5 % slower.)
+    const bool compact = shared_machine && a.rows >= static_cast<unsigned long long>(ctx->sm_count) * 6;
+    if (!compact && a.rows < static_cast<unsigned long long>(ctx->sm_count) * 12) {
         wpr = static_cast<unsigned>((want_warps + a.rows - 1) / a.rows);
         if (wpr > a.chunks) wpr = a.chunks;
     }
@@ -656,11 +661,11 @@ int launch_one(lokal_cuda_ctx* ctx, cudaStream_t s, QkArgs a, bool fast_ok) {
     return LOKAL_OK;
 }
 
-int launch_by_type(lokal_cuda_ctx* ctx, cudaStream_t s, const QkArgs& a, int dtype, bool fast_ok) {
+int launch_by_type(lokal_cuda_ctx* ctx, cudaStream_t s, const QkArgs& a, int dtype, bool fast_ok, bool shared_machine) {
     switch (dtype) {
-        case LOKAL_F32: return launch_one<float>(ctx, s, a, fast_ok);
-        case LOKAL_F16: return launch_one<__half>(ctx, s, a, fast_ok);
-        default: return launch_one<__nv_bfloat16>(ctx, s, a, fast_ok);
+        case LOKAL_F32: return launch_one<float>(ctx, s, a, fast_ok, shared_machine);
+        case LOKAL_F16: return launch_one<__half>(ctx, s, a, fast_ok, shared_machine);
+        default: return launch_one<__nv_bfloat16>(ctx, s, a, fast_ok, shared_machine);
     }
 }
 
@@ -693,7 +698,7 @@ int launch_rope_table(lokal_cuda_ctx* ctx, cudaStream_t s, float theta, uint32_t
     return LOKAL_OK;
 }
 
-int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_params& p) {
+int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_params& p, bool shared_machine) {
     if (!p.cos_sin) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: cos_sin table is null");
     if (!p.q && !p.k) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: both q and k are null");
     if (p.head_dim == 0 || (p.head_dim & 1u)) return ctx->fail(LOKAL_ERR_BAD_ARG, "qk_rope: head_dim %u must be even and non-zero", p.head_dim);
@@ -760,7 +765,7 @@ int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_para
         a.n_kv = p.n_kv_heads;
         const bool fast = table_fast && tensor_fast(p.q, a.q_out, a.q_stride, a.q_out_stride, p.q_dtype) &&
                           tensor_fast(p.k, a.k_out, a.k_stride, a.k_out_stride, p.k_dtype);
-        return launch_by_type(ctx, s, a, p.q_dtype, fast);
+        return launch_by_type(ctx, s, a, p.q_dtype, fast, shared_machine);
     }
     // q and k of different types (the reference GPU layout: f32 q, f16 k in the cache): one launch each.
     if (p.q) {
@@ -770,7 +775,7 @@ int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_para
         aq.n_q = p.n_q_heads;
         aq.n_kv = 0;
         const bool fast = table_fast && tensor_fast(p.q, a.q_out, a.q_stride, a.q_out_stride, p.q_dtype);
-        int rc = launch_by_type(ctx, s, aq, p.q_dtype, fast);
+        int rc = launch_by_type(ctx, s, aq, p.q_dtype, fast, shared_machine);
         if (rc != LOKAL_OK) return rc;
     }
     if (p.k) {
@@ -780,7 +785,7 @@ int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_para
         ak.n_q = 0;
         ak.n_kv = p.n_kv_heads;
         const bool fast = table_fast && tensor_fast(p.k, a.k_out, a.k_stride, a.k_out_stride, p.k_dtype);
-        return launch_by_type(ctx, s, ak, p.k_dtype, fast);
+        return launch_by_type(ctx, s, ak, p.k_dtype, fast, shared_machine);
     }
     return LOKAL_OK;
 }

@@ -1,6 +1,6 @@
 """A second, independent reading of the GGUF block formats: vectorised numpy decoders written from the block
 layouts (sizeof and field order as src/gguf/dequant.rs:94-114 lists them), used to cross-check the C++ oracle
-before either judges the GPU. Every f32 multiply / subtract is a separate numpy f32 operation, so the rounding
+before either is used to check the GPU. Every f32 multiply / subtract is a separate numpy f32 operation, so the rounding
 sequence is the one the reference's expressions have. Returns f32 arrays of shape [n_blocks * elems]."""
 import numpy as np
 

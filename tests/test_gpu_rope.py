@@ -314,3 +314,23 @@ def test_qwen35_partial_rope_large_batch(ctx, dev, oracle, dtype, monkeypatch):
     else:
         synth.check_half(q1, rq, "q", dtype, atol=ROPE_HALF_ATOL)
         synth.check_half(k1, rk, "k", dtype, atol=ROPE_HALF_ATOL)
+
+
+@pytest.mark.parametrize("dtype,nq,nkv,hd,norm", [(BF16, 40, 7, 128, True), (F32, 20, 3, 256, True), (BF16, 80, 12, 256, True),
+                                                   (F32, 40, 7, 128, False)])
+def test_rows_that_fill_the_staging_budget(ctx, dev, oracle, dtype, nq, nkv, hd, norm):
+    # Rows whose staged size sits at the edge of the 48 KB a kernel gets without opting in (47 head slots of 128 in
+    # bf16 with qk-norm: four rows per CTA fit the dynamic part alone, but not together with the staged norm weights):
+    # the launcher must count the static part too and pick fewer rows per CTA, or another kernel, never a failed launch.
+    cfg = synth.LayerConfig("edge", dtype, 1900, 64, 64, nq, nkv, hd, 100, 1e6, 1e-6, 1, qk_bias=False, qk_norm=norm, seed=47)
+    rows = cfg.rows
+    d = synth.layer_inputs(cfg, rows)
+    q, k = run_qk(ctx, dev, cfg, d, rows, pos0=3)
+    rq, rk = oracle.qk_rope_rows(d["q"], d["k"], n_q_heads=nq, n_kv_heads=nkv, head_dim=hd, theta=cfg.theta, eps=cfg.eps,
+                                 q_norm_w=d.get("q_norm_w"), k_norm_w=d.get("k_norm_w"), pos0=3, threads=8)
+    if dtype == F32:
+        synth.check_f32(q, rq, "q")
+        synth.check_f32(k, rk, "k")
+    else:
+        synth.check_half(q, rq, "q", dtype, atol=ROPE_HALF_ATOL)
+        synth.check_half(k, rk, "k", dtype, atol=ROPE_HALF_ATOL)
