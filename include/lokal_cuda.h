@@ -284,6 +284,18 @@ LOKAL_API int lokal_cuda_embed_gather(lokal_cuda_ctx* ctx, lokal_cuda_stream s, 
                                       size_t vocab, size_t dim, const uint32_t* ids, size_t n, void* out,
                                       int out_dtype);
 
+/* Embedding gather and the RMSNorm that follows it in a step, as one call: x[i] = dequant(table[ids[i]]) and
+ * xn[i] = rmsnorm(x[i], w, eps). The reference's step starts with exactly this pair (Model::forward, src/model.rs:200-209:
+ * the row copy, then the first block's input_layernorm; MetalSession::run_from encodes `embed` and `rmsnorm*` back to
+ * back, src/gpu/metal.rs:2525, 2552). With a quantised table the norm rides in the gather's launch: the warp that stored
+ * a row sums the squares of the values as stored (rounded to out_dtype, what a separate norm launch would read) and
+ * writes xn. Float tables and unaligned buffers run the two launches one after the other; the results follow the same
+ * definition either way. x and xn are n x dim of out_dtype; w is [dim] of w_dtype. Out-of-range ids as in embed_gather
+ * (x and xn rows zero, LOKAL_ERR_ID_RANGE at the next synchronisation). */
+LOKAL_API int lokal_cuda_embed_gather_rmsnorm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* table, int ggml_type,
+                                              size_t vocab, size_t dim, const uint32_t* ids, size_t n, void* x, void* xn,
+                                              const void* w, float eps, int out_dtype, int w_dtype);
+
 /* Dequantise `rows` consecutive rows: the bit-for-bit gate kernel
  * lm_dequant_oracle (src/gpu/kernels.metal:1417-1428, LmDeqParams :1411). */
 LOKAL_API int lokal_cuda_dequant_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, int ggml_type, const void* src,

@@ -129,6 +129,7 @@ SIGNATURES = {
     "lokal_cuda_qk_rope_pos_noalloc": (_i, [_vp, _vp, C.POINTER(QkRopeParams), _f, _vp, _i64]),
     "lokal_cuda_swiglu": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i]),
     "lokal_cuda_embed_gather": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _vp, _sz, _vp, _i]),
+    "lokal_cuda_embed_gather_rmsnorm": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _vp, _sz, _vp, _vp, _vp, _f, _i, _i]),
     "lokal_cuda_dequant_rows": (_i, [_vp, _vp, _i, _vp, _sz, _sz, _vp, _i]),
     "lokal_cuda_window_cfg": (_i, [C.c_uint64, C.c_uint64, C.c_uint64, C.POINTER(KvLayout)]),
     "lokal_cuda_window_slot_of": (C.c_uint64, [C.POINTER(KvLayout), C.c_uint64]),

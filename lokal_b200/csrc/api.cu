@@ -476,6 +476,15 @@ int lokal_cuda_embed_gather(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void
     return lokal::launch_gather(ctx, as_stream(s), table, ggml_type, vocab, dim, ids, n, out, out_dtype);
 }
 
+int lokal_cuda_embed_gather_rmsnorm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const void* table, int ggml_type, size_t vocab,
+                                    size_t dim, const uint32_t* ids, size_t n, void* x, void* xn, const void* w, float eps,
+                                    int out_dtype, int w_dtype) {
+    LOKAL_ENTER(ctx);
+    if (!ids && n) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather_rmsnorm: ids are null");
+    if (!w || !xn) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather_rmsnorm: weights and the normed output must be non-null");
+    return lokal::launch_gather_norm(ctx, as_stream(s), table, ggml_type, vocab, dim, ids, n, x, out_dtype, w, w_dtype, xn, eps, nullptr);
+}
+
 int lokal_cuda_dequant_rows(lokal_cuda_ctx* ctx, lokal_cuda_stream s, int ggml_type, const void* src, size_t rows,
                             size_t cols, void* out, int out_dtype) {
     LOKAL_ENTER(ctx);

@@ -495,4 +495,7 @@ int launch_swiglu(lokal_cuda_ctx* ctx, cudaStream_t s, const void* gate, const v
                   size_t n, int dtype, int h_dtype);
 int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int ggml_type, size_t vocab, size_t dim,
                   const uint32_t* ids, size_t n, void* out, int out_dtype);
+int launch_gather_norm(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int ggml_type, size_t vocab, size_t dim,
+                       const uint32_t* ids, size_t n, void* out, int out_dtype, const void* norm_w, int w_dtype, void* xn,
+                       float eps, int* launches);
 }  // namespace lokal

@@ -48,6 +48,11 @@ struct GatherArgs {
     unsigned* err_word;
     unsigned wait_limit;   // polls of a staged copy's mbarrier before the kernel gives up (kWaitLimit)
     unsigned extra_tx;     // 0; a test sets it so that a copy never completes its barrier and the bounded wait runs out
+    // gather fused with the RMSNorm that follows it in a step (the FUSE variant of the staged kernel)
+    const void* norm_w;    // [dim] weights
+    void* xn;              // [n][dim] normed rows, of the output type
+    float eps, inv_dim;
+    int w_dtype, w_vec_ok;
 };
 
 // ---- block decoders: EPL consecutive elements starting at element e (e % EPL == 0), as EPL/2 pairs ----
@@ -591,7 +596,12 @@ __device__ __forceinline__ void store_out16(OutT* dst, const float2 (&y)[VecOf<O
 constexpr unsigned kGatherStages = LOKAL_GATHER_STAGES;
 static_assert(kGatherStages >= 2 && kGatherStages <= 4, "the row loop is unrolled by the ring length");
 
-template <int QT, typename OutT>
+// FUSE: the first RMSNorm of a step in the same launch (MetalSession::run_from encodes `embed` and then
+// `rmsnorm` over the same rows, src/gpu/metal.rs:2525, 2552). The warp that has just stored a row x accumulates the
+// sum of squares of the values AS STORED (rounded to the row type, what a separate norm launch would read), reads its
+// own 16-byte vectors back (they are in L2), and writes xn = (x * scale) * w: one launch and one pass over the table
+// row instead of two launches.
+template <int QT, typename OutT, bool FUSE = false>
 __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherArgs a) {
     pdl_sync();
     constexpr int EPL = VecOf<OutT>::N;
@@ -672,6 +682,20 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
     // Decodes the row waiting in stage st into output row i; false when the bounded wait on its copy gave up.
     auto consume = [&](unsigned long long i, unsigned st) -> bool {
         OutT* orow = reinterpret_cast<OutT*>(a.out) + i * a.dim;
+        float2 ssq = make_float2(0.0f, 0.0f);  // FUSE: this lane's sum of squares of the row as stored
+        // one 16-byte vector of the row: stored, and (FUSE) its stored values squared and summed
+        auto emit = [&](unsigned e, const uint4& pk) {
+            st_stream(orow + e, pk);
+            if constexpr (FUSE) {
+                float2 r[EPL / 2];
+                unpack16p<OutT>(pk, r);
+#pragma unroll
+                for (int k = 0; k < EPL / 2; k++) {
+                    if (sizeof(OutT) == 2) ssq = fma2(r[k], r[k], ssq);
+                    else ssq = add2(ssq, mul2(r[k], r[k]));
+                }
+            }
+        };
         const unsigned m = sel(mode, st);
         if (m == 1) {
             const unsigned ph = sel(parity, st);
@@ -692,7 +716,7 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
             float2 z[EPL / 2];
 #pragma unroll
             for (int k = 0; k < EPL / 2; k++) z[k] = make_float2(0.0f, 0.0f);
-            for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) store_out16<OutT>(orow + e, z);
+            for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) emit(e, pack16p<OutT>(z));
         } else {
             const unsigned char* row = sptr(st) + sel(offs, st);
             constexpr unsigned kSmallBlock = QT == LOKAL_Q8_0 ? 34u : (QT == LOKAL_Q5_0 ? 22u : ((QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL) ? 18u : 0u));
@@ -703,11 +727,11 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
                 constexpr bool kHalfPath = std::is_same<OutT, __half>::value && (QT == LOKAL_Q8_0 || QT == LOKAL_Q4_0 || QT == LOKAL_Q5_0);
                 for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL, bp += EPL * kSmallBlock) {
                     if constexpr (kHalfPath) {
-                        st_stream(orow + e, decode_small_block_h8<QT>(bp, in_block));
+                        emit(e, decode_small_block_h8<QT>(bp, in_block));
                     } else {
                         float2 y[EPL / 2];
                         decode_block<QT, EPL, true>(bp, in_block, lut, y);
-                        store_out16<OutT>(orow + e, y);
+                        emit(e, pack16p<OutT>(y));
                     }
                 }
             } else {
@@ -731,14 +755,14 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
                                 const float d1s = __shfl_sync(0xffffffffu, d1, src_lane), nm1s = __shfl_sync(0xffffffffu, nm1, src_lane);
                                 float2 y[EPL / 2];
                                 k45_quants<QT, EPL>(bp, lane * 8u, both(d1s), both(nm1s), y);
-                                store_out16<OutT>(orow + e, y);
+                                emit(e, pack16p<OutT>(y));
                             }
                         } else {
                             for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
                                 const float d1s = __shfl_sync(0xffffffffu, d1, e >> 5), nm1s = __shfl_sync(0xffffffffu, nm1, e >> 5);
                                 float2 y[EPL / 2];
                                 k45_quants<QT, EPL>(row + (e >> 8) * BB, e & 255u, both(d1s), both(nm1s), y);
-                                store_out16<OutT>(orow + e, y);
+                                emit(e, pack16p<OutT>(y));
                             }
                         }
                         done = true;
@@ -749,13 +773,29 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
                         float2 y[EPL / 2];
                         if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
                         else decode_block<QT, EPL>(row, e, lut, y);
-                        store_out16<OutT>(orow + e, y);
+                        emit(e, pack16p<OutT>(y));
                     }
                 }
             }
         }
         __syncwarp();  // every lane is done with the stage before it is refilled
         put(mode, st, 0u);
+        if constexpr (FUSE) {
+            // xn = (x * scale) * w over the row this warp has just stored; each lane reads back its own vectors
+            const float ss = warp_sum(ssq.x + ssq.y);
+            const float scale = inv_rms<OutT>(ss, static_cast<float>(a.dim), a.inv_dim, a.eps);
+            const float2 s2 = make_float2(scale, scale);
+            OutT* nrow = reinterpret_cast<OutT*>(a.xn) + i * a.dim;
+            for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
+                float2 v[EPL / 2], y[EPL / 2];
+                unpack16p<OutT>(*reinterpret_cast<const uint4*>(orow + e), v);
+                float wf[EPL];
+                load_w<EPL>(a.norm_w, a.w_dtype, e, a.w_vec_ok, wf);
+#pragma unroll
+                for (int k = 0; k < EPL / 2; k++) y[k] = mul2(mul2(v[k], s2), make_float2(wf[2 * k], wf[2 * k + 1]));
+                st_stream(nrow + e, pack16p<OutT>(y));
+            }
+        }
         return true;
     };
 
@@ -861,8 +901,11 @@ __global__ void __launch_bounds__(256) gather_float_kernel(const GatherArgs a, i
     }
 }
 
+// Returns through *fused whether the norm went into the gather launch (quantised table, staged kernel); the caller
+// launches the norm itself otherwise.
 template <typename OutT>
-int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type, bool aligned) {
+int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type, bool aligned, bool* fused) {
+    if (fused) *fused = false;
     const unsigned long long row_warps_blocks = (a.n + 7) / 8;
     if (row_warps_blocks > 0x7fffffffull) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: too many rows for one launch");
     if (ggml_type == LOKAL_F32 || ggml_type == LOKAL_F16 || ggml_type == LOKAL_BF16) {
@@ -889,7 +932,10 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
         return LOKAL_OK;
     }
     void (*kern)(const GatherArgs) = nullptr;
-    for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT>; });
+    const bool fuse = a.norm_w != nullptr;
+    if (fuse) for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT, true>; });
+    else for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT, false>; });
+    if (fused) *fused = fuse;
     if (smem > 48u * 1024u) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "embed_gather: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -918,7 +964,22 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
 
 int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int ggml_type, size_t vocab, size_t dim,
                   const uint32_t* ids, size_t n, void* out, int out_dtype) {
+    return launch_gather_norm(ctx, s, table, ggml_type, vocab, dim, ids, n, out, out_dtype, nullptr, 0, nullptr, 0.0f, nullptr);
+}
+
+// Gather, and (norm_w != null) the RMSNorm of the gathered rows into xn: in the same launch where the staged kernel
+// takes the table, as a second launch otherwise. *launches, when given, receives the number of kernels launched.
+int launch_gather_norm(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int ggml_type, size_t vocab, size_t dim,
+                       const uint32_t* ids, size_t n, void* out, int out_dtype, const void* norm_w, int w_dtype, void* xn,
+                       float eps, int* launches) {
+    if (launches) *launches = 0;
     if (!table || !out) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: table and out must be non-null");
+    if (norm_w) {
+        if (!xn) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather_rmsnorm: the normed output is null");
+        if (!is_act_type(w_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather_rmsnorm: weight type %d is not F32/F16/BF16", w_dtype);
+        if (!aligned_to(norm_w, type_size(w_dtype)) || (is_act_type(out_dtype) && !aligned_to(xn, type_size(out_dtype))))
+            return ctx->fail(LOKAL_ERR_MISALIGNED, "embed_gather_rmsnorm: a pointer is not aligned to its element size");
+    }
     const size_t be = lokal_cuda_blk_elems(ggml_type);
     if (be == 0) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: ggml type %d is not a float type, a Q*_0 / Q*_K block type or an i-quant (Q4_1, Q5_1, Q8_1, Q8_K are not covered)", ggml_type);
     if (!is_act_type(out_dtype)) return ctx->fail(LOKAL_ERR_UNSUPPORTED, "embed_gather: output type %d is not F32/F16/BF16", out_dtype);
@@ -957,11 +1018,29 @@ int launch_gather(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, int gg
                              ggml_type, g.name);
     }
     const bool aligned = aligned_to(table, 16) && aligned_to(out, 16) && (dim * type_size(out_dtype)) % 16 == 0;
-    switch (out_dtype) {
-        case LOKAL_F32: return launch_out<float>(ctx, s, a, ggml_type, aligned);
-        case LOKAL_F16: return launch_out<__half>(ctx, s, a, ggml_type, aligned);
-        default: return launch_out<__nv_bfloat16>(ctx, s, a, ggml_type, aligned);
+    if (norm_w && aligned && aligned_to(xn, 16) && tune_env("LOKAL_CUDA_GATHER_FUSE_NORM", 1) != 0) {
+        a.norm_w = norm_w;
+        a.xn = xn;
+        a.eps = eps;
+        a.inv_dim = 1.0f / static_cast<float>(dim);
+        a.w_dtype = w_dtype;
+        a.w_vec_ok = aligned_to(norm_w, 16);
     }
+    bool fused = false;
+    int rc;
+    switch (out_dtype) {
+        case LOKAL_F32: rc = launch_out<float>(ctx, s, a, ggml_type, aligned, &fused); break;
+        case LOKAL_F16: rc = launch_out<__half>(ctx, s, a, ggml_type, aligned, &fused); break;
+        default: rc = launch_out<__nv_bfloat16>(ctx, s, a, ggml_type, aligned, &fused); break;
+    }
+    if (rc != LOKAL_OK) return rc;
+    if (launches) *launches = 1;
+    if (norm_w && !fused) {  // float tables, the any-alignment kernel: the norm is its own launch
+        rc = launch_norm(ctx, s, out, nullptr, norm_w, xn, nullptr, n, dim, eps, out_dtype, w_dtype, 0);
+        if (rc != LOKAL_OK) return rc;
+        if (launches) *launches = 2;
+    }
+    return LOKAL_OK;
 }
 
 }  // namespace lokal

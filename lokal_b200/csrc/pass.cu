@@ -126,13 +126,14 @@ int layer_ops(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, cudaStream_t s_rope, cuda
 int step_head(lokal_cuda_ctx* ctx, lokal_cuda_pass* P, cudaStream_t s_norm, cudaStream_t s_rope, const uint32_t* ids_dev,
               const int32_t* pos_dev, int64_t pos0, size_t rows) {
     const lokal_pass_config& c = P->cfg;
-    int rc = lokal::launch_gather(ctx, s_norm, P->embed_table, c.embed_type, c.vocab, c.hidden, ids_dev, rows, P->x, c.dtype);
+    // gather and first input norm: one launch for a quantised table
+    int head_launches = 0;
+    int rc = lokal::launch_gather_norm(ctx, s_norm, P->embed_table, c.embed_type, c.vocab, c.hidden, ids_dev, rows, P->x, c.dtype,
+                                       P->norm_w, c.w_dtype, P->xn0, c.eps, &head_launches);
     if (rc != LOKAL_OK) return rc;
     rc = lokal::launch_rope_table(ctx, s_rope, c.theta, c.rot_dim, pos_dev, pos0, rows, P->cos_sin);
     if (rc != LOKAL_OK) return rc;
-    rc = lokal::launch_norm(ctx, s_norm, P->x, nullptr, P->norm_w, P->xn0, nullptr, rows, c.hidden, c.eps, c.dtype, c.w_dtype, 0);
-    if (rc != LOKAL_OK) return rc;
-    P->launches += 3;
+    P->launches += 1 + static_cast<unsigned>(head_launches);
     return LOKAL_OK;
 }
 

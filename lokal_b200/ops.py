@@ -200,6 +200,11 @@ class Context:
         self._check(self._lib.lokal_cuda_embed_gather(self._h, stream, _ptr(table), ggml_type, vocab, dim, _ptr(ids),
                                                       n, _ptr(out), out_dtype))
 
+    def embed_gather_rmsnorm(self, table, ids, x, xn, w, *, ggml_type, vocab, dim, n, eps, out_dtype=F32, w_dtype=F32, stream=None):
+        """x[i] = dequant(table[ids[i]]), xn[i] = rmsnorm(x[i], w, eps): one launch for a quantised table."""
+        self._check(self._lib.lokal_cuda_embed_gather_rmsnorm(self._h, stream, _ptr(table), ggml_type, vocab, dim, _ptr(ids), n,
+                                                               _ptr(x), _ptr(xn), _ptr(w), eps, out_dtype, w_dtype))
+
     def dequant_rows(self, src, out, *, ggml_type, rows, cols, out_dtype=F32, stream=None):
         self._check(self._lib.lokal_cuda_dequant_rows(self._h, stream, ggml_type, _ptr(src), rows, cols, _ptr(out),
                                                       out_dtype))

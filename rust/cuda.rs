@@ -278,7 +278,9 @@ impl<'e> StepCore<'e> {
             check(ctx, lokal_cuda_embed_gather(ctx, s, e.embed, e.embed_type, e.cfg.vocab_size, h, self.ids, n, self.x, LOKAL_F32))?;
             check(ctx, lokal_cuda_rope_table(ctx, s, e.cfg.rope_theta, hd, self.positions, 0, n, self.rope_table))?;
             check(ctx, lokal_cuda_kv_rows(ctx, s, &self.layout, self.positions, 0, self.slots, 0, n, self.cache_rows))?;
-            // first input norm; every later one is fused with the residual add that precedes it
+            // first input norm, with the f16 copy the projections read; every later norm is fused with the residual add
+            // that precedes it. (An engine that keeps 16-bit activations and needs no second copy takes gather and
+            // norm as one launch: lokal_cuda_embed_gather_rmsnorm.)
             check(ctx, lokal_cuda_rmsnorm(ctx, s, self.x, e.layers[0].input_ln, self.xn, self.xn_h, n, h, eps, LOKAL_F32, LOKAL_F16, LOKAL_F16))?;
             for (l, w) in e.layers.iter().enumerate() {
                 e.mm.matmul(s, self.xn_h, w.q_proj, n, self.q)?;

@@ -245,6 +245,9 @@ pub fn lokal_cuda_create(device: c_int, out: *mut *mut LokalCudaCtx) -> c_int;
         out: *mut c_void, out_h: *mut c_void, n: usize, dtype: c_int, h_dtype: c_int) -> c_int;
     pub fn lokal_cuda_embed_gather(ctx: *mut LokalCudaCtx, s: LokalCudaStream, table: *const c_void,
         ggml_type: c_int, vocab: usize, dim: usize, ids: *const u32, n: usize, out: *mut c_void, out_dtype: c_int) -> c_int;
+    pub fn lokal_cuda_embed_gather_rmsnorm(ctx: *mut LokalCudaCtx, s: LokalCudaStream, table: *const c_void, ggml_type: c_int,
+        vocab: usize, dim: usize, ids: *const u32, n: usize, x: *mut c_void, xn: *mut c_void, w: *const c_void, eps: f32,
+        out_dtype: c_int, w_dtype: c_int) -> c_int;
     pub fn lokal_cuda_dequant_rows(ctx: *mut LokalCudaCtx, s: LokalCudaStream, ggml_type: c_int,
         src: *const c_void, rows: usize, cols: usize, out: *mut c_void, out_dtype: c_int) -> c_int;
     pub fn lokal_cuda_window_cfg(window: u64, sink: u64, prefill_chunk: u64, out: *mut LokalKvLayout) -> c_int;

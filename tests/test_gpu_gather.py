@@ -248,3 +248,73 @@ def test_f16_rows_of_single_product_types_over_every_scale_and_quant(ctx, dev, o
     rows = slice(0x3000, 0x3040)
     ref = synth.round_to(oracle.embed_gather(table[rows.start * per_row * bb:rows.stop * per_row * bb], ty, 64, 256, np.arange(64, dtype=np.uint32)), F16)
     synth.assert_bits_equal(got[rows], ref, "oracle slice")
+
+
+@pytest.mark.parametrize("ty,dim", [(Q8_0, 896), (Q8_0, 2048), (Q4_K, 1024), (Q4_K, 2304), (14, 512), (21, 768), (20, 64)])
+@pytest.mark.parametrize("out_dtype", [F32, F16, BF16])
+def test_gather_fused_with_the_first_norm(ctx, dev, oracle, ty, dim, out_dtype, monkeypatch):
+    """lokal_cuda_embed_gather_rmsnorm: x is bit for bit the gather's, xn is the RMSNorm of x as stored (rounded to the row
+    type), within the norm's bar against the oracle, and equal to what gather + rmsnorm give as two launches to the last
+    bits of the scale; an out-of-range id gives zero rows in both outputs and the error code."""
+    import lokal_b200 as L
+    if ty in L.capi.GRID_TYPES:
+        from test_oracle_iq_grids import GRIDS
+        ctx.set_iq_grids(GRIDS)
+        oracle.set_iq_grids(GRIDS)
+    vocab, n, eps = 300, 700, 1e-6
+    table = synth.quant_table(ty, vocab, dim, 31) if ty not in (Q8_0, Q4_K) else (synth.q8_0_table if ty == Q8_0 else synth.q4_k_table)(vocab, dim, 31)
+    ids = synth.token_ids_uniform(vocab, n, 32)
+    ids[5] = vocab + 7  # out of range
+    w = synth.round_to(1 + 0.1 * np.random.default_rng(33).standard_normal(dim, dtype=np.float32), out_dtype)
+    dt, di, dw = dev.put(table), dev.put(ids.view(np.int32)), dev.put(w, out_dtype)
+    x, xn = dev.empty((n, dim), out_dtype, fill=5.0), dev.empty((n, dim), out_dtype, fill=5.0)
+    ctx.embed_gather_rmsnorm(dt, di, x, xn, dw, ggml_type=ty, vocab=vocab, dim=dim, n=n, eps=eps, out_dtype=out_dtype, w_dtype=out_dtype)
+    with pytest.raises(L.LokalCudaError) as e:
+        ctx.stream_sync()
+    assert e.value.status == L.capi.ERR_ID_RANGE
+    good = np.ones(n, bool)
+    good[5] = False
+    want_x = synth.round_to(oracle.embed_gather(table, ty, vocab, dim, np.where(good, ids, 0).astype(np.uint32)), out_dtype)
+    want_x[5] = 0.0
+    got_x, got_xn = dev.get(x), dev.get(xn)
+    synth.assert_bits_equal(got_x, want_x, "x of the fused call")
+    assert (got_xn[5] == 0.0).all()
+    _, ref_xn = oracle.add_rmsnorm_rows(want_x, None, w, eps)  # norm of the rows AS STORED
+    if out_dtype == F32:
+        # quantised rows can be large (scales |N(0, 0.01)| times quants up to 127): compare relative to the row's magnitude
+        tol = 1e-5 * np.maximum(1.0, np.abs(ref_xn).max())
+        assert np.abs(got_xn - ref_xn).max() <= tol
+    else:
+        synth.check_half(got_xn[good], ref_xn[good], "xn of the fused call", out_dtype, atol=1e-6)
+    # the two-launch form (LOKAL_CUDA_GATHER_FUSE_NORM=0 keeps the norm in its own launch)
+    x2, xn2 = dev.empty((n, dim), out_dtype, fill=5.0), dev.empty((n, dim), out_dtype, fill=5.0)
+    monkeypatch.setenv("LOKAL_CUDA_GATHER_FUSE_NORM", "0")
+    ctx.embed_gather_rmsnorm(dt, di, x2, xn2, dw, ggml_type=ty, vocab=vocab, dim=dim, n=n, eps=eps, out_dtype=out_dtype, w_dtype=out_dtype)
+    monkeypatch.delenv("LOKAL_CUDA_GATHER_FUSE_NORM")
+    with pytest.raises(L.LokalCudaError):
+        ctx.stream_sync()
+    synth.assert_bits_equal(dev.get(x2), got_x, "x, two launches")
+    two = dev.get(xn2)
+    rel = np.abs(two - got_xn) / np.maximum(np.abs(two), 1e-20)
+    assert rel.max() <= (2e-6 if out_dtype == F32 else 2.0 ** -7), "fused and two-launch norms differ by more than the last bits of the scale"
+
+
+def test_gather_rmsnorm_on_float_tables_and_refusals(ctx, dev, oracle):
+    import lokal_b200 as L
+    vocab, dim, n = 50, 96, 33
+    table = synth.f32_table(vocab, dim, 3)
+    ids = synth.token_ids_uniform(vocab, n, 4)
+    w = (1 + 0.1 * np.random.default_rng(5).standard_normal(dim, dtype=np.float32)).astype(np.float32)
+    dt, di, dw = dev.put(table), dev.put(ids.view(np.int32)), dev.put(w)
+    x, xn = dev.empty((n, dim), F32, fill=5.0), dev.empty((n, dim), F32, fill=5.0)
+    ctx.embed_gather_rmsnorm(dt, di, x, xn, dw, ggml_type=F32, vocab=vocab, dim=dim, n=n, eps=1e-5)
+    ctx.stream_sync()
+    synth.assert_bits_equal(dev.get(x), table[ids], "dense rows")
+    _, ref = oracle.add_rmsnorm_rows(table[ids], None, w, 1e-5)
+    synth.check_f32(dev.get(xn), ref, "norm of dense rows")
+    for kw in (dict(w=None), dict(xn=None)):
+        args = dict(table=dt, ids=di, x=x, xn=xn, w=dw)
+        args.update(kw)
+        with pytest.raises(L.LokalCudaError) as e:
+            ctx.embed_gather_rmsnorm(args["table"], args["ids"], args["x"], args["xn"], args["w"], ggml_type=F32, vocab=vocab, dim=dim, n=n, eps=1e-5)
+        assert e.value.status == L.capi.ERR_BAD_ARG
