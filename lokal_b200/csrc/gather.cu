@@ -41,6 +41,10 @@ struct GatherArgs {
     unsigned long long n;
     unsigned long long vocab;
     unsigned long long table_bytes;
+    // The staged kernel keeps its row bookkeeping in 32 bits (the host hands it at most 2^30 rows per launch):
+    unsigned n32;        // rows of this launch
+    unsigned max_id;     // min(vocab, 2^32) - 1: an id above it is out of range
+    unsigned bulk_ids;   // ids below it have their 16-byte-aligned window inside the table (all but, at most, the last row)
     unsigned dim;
     unsigned row_bytes;
     unsigned stage_bytes;  // per warp per stage, multiple of 16
@@ -603,7 +607,7 @@ static_assert(kGatherStages >= 2 && kGatherStages <= 4, "the row loop is unrolle
 // row instead of two launches.
 template <int QT, typename OutT, bool FUSE = false>
 __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherArgs a) {
-    pdl_sync();
+    pdl_launch();  // the wait for the kernel before this one comes after the shared-memory set-up, which touches no global memory
     constexpr int EPL = VecOf<OutT>::N;
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr unsigned NST = kGatherStages;
@@ -623,9 +627,13 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
         if (threadIdx.x < 16) lut[threadIdx.x] = iq4_value(threadIdx.x);
         __syncthreads();
     }
+    pdl_wait();
 
-    const unsigned long long total_warps = static_cast<unsigned long long>(gridDim.x) * warps_per_cta;
-    const unsigned long long first = static_cast<unsigned long long>(blockIdx.x) * warps_per_cta + warp_in_cta;
+    // Rows, ids and the look-ahead are 32-bit values here: a row costs this warp a fixed number of instructions before
+    // its first element is decoded, and every lane executes them.
+    const unsigned total_warps = gridDim.x * warps_per_cta;
+    const unsigned first = blockIdx.x * warps_per_cta + warp_in_cta;
+    const unsigned n = a.n32;
 
     // Ring state of the stages (uniform across the warp), one register per stage and field:
     //   mode    0 = row invalid (zero fill), 1 = bulk copy issued, 2 = bytes already placed by plain loads
@@ -652,24 +660,22 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
     auto bar = [&](unsigned st) { return bar0 + 8 * st; };
 
     // The id of a row is fetched one iteration before the row's copy is issued, so the copy never waits for it.
-    auto id_of = [&](unsigned long long i) { return a.ids ? static_cast<unsigned long long>(__ldg(a.ids + i)) : i; };
-    auto issue = [&](unsigned long long id, unsigned st) {
-        if (id >= a.vocab) {
+    auto id_of = [&](unsigned i) { return a.ids ? __ldg(a.ids + i) : i; };
+    auto issue = [&](unsigned id, unsigned st) {
+        if (id > a.max_id) {
             put(mode, st, 0u);
             if (lane == 0) atomicOr(a.err_word, kErrIdRange);
             return;
         }
-        const unsigned long long start = id * a.row_bytes;
-        const unsigned long long w0 = start & ~15ull;
-        const unsigned long long w1 = (start + a.row_bytes + 15ull) & ~15ull;
-        const unsigned off = static_cast<unsigned>(start - w0);
+        const unsigned long long start = static_cast<unsigned long long>(id) * a.row_bytes;  // one widening multiply
+        const unsigned off = static_cast<unsigned>(start) & 15u;
         put(offs, st, off);
-        if (w1 <= a.table_bytes) {
+        if (id < a.bulk_ids) {
             put(mode, st, 1u);
             if (lane == 0) {
-                const unsigned bytes = static_cast<unsigned>(w1 - w0);
+                const unsigned bytes = (off + a.row_bytes + 15u) & ~15u;
                 mbar_expect_tx(bar(st), bytes + a.extra_tx);
-                bulk_copy_g2s(smem_addr(sptr(st)), a.table + w0, bytes, bar(st));
+                bulk_copy_g2s(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st));
             }
         } else {
             // The window would run past the end of the table (last row only): plain byte loads.
@@ -680,8 +686,8 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
     };
 
     // Decodes the row waiting in stage st into output row i; false when the bounded wait on its copy gave up.
-    auto consume = [&](unsigned long long i, unsigned st) -> bool {
-        OutT* orow = reinterpret_cast<OutT*>(a.out) + i * a.dim;
+    auto consume = [&](unsigned i, unsigned st) -> bool {
+        OutT* orow = reinterpret_cast<OutT*>(a.out) + static_cast<unsigned long long>(i) * a.dim;
         float2 ssq = make_float2(0.0f, 0.0f);  // FUSE: this lane's sum of squares of the row as stored
         // one 16-byte vector of the row: stored, and (FUSE) its stored values squared and summed
         auto emit = [&](unsigned e, const uint4& pk) {
@@ -785,7 +791,7 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
             const float ss = warp_sum(ssq.x + ssq.y);
             const float scale = inv_rms<OutT>(ss, static_cast<float>(a.dim), a.inv_dim, a.eps);
             const float2 s2 = make_float2(scale, scale);
-            OutT* nrow = reinterpret_cast<OutT*>(a.xn) + i * a.dim;
+            OutT* nrow = reinterpret_cast<OutT*>(a.xn) + static_cast<unsigned long long>(i) * a.dim;
             for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
                 float2 v[EPL / 2], y[EPL / 2];
                 unpack16p<OutT>(*reinterpret_cast<const uint4*>(orow + e), v);
@@ -801,37 +807,250 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
 
     // Prologue: the copies of this warp's first NST - 1 rows are in flight before the first one is decoded, and the
     // id of the row after them is on its way.
-    unsigned long long id_next = 0;
+    unsigned id_next = 0;
     {
-        unsigned long long r = first;
+        unsigned r = first;
 #pragma unroll
         for (unsigned st = 0; st + 1 < NST; st++, r += total_warps) {
-            if (r < a.n) issue(id_of(r), st);
+            if (r < n) issue(id_of(r), st);
         }
-        if (r < a.n) id_next = id_of(r);
+        if (r < n) id_next = id_of(r);
     }
     constexpr bool kUnrollRing = QT == LOKAL_Q8_0 || QT == LOKAL_Q5_0 || QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL;
-    auto step = [&](unsigned long long i, unsigned st) {  // row i waits in stage st; the copy issued now goes to the stage before it
-        const unsigned long long ahead = i + (NST - 1) * total_warps;
-        if (ahead < a.n) {
+    auto step = [&](unsigned i, unsigned st) {  // row i waits in stage st; the copy issued now goes to the stage before it
+        const unsigned ahead = i + (NST - 1) * total_warps;  // n <= 2^30 and a grid has fewer than 2^20 warps: no wrap
+        if (ahead < n) {
             issue(id_next, (st + NST - 1) % NST);
-            if (ahead + total_warps < a.n) id_next = id_of(ahead + total_warps);
+            if (ahead + total_warps < n) id_next = id_of(ahead + total_warps);
         }
         return consume(i, st);
     };
-    unsigned long long i = first;
+    unsigned i = first;
     if constexpr (kUnrollRing) {
-        while (i < a.n) {
+        while (i < n) {
 #pragma unroll
             for (unsigned st = 0; st < NST; st++) {
-                if (i >= a.n) break;
+                if (i >= n) break;
                 if (!step(i, st)) return;
                 i += total_warps;
             }
         }
     } else {
-        for (unsigned st = 0; i < a.n; i += total_warps, st = (st + 1 == NST) ? 0u : st + 1) {
+        for (unsigned st = 0; i < n; i += total_warps, st = (st + 1 == NST) ? 0u : st + 1) {
             if (!step(i, st)) return;
+        }
+    }
+}
+
+// ---- staged kernel, two rows per warp: 16-bit output rows ----
+// A row costs its warp a fixed ~120 instructions of bookkeeping (id, window, copy, wait, pointers) whatever its
+// length, and a 16-byte store of 16-bit values covers eight elements, so a warp finishes a 1024-element row in four
+// steps: for the embedding widths in use the bookkeeping is half of all instructions, and the kernel above is bound
+// by instruction issue (measured: 157 / 260 / 392 instructions per row for Q8_0 rows of 256 / 896 / 2048 elements
+// to f16, whatever the ids). Here each half of the warp owns a row: lanes 0-15 row 2p, lanes 16-31 row 2p + 1. The
+// bookkeeping instructions are the same ones, executed once for both rows with per-half values (ids, windows and
+// pointers differ by lane); lanes 0 and 16 issue their rows' copies in one instruction each, both against the one
+// mbarrier of the stage (two arrivals: a lane whose row needs no copy arrives with zero bytes, so every issued stage
+// completes and the wait stays warp-uniform). Same decoders, same values, same stores as the kernel above.
+//   mode of a half's row in a stage: 0 = id out of range (zero fill), 1 = bulk copy issued, 2 = bytes placed by plain
+//   loads, 3 = no row (the half past the last row of an odd count)
+template <int QT, typename OutT>
+__global__ void __launch_bounds__(256) gather_quant_pair_kernel(const GatherArgs a) {
+    pdl_launch();  // the wait for the kernel before this one comes after the shared-memory set-up
+    constexpr int EPL = VecOf<OutT>::N;
+    static_assert(EPL == 8, "two rows per warp are for 16-bit output rows");
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr unsigned NST = kGatherStages;
+    const unsigned warps_per_cta = blockDim.x >> 5;
+    const unsigned warp_in_cta = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned half = lane >> 4, l16 = lane & 15u;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem);
+    // this lane's row buffer of stage 0; stage st lies 2 * st * stage_bytes further on
+    unsigned char* stage0 = smem + ((warps_per_cta * NST * 8 + 127u) & ~127u) + (warp_in_cta * NST * 2u + half) * a.stage_bytes;
+    const uint32_t bar0 = smem_addr(&bars[warp_in_cta * NST]);
+    if (lane == 0) {
+#pragma unroll
+        for (unsigned st = 0; st < NST; st++) mbar_init(bar0 + 8 * st, 2);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    __shared__ float lut[16];  // the IQ4 codebook as floats; unused by the other block types
+    if constexpr (QT == LOKAL_IQ4_NL || QT == LOKAL_IQ4_XS) {
+        if (threadIdx.x < 16) lut[threadIdx.x] = iq4_value(threadIdx.x);
+        __syncthreads();
+    }
+    pdl_wait();
+
+    const unsigned total_warps = gridDim.x * warps_per_cta;
+    const unsigned first = blockIdx.x * warps_per_cta + warp_in_cta;  // pairs are dealt to warps grid-stride
+    const unsigned n = a.n32, n_pairs = (n + 1u) >> 1;
+
+    unsigned mode[NST], parity[NST], offs[NST];  // mode and offs differ between the halves, parity does not
+#pragma unroll
+    for (unsigned st = 0; st < NST; st++) {
+        mode[st] = 3u;
+        parity[st] = offs[st] = 0;
+    }
+    auto sel = [&](const unsigned (&arr)[NST], unsigned st) {
+        unsigned v = arr[0];
+#pragma unroll
+        for (unsigned t = 1; t < NST; t++) v = st == t ? arr[t] : v;
+        return v;
+    };
+    auto put = [&](unsigned (&arr)[NST], unsigned st, unsigned v) {
+#pragma unroll
+        for (unsigned t = 0; t < NST; t++) arr[t] = st == t ? v : arr[t];
+    };
+    auto sptr = [&](unsigned st) { return stage0 + st * 2u * a.stage_bytes; };
+    auto bar = [&](unsigned st) { return bar0 + 8 * st; };
+
+    // id of this half's row of pair p (the value is unused when the row does not exist)
+    auto id_of = [&](unsigned p) {
+        const unsigned i = 2u * p + half;
+        const unsigned ic = i < n ? i : n - 1u;
+        return a.ids ? __ldg(a.ids + ic) : ic;
+    };
+    auto issue = [&](unsigned p, unsigned id, unsigned st) {
+        unsigned m = 3u, off = 0, bytes = 0;
+        unsigned long long start = 0;
+        if (2u * p + half < n) {
+            if (id > a.max_id) {
+                m = 0u;
+                if (l16 == 0) atomicOr(a.err_word, kErrIdRange);
+            } else {
+                start = static_cast<unsigned long long>(id) * a.row_bytes;
+                off = static_cast<unsigned>(start) & 15u;
+                m = id < a.bulk_ids ? 1u : 2u;
+            }
+        }
+        put(offs, st, off);
+        put(mode, st, m);
+        if (l16 == 0) {
+            if (m == 1u) bytes = (off + a.row_bytes + 15u) & ~15u;
+            mbar_expect_tx(bar(st), m == 1u ? bytes + a.extra_tx : 0u);  // an arrival either way
+            if (m == 1u) bulk_copy_g2s(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st));
+        }
+        if (m == 2u) {  // the window would run past the end of the table (last row only): plain byte loads
+            unsigned char* dst = sptr(st) + off;
+            for (unsigned bidx = l16; bidx < a.row_bytes; bidx += 16) dst[bidx] = __ldg(a.table + start + bidx);
+        }
+    };
+
+    // Decodes the rows waiting in stage st into output rows 2p and 2p + 1; false when the bounded wait gave up.
+    auto consume = [&](unsigned p, unsigned st) -> bool {
+        const unsigned ph = sel(parity, st);
+        if (!mbar_wait_bounded(bar(st), ph, a.wait_limit)) {
+            if (lane == 0) atomicOr(a.err_word, kErrTimeout);
+            // give the copies still in flight one more bounded chance to land before leaving
+#pragma unroll
+            for (unsigned t = 0; t < NST; t++) {
+                if (t != st && __any_sync(0xffffffffu, mode[t] == 1u)) mbar_wait_bounded(bar(t), parity[t], a.wait_limit);
+            }
+            return false;
+        }
+        put(parity, st, ph ^ 1u);
+        __syncwarp();  // bytes placed by plain loads are visible to the half that reads them
+        const unsigned m = sel(mode, st);
+        OutT* orow = reinterpret_cast<OutT*>(a.out) + static_cast<unsigned long long>(2u * p + half) * a.dim;
+        const unsigned char* row = sptr(st) + sel(offs, st);
+        auto generic_row = [&]() {
+            for (unsigned e = l16 * EPL; e < a.dim; e += 16 * EPL) {
+                float2 y[EPL / 2];
+                if constexpr (kIsGridType<QT>) decode_grid_block<QT, EPL>(row, e, a.grid, y);
+                else decode_block<QT, EPL>(row, e, lut, y);
+                st_stream(orow + e, pack16p<OutT>(y));
+            }
+        };
+        if (__all_sync(0xffffffffu, m == 1u || m == 2u)) {  // both rows are there: the usual case, no divergence
+            constexpr unsigned kSmallBlock = QT == LOKAL_Q8_0 ? 34u : (QT == LOKAL_Q5_0 ? 22u : ((QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL) ? 18u : 0u));
+            if constexpr (kSmallBlock != 0) {
+                // 32-element blocks: a lane's offset inside its block never changes, and every step moves it four blocks on
+                const unsigned char* bp = row + (l16 >> 2) * kSmallBlock;
+                const unsigned in_block = (l16 * EPL) & 31u;
+                constexpr bool kHalfPath = std::is_same<OutT, __half>::value && (QT == LOKAL_Q8_0 || QT == LOKAL_Q4_0 || QT == LOKAL_Q5_0);
+                for (unsigned e = l16 * EPL; e < a.dim; e += 16 * EPL, bp += 4 * kSmallBlock) {
+                    if constexpr (kHalfPath) {
+                        st_stream(orow + e, decode_small_block_h8<QT>(bp, in_block));
+                    } else {
+                        float2 y[EPL / 2];
+                        decode_block<QT, EPL, true>(bp, in_block, lut, y);
+                        st_stream(orow + e, pack16p<OutT>(y));
+                    }
+                }
+            } else if constexpr (QT == LOKAL_Q4_K || QT == LOKAL_Q5_K) {
+                if (a.dim <= 1024u) {
+                    // Lane l of a half works out the scale and min of sub-blocks l and l + 16 of its row once; a step
+                    // (half a super-block per half-warp) fetches the pair of its sub-block with two shuffles. a.dim is a
+                    // multiple of 256, so every lane takes the same number of steps and all 32 execute every shuffle.
+                    constexpr unsigned BB = QT == LOKAL_Q4_K ? 144 : 176;
+                    float d1a = 0.0f, nm1a = 0.0f, d1b = 0.0f, nm1b = 0.0f;
+                    if (l16 * 32u < a.dim) k45_scale_min(row + (l16 >> 3) * BB, l16 & 7u, d1a, nm1a);
+                    if ((l16 + 16u) * 32u < a.dim) k45_scale_min(row + ((l16 + 16u) >> 3) * BB, l16 & 7u, d1b, nm1b);
+                    const unsigned src = (lane & 16u) + (l16 >> 2);
+                    const unsigned char* bp = row;
+                    for (unsigned k = 0, e = l16 * EPL; e < a.dim; k += 2, e += 256, bp += BB) {
+                        const float pd = k >= 4 ? d1b : d1a, pm = k >= 4 ? nm1b : nm1a;  // sub-blocks 16.. live in the second slot
+#pragma unroll
+                        for (unsigned h = 0; h < 2; h++) {
+                            const unsigned from = src + 4u * ((k + h) & 3u);
+                            const float ds = __shfl_sync(0xffffffffu, pd, from), ms = __shfl_sync(0xffffffffu, pm, from);
+                            float2 y[EPL / 2];
+                            k45_quants<QT, EPL>(bp, l16 * EPL + 128u * h, both(ds), both(ms), y);
+                            st_stream(orow + e + 128u * h, pack16p<OutT>(y));
+                        }
+                    }
+                } else {
+                    generic_row();
+                }
+            } else {
+                generic_row();
+            }
+        } else if (m == 0u) {
+            float2 z[EPL / 2];
+#pragma unroll
+            for (int k = 0; k < EPL / 2; k++) z[k] = make_float2(0.0f, 0.0f);
+            for (unsigned e = l16 * EPL; e < a.dim; e += 16 * EPL) st_stream(orow + e, pack16p<OutT>(z));
+        } else if (m != 3u) {
+            generic_row();
+        }
+        __syncwarp();  // every lane is done with the stage before it is refilled
+        put(mode, st, 3u);
+        return true;
+    };
+
+    // Prologue: the copies of this warp's first NST - 1 pairs are in flight before the first one is decoded, and the
+    // ids of the pair after them are on their way.
+    unsigned id_next = 0;
+    {
+        unsigned r = first;
+#pragma unroll
+        for (unsigned st = 0; st + 1 < NST; st++, r += total_warps) {
+            if (r < n_pairs) issue(r, id_of(r), st);
+        }
+        if (r < n_pairs) id_next = id_of(r);
+    }
+    constexpr bool kUnrollRing = QT == LOKAL_Q8_0 || QT == LOKAL_Q5_0 || QT == LOKAL_Q4_0 || QT == LOKAL_IQ4_NL;
+    auto step = [&](unsigned p, unsigned st) {  // pair p waits in stage st; the copies issued now go to the stage before it
+        const unsigned ahead = p + (NST - 1) * total_warps;
+        if (ahead < n_pairs) {
+            issue(ahead, id_next, (st + NST - 1) % NST);
+            if (ahead + total_warps < n_pairs) id_next = id_of(ahead + total_warps);
+        }
+        return consume(p, st);
+    };
+    unsigned p = first;
+    if constexpr (kUnrollRing) {
+        while (p < n_pairs) {
+#pragma unroll
+            for (unsigned st = 0; st < NST; st++) {
+                if (p >= n_pairs) break;
+                if (!step(p, st)) return;
+                p += total_warps;
+            }
+        }
+    } else {
+        for (unsigned st = 0; p < n_pairs; p += total_warps, st = (st + 1 == NST) ? 0u : st + 1) {
+            if (!step(p, st)) return;
         }
     }
 }
@@ -922,7 +1141,15 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
     // quantised table
     const unsigned warps = 8;
     a.stage_bytes = ((a.row_bytes + 15u) & ~15u) + 32u;
-    const size_t smem = ((warps * kGatherStages * 8 + 127u) & ~127u) + static_cast<size_t>(warps) * kGatherStages * a.stage_bytes;
+    const bool fuse = a.norm_w != nullptr;
+    // 16-bit rows: two rows per warp (gather_quant_pair_kernel), unless the norm is fused into the launch or the doubled
+    // staging area does not fit. LOKAL_CUDA_GATHER_PAIR=0 keeps one row per warp.
+    bool pair = sizeof(OutT) == 2 && !fuse && tune_env("LOKAL_CUDA_GATHER_PAIR", 1) != 0;
+    auto smem_of = [&](bool two) {
+        return ((warps * kGatherStages * 8 + 127u) & ~127u) + static_cast<size_t>(warps) * kGatherStages * (two ? 2u : 1u) * a.stage_bytes;
+    };
+    if (pair && smem_of(true) > 200u * 1024u) pair = false;
+    const size_t smem = smem_of(pair);
     const bool staged = aligned && smem <= 200u * 1024u && (a.row_bytes % 2 == 0);
     if (!staged) {
         for_quant_type(ggml_type, [&](auto qt) {
@@ -932,31 +1159,64 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
         return LOKAL_OK;
     }
     void (*kern)(const GatherArgs) = nullptr;
-    const bool fuse = a.norm_w != nullptr;
-    if (fuse) for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT, true>; });
-    else for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT, false>; });
+    if constexpr (sizeof(OutT) == 2) {
+        if (pair) for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_pair_kernel<decltype(qt)::value, OutT>; });
+    }
+    if (!pair) {
+        if (fuse) for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT, true>; });
+        else for_quant_type(ggml_type, [&](auto qt) { kern = gather_quant_staged_kernel<decltype(qt)::value, OutT, false>; });
+    }
     if (fused) *fused = fuse;
     if (smem > 48u * 1024u) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "embed_gather: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    // Grid: 8 CTAs per SM for 16-bit rows, 24 for f32 rows (or what shared memory allows), each warp walking a
-    // grid-stride list of rows. That is more than are resident at once (a decoder of 48 registers holds five
-    // 256-thread CTAs per SM), and measured better than a grid of exactly the resident CTAs: later CTAs start as earlier
-    // ones finish and even out the tail (Q8_0 to f16 rows: 25.4 against 28.0 us). The f32 rows, which are bound by
-    // the store path rather than by instruction issue, gain from a finer grain still (Q8_0 / Q4_K / Q6_K to f32:
-    // 45.7 / 49.5 / 49.4 us at 8 CTAs per SM, 41.2 / 45.4 / 46.4 us at 24); the 16-bit rows, which are issue-bound,
-    // lose to the per-CTA prologue beyond 8. LOKAL_CUDA_GATHER_CTAS_PER_SM overrides.
-    const unsigned want_per_sm = sizeof(OutT) == 4 ? 24u : 8u;
-    unsigned per_sm = static_cast<unsigned>((220u * 1024u) / (smem + 1024u));
-    if (per_sm > 8) per_sm = want_per_sm;
-    if (per_sm < 1) per_sm = 1;
+    // Grid: 16 CTAs per SM for 16-bit rows, 24 for f32 rows (or what shared memory allows), each warp walking a
+    // grid-stride list of rows or row pairs. That is more than are resident at once (a decoder of 40-48 registers holds
+    // five or six 256-thread CTAs per SM), and measured better than a grid of exactly the resident CTAs: later CTAs
+    // start as earlier ones finish and even out the tail (Q8_0 to f16 rows: 25.4 against 28.0 us). Measured on the
+    // 65,536-id gather, CTAs per SM 8 / 12 / 16 / 24: Q8_0 to f16 26.1 / 25.7 / 24.5 / 24.2 us and Q4_K to f16
+    // 27.0 / 25.6 / 26.0 / 27.0 us with two rows per warp; Q8_0 / Q4_K / Q6_K to f32 45.7 / 49.5 / 49.4 us at 8 and
+    // 41.2 / 45.4 / 46.4 us at 24. LOKAL_CUDA_GATHER_CTAS_PER_SM overrides.
+    const unsigned want_per_sm = sizeof(OutT) == 4 ? 24u : 16u;
+    unsigned per_sm = want_per_sm;  // CTAs of the grid per SM, not resident ones: wide rows simply run in more waves
     const long forced_ctas = tune_env("LOKAL_CUDA_GATHER_CTAS_PER_SM", 0);
     if (forced_ctas >= 1 && forced_ctas <= 64) per_sm = static_cast<unsigned>(forced_ctas);
-    unsigned long long grid = static_cast<unsigned long long>(ctx->sm_count) * per_sm;
-    if (grid > row_warps_blocks) grid = row_warps_blocks;
-    launch_k(kern, static_cast<unsigned>(grid), warps * 32, smem, s, a);
-    LOKAL_CHECK_LAUNCH(ctx, "gather_quant_staged_kernel");
+    // The kernel counts rows and ids in 32 bits. ids are 32-bit values already; `bulk_ids` says which of them may be
+    // fetched as a 16-byte-aligned window without reading past the table (every row but, when the table's size is
+    // not a multiple of 16, the last); and a call of more than 2^30 rows goes out as several launches over
+    // consecutive slices of ids and output (LOKAL_CUDA_GATHER_CHUNK_ROWS lowers the slice for a test). Without ids
+    // (row i of the table to row i of the output) a slice also moves the table pointer, so that ids stay below 2^30.
+    a.max_id = static_cast<unsigned>((a.vocab < (1ull << 32) ? a.vocab : (1ull << 32)) - 1ull);
+    unsigned long long chunk = 1ull << 30;
+    const long forced_chunk = tune_env("LOKAL_CUDA_GATHER_CHUNK_ROWS", 0);
+    if (forced_chunk >= 1 && static_cast<unsigned long long>(forced_chunk) < chunk) chunk = static_cast<unsigned long long>(forced_chunk);
+    const unsigned long long n_all = a.n;
+    for (unsigned long long off = 0; off < n_all; off += chunk) {
+        GatherArgs c = a;
+        c.n = n_all - off < chunk ? n_all - off : chunk;
+        c.n32 = static_cast<unsigned>(c.n);
+        c.out = static_cast<OutT*>(a.out) + off * a.dim;
+        if (a.xn) c.xn = static_cast<OutT*>(a.xn) + off * a.dim;
+        if (a.ids) {
+            c.ids = a.ids + off;
+        } else {  // row i of the table to row i of the output (n <= vocab, checked by the caller)
+            c.table = a.table + off * a.row_bytes;
+            c.vocab = a.vocab - off;
+            c.table_bytes = a.table_bytes - off * a.row_bytes;
+            c.max_id = static_cast<unsigned>((c.vocab < (1ull << 32) ? c.vocab : (1ull << 32)) - 1ull);
+        }
+        // ids whose window [start & ~15, (start + row_bytes + 15) & ~15) ends inside the table: counted down from the last
+        unsigned long long bulk = c.vocab;
+        while (bulk > 0 && ((bulk * c.row_bytes + 15ull) & ~15ull) > c.table_bytes) bulk--;
+        if ((reinterpret_cast<uintptr_t>(c.table) & 15u) != 0) bulk = 0;  // a moved table pointer off the 16-byte grid: plain loads
+        c.bulk_ids = bulk > 0xffffffffull ? 0xffffffffu : static_cast<unsigned>(bulk);
+        const unsigned long long blocks = ((pair ? (c.n + 1) / 2 : c.n) + warps - 1) / warps;  // a warp per row, or per pair of rows
+        unsigned long long grid = static_cast<unsigned long long>(ctx->sm_count) * per_sm;
+        if (grid > blocks) grid = blocks;
+        launch_k(kern, static_cast<unsigned>(grid), warps * 32, smem, s, c);
+        LOKAL_CHECK_LAUNCH(ctx, "gather_quant_staged_kernel");
+    }
     return LOKAL_OK;
 }
 
@@ -994,6 +1254,7 @@ int launch_gather_norm(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, i
     const size_t rb = lokal_cuda_row_bytes(ggml_type, dim);
     if (rb > 0xffffffffu) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: row of %zu bytes is too large", rb);
     if (n == 0) return LOKAL_OK;
+    if (!ids && n > vocab) return ctx->fail(LOKAL_ERR_BAD_ARG, "embed_gather: %zu rows asked of a table of %zu without an id list", n, vocab);
     GatherArgs a{};
     a.table = static_cast<const unsigned char*>(table);
     a.ids = ids;

@@ -318,3 +318,61 @@ def test_gather_rmsnorm_on_float_tables_and_refusals(ctx, dev, oracle):
         with pytest.raises(L.LokalCudaError) as e:
             ctx.embed_gather_rmsnorm(args["table"], args["ids"], args["x"], args["xn"], args["w"], ggml_type=F32, vocab=vocab, dim=dim, n=n, eps=1e-5)
         assert e.value.status == L.capi.ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("ty,dim", [(Q8_0, 896), (Q4_K, 1024)])
+@pytest.mark.parametrize("chunk", [1000, 1001])
+def test_a_call_split_into_several_launches(ctx, dev, oracle, ty, dim, chunk, monkeypatch):
+    """The staged kernel counts rows in 32 bits, so a call of more than 2^30 rows goes out as several launches over
+    consecutive slices. The test lowers the slice to 1000 / 1001 rows (1001 moves the table pointer of the id-less form
+    off the 16-byte grid, which sends those slices through the plain-load staging) and compares with one launch."""
+    vocab = 2300
+    table = (synth.q8_0_table if ty == Q8_0 else synth.q4_k_table)(vocab, dim, seed=11)
+    ids = np.concatenate([synth.token_ids_zipf(vocab, 3300, seed=5), [vocab - 1, 0, vocab - 1]]).astype(np.uint32)
+    want = oracle.embed_gather(table, ty, vocab, dim, ids)
+    whole = oracle.embed_gather(table, ty, vocab, dim, np.arange(vocab, dtype=np.uint32))
+    monkeypatch.setenv("LOKAL_CUDA_GATHER_CHUNK_ROWS", str(chunk))
+    for out_dtype in (F32, F16):
+        synth.assert_bits_equal(gather(ctx, dev, table, ty, vocab, dim, ids, out_dtype), synth.round_to(want, out_dtype), "sliced gather")
+        synth.assert_bits_equal(dequant(ctx, dev, table, ty, vocab, dim, out_dtype), synth.round_to(whole, out_dtype), "sliced dequant of the whole table")
+
+
+@pytest.mark.parametrize("ty,dim", [(Q8_0, 896), (Q8_0, 32), (Q4_K, 1024), (Q4_K, 512), (Q4_K, 1280), (13, 768), (14, 256), (20, 64), (21, 512), (19, 256)])
+@pytest.mark.parametrize("out_dtype", [F16, BF16])
+def test_two_rows_per_warp_against_one(ctx, dev, oracle, ty, dim, out_dtype, monkeypatch):
+    """16-bit rows are decoded two to a warp. Odd and tiny row counts, the table's last row (whose window may need the
+    plain-load staging) in either half, ids out of range in either half: bit for bit the oracle's rows, and the same
+    bytes as the one-row-per-warp kernel."""
+    import lokal_b200 as L
+    if ty in L.capi.GRID_TYPES:
+        from test_oracle_iq_grids import GRIDS
+        ctx.set_iq_grids(GRIDS)
+        oracle.set_iq_grids(GRIDS)
+    vocab = 301
+    table = synth.quant_table(ty, vocab, dim, seed=ty + dim)
+    for n in (1, 2, 3, 777):
+        ids = synth.token_ids_uniform(vocab, n, seed=n).astype(np.uint32)
+        ids[-1] = vocab - 1
+        if n > 2:
+            ids[0] = vocab - 1
+            ids[n // 2] = vocab - 1
+        want = synth.round_to(oracle.embed_gather(table, ty, vocab, dim, ids), out_dtype)
+        got = gather(ctx, dev, table, ty, vocab, dim, ids, out_dtype)
+        synth.assert_bits_equal(got, want, f"two rows per warp, n={n}")
+        monkeypatch.setenv("LOKAL_CUDA_GATHER_PAIR", "0")
+        synth.assert_bits_equal(gather(ctx, dev, table, ty, vocab, dim, ids, out_dtype), got, f"one row per warp, n={n}")
+        monkeypatch.delenv("LOKAL_CUDA_GATHER_PAIR")
+    # out-of-range ids in the low half, the high half and both halves of a pair
+    ids = synth.token_ids_uniform(vocab, 41, seed=9).astype(np.uint32)
+    bad = [4, 9, 20, 21, 40]
+    ids[bad] = [vocab, 4000000000, vocab + 5, vocab, vocab]
+    good = [i for i in range(41) if i not in bad]
+    dt, di = dev.put(table), dev.put(ids)
+    out = dev.empty((42, dim), out_dtype, fill=4.0)
+    ctx.embed_gather(dt, di, out, ggml_type=ty, vocab=vocab, dim=dim, n=41, out_dtype=out_dtype)
+    with pytest.raises(L.LokalCudaError) as e:
+        ctx.stream_sync()
+    assert e.value.status == L.capi.ERR_ID_RANGE
+    got = dev.get(out)
+    synth.assert_bits_equal(got[good], synth.round_to(oracle.embed_gather(table, ty, vocab, dim, ids[good]), out_dtype), "valid rows")
+    assert (got[bad] == 0).all() and (got[41] == 4.0).all()

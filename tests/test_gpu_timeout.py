@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 import synth
-from synth import F32, Q8_0
+from synth import F16, F32, Q8_0
 
 pytestmark = pytest.mark.gpu
 
@@ -26,17 +26,16 @@ def feed(monkeypatch):
     monkeypatch.delenv("LOKAL_CUDA_WAIT_LIMIT")
 
 
-@pytest.mark.parametrize("kernel", ["batch", "warp"])
-def test_gather_wait_runs_out_and_reports(ctx, dev, oracle, monkeypatch, kernel):
+@pytest.mark.parametrize("out_dtype", [F32, F16])  # one row per warp (f32 rows) and two rows per warp (16-bit rows)
+def test_gather_wait_runs_out_and_reports(ctx, dev, oracle, monkeypatch, out_dtype):
     import lokal_b200 as L
-    vocab, dim, n = 64, 256, 40
+    vocab, dim, n = 64, 256, 41
     table = synth.q8_0_table(vocab, dim, 3)
     ids = synth.token_ids_uniform(vocab, n, 4)
     dt, di = dev.put(table), dev.put(ids.view(np.int32))
-    out = dev.empty((n, dim), F32, fill=7.0)
-    monkeypatch.setenv("LOKAL_CUDA_GATHER_KERNEL", kernel)
+    out = dev.empty((n, dim), out_dtype, fill=7.0)
     starve(monkeypatch)
-    ctx.embed_gather(dt, di, out, ggml_type=Q8_0, vocab=vocab, dim=dim, n=n, out_dtype=F32)
+    ctx.embed_gather(dt, di, out, ggml_type=Q8_0, vocab=vocab, dim=dim, n=n, out_dtype=out_dtype)
     with pytest.raises(L.LokalCudaError) as e:
         ctx.stream_sync()
     assert e.value.status == L.capi.ERR_TIMEOUT
@@ -44,9 +43,10 @@ def test_gather_wait_runs_out_and_reports(ctx, dev, oracle, monkeypatch, kernel)
     # the error word was cleared with the report; the same call without the starved barrier is bit-exact
     feed(monkeypatch)
     ctx.stream_sync()
-    ctx.embed_gather(dt, di, out, ggml_type=Q8_0, vocab=vocab, dim=dim, n=n, out_dtype=F32)
+    ctx.embed_gather(dt, di, out, ggml_type=Q8_0, vocab=vocab, dim=dim, n=n, out_dtype=out_dtype)
     ctx.stream_sync()
-    synth.assert_bits_equal(dev.get(out), oracle.embed_gather(table, Q8_0, vocab, dim, ids), "gather after a timed-out launch")
+    want = synth.round_to(oracle.embed_gather(table, Q8_0, vocab, dim, ids), out_dtype)
+    synth.assert_bits_equal(dev.get(out), want, "gather after a timed-out launch")
 
 
 def test_staged_rope_wait_runs_out_and_reports(ctx, dev, oracle, monkeypatch):
