@@ -45,6 +45,7 @@ struct GatherArgs {
     unsigned n32;        // rows of this launch
     unsigned max_id;     // min(vocab, 2^32) - 1: an id above it is out of range
     unsigned bulk_ids;   // ids below it have their 16-byte-aligned window inside the table (all but, at most, the last row)
+    unsigned out32;      // every output row starts on a 32-byte boundary: a lane may store 32 bytes at once
     unsigned dim;
     unsigned row_bytes;
     unsigned stage_bytes;  // per warp per stage, multiple of 16
@@ -474,6 +475,13 @@ __device__ __forceinline__ uint4 decode_small_block_h8(const unsigned char* b, u
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
+// 32 bytes to a 32-byte-aligned address in one store: a lane fills a whole sector.
+__device__ __forceinline__ void st_stream32(void* p, const uint4& a, const uint4& b) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x),
+                 "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 // Codebook types in the staged kernel. EPL consecutive elements are half a run (EPL = 4) or one run (EPL = 8): one
 // scale, one byte of signs (or one delta), and one 8-byte codebook entry (IQ1 / IQ2) or two 4-byte entries (IQ3),
 // fetched once. Same values and rounding order as dequant_grid_elem; a sign is applied by flipping the sign bit,
@@ -705,7 +713,8 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
         const unsigned m = sel(mode, st);
         if (m == 1) {
             const unsigned ph = sel(parity, st);
-            if (!mbar_wait_bounded(bar(st), ph, a.wait_limit)) {
+            // the vote makes the outcome the same for every lane: a wait that ran out for one counts as run out for all
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(st), ph, a.wait_limit))) {
                 if (lane == 0) atomicOr(a.err_word, kErrTimeout);
                 // give the copies still in flight one more bounded chance to land before leaving
 #pragma unroll
@@ -773,6 +782,25 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
                         }
                         done = true;
                     }
+                }
+                if constexpr (kIsGridType<QT> && sizeof(OutT) == 4 && !FUSE) {
+                    // f32 rows of the codebook types: a lane takes a whole run of eight values (one scale, one byte of
+                    // signs or one delta, one codebook entry) instead of half a run, which halves the index and scale
+                    // work per value, and stores its 32 bytes as one sector where the rows are 32-byte aligned.
+                    // a.dim is a multiple of 256 for these types, so a step of 256 values never overruns the row.
+                    for (unsigned e = lane * 8u; e < a.dim; e += 256u) {
+                        float2 y[4];
+                        decode_grid_block<QT, 8>(row, e, a.grid, y);
+                        const uint4 lo = make_uint4(__float_as_uint(y[0].x), __float_as_uint(y[0].y), __float_as_uint(y[1].x), __float_as_uint(y[1].y));
+                        const uint4 hi = make_uint4(__float_as_uint(y[2].x), __float_as_uint(y[2].y), __float_as_uint(y[3].x), __float_as_uint(y[3].y));
+                        if (a.out32) {
+                            st_stream32(orow + e, lo, hi);
+                        } else {
+                            st_stream(orow + e, lo);
+                            st_stream(orow + e + 4, hi);
+                        }
+                    }
+                    done = true;
                 }
                 if (!done) {
                     for (unsigned e = lane * EPL; e < a.dim; e += 32 * EPL) {
@@ -939,7 +967,8 @@ __global__ void __launch_bounds__(256) gather_quant_pair_kernel(const GatherArgs
     // Decodes the rows waiting in stage st into output rows 2p and 2p + 1; false when the bounded wait gave up.
     auto consume = [&](unsigned p, unsigned st) -> bool {
         const unsigned ph = sel(parity, st);
-        if (!mbar_wait_bounded(bar(st), ph, a.wait_limit)) {
+        // the vote makes the outcome the same for every lane: a wait that ran out for one counts as run out for all
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(st), ph, a.wait_limit))) {
             if (lane == 0) atomicOr(a.err_word, kErrTimeout);
             // give the copies still in flight one more bounded chance to land before leaving
 #pragma unroll
@@ -1089,30 +1118,45 @@ __global__ void __launch_bounds__(256) gather_float_kernel(const GatherArgs a, i
     if (!valid && lane == 0) atomicOr(a.err_word, kErrIdRange);
     const SrcT* row = reinterpret_cast<const SrcT*>(a.table) + (valid ? id : 0) * a.dim;
     if (vec_ok) {
-        for (unsigned e = lane * N; e < a.dim; e += 32 * N) {
-            float f[N];
-            if (valid) unpack16<SrcT>(ld_keep(row + e), f);
-            else {
+        // Four source vectors per lane are loaded before the first of them is stored, so a row of up to 4 x 512 bytes
+        // costs its warp one memory round trip instead of one per vector.
+        constexpr unsigned kAhead = 4;
+        for (unsigned e0 = lane * N; e0 < a.dim; e0 += kAhead * 32 * N) {
+            uint4 v[kAhead];
 #pragma unroll
-                for (int k = 0; k < N; k++) f[k] = 0.0f;
+            for (unsigned j = 0; j < kAhead; j++) {
+                const unsigned e = e0 + j * 32 * N;
+                v[j] = (valid && e < a.dim) ? ld_keep(row + e) : make_uint4(0, 0, 0, 0);  // all-zero bits are 0.0 in every source type
             }
-            constexpr int ON = VecOf<OutT>::N;
-            if (ON == N) {
-                float g[ON];
 #pragma unroll
-                for (int k = 0; k < ON; k++) g[k] = f[k % N];
-                st_stream(orow + e, pack16<OutT>(g));
-            } else if (ON < N) {  // 16-bit source, f32 out: two 16-byte stores
-#pragma unroll
-                for (int h = 0; h < N / ON; h++) {
+            for (unsigned j = 0; j < kAhead; j++) {
+                const unsigned e = e0 + j * 32 * N;
+                if (e >= a.dim) break;
+                float f[N];
+                unpack16<SrcT>(v[j], f);
+                constexpr int ON = VecOf<OutT>::N;
+                if (ON == N) {
                     float g[ON];
 #pragma unroll
-                    for (int k = 0; k < ON; k++) g[k] = f[(h * ON + k) % N];
-                    st_stream(orow + e + h * ON, pack16<OutT>(g));
-                }
-            } else {  // f32 source, 16-bit out: 4 elements = 8 bytes
+                    for (int k = 0; k < ON; k++) g[k] = f[k % N];
+                    st_stream(orow + e, pack16<OutT>(g));
+                } else if (ON < N) {  // 16-bit source, f32 out: 32 bytes per lane, one store where the rows are 32-byte aligned
+                    float g0[ON], g1[ON];
 #pragma unroll
-                for (int k = 0; k < N; k++) orow[e + k] = from_f32<OutT>(f[k]);
+                    for (int k = 0; k < ON; k++) {
+                        g0[k] = f[k % N];
+                        g1[k] = f[(ON + k) % N];
+                    }
+                    if (a.out32) {
+                        st_stream32(orow + e, pack16<OutT>(g0), pack16<OutT>(g1));
+                    } else {
+                        st_stream(orow + e, pack16<OutT>(g0));
+                        st_stream(orow + e + ON, pack16<OutT>(g1));
+                    }
+                } else {  // f32 source, 16-bit out: 4 elements = 8 bytes
+#pragma unroll
+                    for (int k = 0; k < N; k++) orow[e + k] = from_f32<OutT>(f[k]);
+                }
             }
         }
     } else {
@@ -1132,6 +1176,7 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
         const int vec_ok = aligned && (static_cast<size_t>(a.dim) * ses) % 16 == 0 &&
                            (static_cast<size_t>(a.dim) * sizeof(OutT)) % 16 == 0;
         const unsigned grid = static_cast<unsigned>(row_warps_blocks);
+        a.out32 = (reinterpret_cast<uintptr_t>(a.out) % 32 == 0 && (static_cast<size_t>(a.dim) * sizeof(OutT)) % 32 == 0) ? 1u : 0u;
         if (ggml_type == LOKAL_F32) launch_k(gather_float_kernel<float, OutT>, grid, 256, 0, s, a, vec_ok);
         else if (ggml_type == LOKAL_F16) launch_k(gather_float_kernel<__half, OutT>, grid, 256, 0, s, a, vec_ok);
         else launch_k(gather_float_kernel<__nv_bfloat16, OutT>, grid, 256, 0, s, a, vec_ok);
@@ -1197,6 +1242,7 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
         c.n = n_all - off < chunk ? n_all - off : chunk;
         c.n32 = static_cast<unsigned>(c.n);
         c.out = static_cast<OutT*>(a.out) + off * a.dim;
+        c.out32 = (reinterpret_cast<uintptr_t>(c.out) % 32 == 0 && (static_cast<size_t>(a.dim) * sizeof(OutT)) % 32 == 0) ? 1u : 0u;
         if (a.xn) c.xn = static_cast<OutT*>(a.xn) + off * a.dim;
         if (a.ids) {
             c.ids = a.ids + off;

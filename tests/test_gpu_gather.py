@@ -132,6 +132,16 @@ def test_float_tables(ctx, dev, oracle, ty, out_dtype, dim):
     ctx.embed_gather(dt, dev.put(ids), out, ggml_type=ty, vocab=vocab, dim=dim, n=500, out_dtype=out_dtype)
     ctx.stream_sync()
     synth.assert_bits_equal(dev.get(out), synth.round_to(want, out_dtype), "float table gather")
+    if dim % 8 == 0:  # rows that start 16 bytes past a 32-byte boundary: the 16-byte stores instead of the 32-byte ones
+        es = 4 if out_dtype == F32 else 2
+        flat = dev.empty((500 * dim + 2 * (16 // es),), out_dtype, fill=4.0)
+        shifted = flat[16 // es:16 // es + 500 * dim]
+        assert shifted.data_ptr() % 32 == 16
+        ctx.embed_gather(dt, dev.put(ids), shifted, ggml_type=ty, vocab=vocab, dim=dim, n=500, out_dtype=out_dtype)
+        ctx.stream_sync()
+        got = dev.get(flat)
+        synth.assert_bits_equal(got[16 // es:-(16 // es)].reshape(500, dim), synth.round_to(want, out_dtype), "float table gather, 16-byte-aligned rows")
+        assert (got[:16 // es] == 4.0).all() and (got[-(16 // es):] == 4.0).all()
 
 
 def test_out_of_range_id_is_reported_and_zero_filled(ctx, dev, oracle):

@@ -82,4 +82,13 @@ def test_random_tables_both_kernels(grid_ctx, dev, oracle, ty):
     grid_ctx.embed_gather(shifted, di, out, ggml_type=ty, vocab=vocab, dim=dim, n=len(ids))
     grid_ctx.stream_sync()
     synth.assert_bits_equal(dev.get(out), want, f"{gguf_np.GRID_NAMES[ty]} per-element gather")
+    # f32 rows that start 16 bytes past a 32-byte boundary: two 16-byte stores per lane instead of one of 32 bytes
+    flat = dev.empty((len(ids) * dim + 8,), F32, fill=4.0)
+    out16 = flat[4:4 + len(ids) * dim]
+    assert out16.data_ptr() % 32 == 16
+    grid_ctx.embed_gather(dev.put(table), di, out16, ggml_type=ty, vocab=vocab, dim=dim, n=len(ids))
+    grid_ctx.stream_sync()
+    got = dev.get(flat)
+    synth.assert_bits_equal(got[4:-4].reshape(len(ids), dim), want, f"{gguf_np.GRID_NAMES[ty]} staged gather, 16-byte-aligned rows")
+    assert (got[:4] == 4.0).all() and (got[-4:] == 4.0).all()
     assert bb * (dim // 256) == oracle.row_bytes(ty, dim)
