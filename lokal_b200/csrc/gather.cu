@@ -1216,7 +1216,7 @@ int launch_out(lokal_cuda_ctx* ctx, cudaStream_t s, GatherArgs a, int ggml_type,
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return ctx->fail(LOKAL_ERR_CUDA, "embed_gather: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    // Grid: 16 CTAs per SM for 16-bit rows, 24 for f32 rows (or what shared memory allows), each warp walking a
+    // Grid: 16 CTAs per SM for 16-bit rows, 24 for f32 rows, each warp walking a
     // grid-stride list of rows or row pairs. That is more than are resident at once (a decoder of 40-48 registers holds
     // five or six 256-thread CTAs per SM), and measured better than a grid of exactly the resident CTAs: later CTAs
     // start as earlier ones finish and even out the tail (Q8_0 to f16 rows: 25.4 against 28.0 us). Measured on the
