@@ -21,7 +21,10 @@
 // a multiple of 34 bytes, so a row start is only 2-byte aligned; the copy
 // fetches the enclosing 16-byte-aligned window and the decode indexes from the
 // remainder. Each lane then produces 16 bytes of output per step (4 f32 or
-// 8 f16/bf16), so every store instruction of a warp writes one 512-byte run.
+// 8 f16/bf16), so every store instruction of a warp writes one 512-byte run
+// (f32 rows of the codebook types: a whole run of 8 values, 32 bytes, per lane).
+// 16-bit output rows are decoded two to a warp (gather_quant_pair_kernel), which
+// shares the per-row bookkeeping between the two halves of the warp.
 // HBM traffic per token: row_bytes for the first touch of a row (hot rows hit
 // L2) plus dim*sizeof(out) written.
 //
@@ -713,9 +716,11 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
         const unsigned m = sel(mode, st);
         if (m == 1) {
             const unsigned ph = sel(parity, st);
-            // the vote makes the outcome the same for every lane: a wait that ran out for one counts as run out for all
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(st), ph, a.wait_limit))) {
-                if (lane == 0) atomicOr(a.err_word, kErrTimeout);
+            // Every lane polls for itself, and every lane whose polls run out reports it (the polls of a warp end
+            // together unless completion falls on the very last one; the lanes that leave are exited threads to the
+            // warp-wide operations of those that go on, and the error word says the launch's output is not to be used).
+            if (!mbar_wait_bounded(bar(st), ph, a.wait_limit)) {
+                atomicOr(a.err_word, kErrTimeout);
                 // give the copies still in flight one more bounded chance to land before leaving
 #pragma unroll
                 for (unsigned t = 0; t < NST; t++) {
@@ -967,13 +972,13 @@ __global__ void __launch_bounds__(256) gather_quant_pair_kernel(const GatherArgs
     // Decodes the rows waiting in stage st into output rows 2p and 2p + 1; false when the bounded wait gave up.
     auto consume = [&](unsigned p, unsigned st) -> bool {
         const unsigned ph = sel(parity, st);
-        // the vote makes the outcome the same for every lane: a wait that ran out for one counts as run out for all
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(st), ph, a.wait_limit))) {
-            if (lane == 0) atomicOr(a.err_word, kErrTimeout);
+        // every lane polls for itself, and every lane whose polls run out reports it (see the kernel above)
+        if (!mbar_wait_bounded(bar(st), ph, a.wait_limit)) {
+            atomicOr(a.err_word, kErrTimeout);
             // give the copies still in flight one more bounded chance to land before leaving
 #pragma unroll
             for (unsigned t = 0; t < NST; t++) {
-                if (t != st && __any_sync(0xffffffffu, mode[t] == 1u)) mbar_wait_bounded(bar(t), parity[t], a.wait_limit);
+                if (t != st && mode[t] == 1u) mbar_wait_bounded(bar(t), parity[t], a.wait_limit);  // the half whose copy it is waits
             }
             return false;
         }

@@ -439,10 +439,11 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
     if (NORM) R::stage_weights(a, w_s);
     __syncthreads();  // norm weights staged; every row's mbarrier initialised before anyone waits on it
     if (!valid) return;
-    // The vote makes the outcome the same for every lane of the warp (the shuffles below need all of them): a wait
-    // that ran out for one lane counts as run out for all.
-    if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar, 0, a.wait_limit))) {
-        if (lane == 0) atomicOr(a.err_word, kErrTimeout);
+    // Every lane polls for itself, and every lane whose polls run out reports it: the polls of a warp end together
+    // unless completion falls on the very last one, and then the lanes that leave are exited threads to the shuffles
+    // of those that go on, while the error word says the launch's output is not to be used.
+    if (!mbar_wait_bounded(bar, 0, a.wait_limit)) {
+        atomicOr(a.err_word, kErrTimeout);
         mbar_wait_bounded(bar, 0, a.wait_limit);  // one more bounded chance for the copies in flight to land before leaving
         return;
     }
