@@ -347,7 +347,8 @@ def test_a_call_split_into_several_launches(ctx, dev, oracle, ty, dim, chunk, mo
         synth.assert_bits_equal(dequant(ctx, dev, table, ty, vocab, dim, out_dtype), synth.round_to(whole, out_dtype), "sliced dequant of the whole table")
 
 
-@pytest.mark.parametrize("ty,dim", [(Q8_0, 896), (Q8_0, 32), (Q4_K, 1024), (Q4_K, 512), (Q4_K, 1280), (13, 768), (14, 256), (20, 64), (21, 512), (19, 256)])
+@pytest.mark.parametrize("ty,dim", [(Q8_0, 896), (Q8_0, 32), (Q4_K, 1024), (Q4_K, 512), (Q4_K, 1280), (13, 768), (14, 256), (20, 64), (21, 512), (19, 256),
+                                    (2, 64), (6, 96), (10, 256), (11, 512), (16, 256), (17, 256), (18, 512), (22, 256), (23, 512), (29, 256)])
 @pytest.mark.parametrize("out_dtype", [F16, BF16])
 def test_two_rows_per_warp_against_one(ctx, dev, oracle, ty, dim, out_dtype, monkeypatch):
     """16-bit rows are decoded two to a warp. Odd and tiny row counts, the table's last row (whose window may need the
