@@ -424,10 +424,12 @@ __global__ void __launch_bounds__(256, 4) qk_rope_staged_kernel(const QkArgs a) 
         for (unsigned off = lane * 128u; off < a.q_row_bytes; off += 32u * 128u) prefetch_l2(qrow + off);
         for (unsigned off = lane * 128u; off < a.k_row_bytes; off += 32u * 128u) prefetch_l2(krow + off);
     }
-    pdl_wait();
-    if (lane == 0 && part == 0) {
+    if (lane == 0 && part == 0) {  // the barrier is set up while the kernel before this one drains
         mbar_init(bar, 1);
         mbar_init_fence();
+    }
+    pdl_wait();
+    if (lane == 0 && part == 0) {
         if (valid) {
             mbar_expect_tx(bar, a.q_row_bytes + a.k_row_bytes + a.extra_tx);
             if (a.q_row_bytes) bulk_copy_g2s(smem_addr(stage), reinterpret_cast<const T*>(a.q) + row * a.q_stride, a.q_row_bytes, bar);
