@@ -138,6 +138,32 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
     return v;
 }
 __device__ __forceinline__ void st_stream(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+// The same accesses with an L2 eviction priority (createpolicy): `keep` for the few megabytes a chain of launches
+// reads and rewrites again and again (the residual stream), so that they survive what streams through L2 between
+// two of those launches.
+__device__ __forceinline__ unsigned long long l2_policy_keep() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint4 ld_stream_l2(const void* p, unsigned long long pol) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.b32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_keep_l2(const void* p, unsigned long long pol) {  // read-only data, cached in L1 too
+    uint4 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.b32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ void st_stream_l2(void* p, uint4 v, unsigned long long pol) {
+    asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(pol)
+                 : "memory");
+}
 __device__ __forceinline__ uint4 ld_keep(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
 template <typename T>

@@ -74,6 +74,7 @@ struct QkArgs {
     const void* q_norm_w;
     const void* k_norm_w;
     const float* cos_sin;
+    int table_keep;  // keep the cos/sin table in L2 between the launches of a step (see RopeRow::init)
     const uint32_t* k_out_rows;
     unsigned long long rows;
     unsigned n_q, n_kv, head_dim, rot_dim;
@@ -148,14 +149,18 @@ struct RopeRow {
         hi_off = hi_of(sub);
         rot_lane = FULL || sub < RL;
         if (rot_lane) {
+            // The table is read again by the rope launch of every layer of a step: its loads carry the high L2
+            // eviction priority (a.table_keep: the table is small against L2), so that the q and k rows streaming
+            // through between two launches do not push it out to HBM.
             const float* tr = a.cos_sin + row * ROT + sub * N;
+            const unsigned long long pol = a.table_keep ? l2_policy_keep() : 0ull;
 #pragma unroll
             for (int j = 0; j < N / 4; j++) {
                 float2 t[2];
-                unpack16p<float>(ld_keep(tr + 4 * j), t);
+                unpack16p<float>(a.table_keep ? ld_keep_l2(tr + 4 * j, pol) : ld_keep(tr + 4 * j), t);
                 cs[2 * j] = t[0];
                 cs[2 * j + 1] = t[1];
-                unpack16p<float>(ld_keep(tr + ROT / 2 + 4 * j), t);
+                unpack16p<float>(a.table_keep ? ld_keep_l2(tr + ROT / 2 + 4 * j, pol) : ld_keep(tr + ROT / 2 + 4 * j), t);
                 sn[2 * j] = t[0];
                 sn[2 * j + 1] = t[1];
             }
@@ -738,6 +743,7 @@ int launch_qk_rope(lokal_cuda_ctx* ctx, cudaStream_t s, const lokal_qk_rope_para
     a.q_norm_w = p.q_norm_w;
     a.k_norm_w = p.k_norm_w;
     a.cos_sin = p.cos_sin;
+    a.table_keep = (static_cast<size_t>(p.rows) * p.rot_dim * 4 <= (32u << 20) && tune_env("LOKAL_CUDA_ROPE_TABLE_KEEP", 1) != 0) ? 1 : 0;
     a.k_out_rows = p.k_out_rows;
     a.rows = p.rows;
     a.head_dim = p.head_dim;
