@@ -160,7 +160,14 @@ LOKAL_API int lokal_cuda_rmsnorm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, const
 /* Residual add (src/model.rs:235-237, 253-255; GPU twin add_inplace,
  * src/gpu/kernels.metal:3591) fused with the RMSNorm that follows it:
  *   x[r] += delta[r]   (in place, f32 add, stored in `dtype`)
- *   xn[r] = rmsnorm(x[r] + delta[r], w, eps)   (from the unrounded f32 sum) */
+ *   xn[r] = rmsnorm(x[r] + delta[r], w, eps)   (from the unrounded f32 sum)
+ * x_inout is the residual stream, which every add-norm of a step reads and
+ * rewrites: when it is at most 32 MB its loads and stores are given the high
+ * L2 eviction priority, so that it stays on chip from one call to the next
+ * (half the HBM traffic of the call). The lines keep that priority until
+ * newer ones of the same priority displace them; an engine that would rather
+ * have all of L2 for its other kernels sets LOKAL_CUDA_NORM_L2_KEEP=0 in the
+ * environment (read per call). Results do not depend on it. */
 LOKAL_API int lokal_cuda_add_rmsnorm(lokal_cuda_ctx* ctx, lokal_cuda_stream s, void* x_inout, const void* delta,
                                      const void* w, void* xn, void* xn_h, size_t rows, size_t dim, float eps,
                                      int dtype, int w_dtype, int h_dtype);
