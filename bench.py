@@ -346,6 +346,20 @@ class StepBench:
         per_token_layer = 2 * 4 * cfg.hidden * es + (2 * (cfg.q_dim + cfg.kv_dim) * es + cfg.head_dim * 4) + 3 * cfg.inter * es
         return cfg.layers * per_token_layer * T + gather + 2 * cfg.hidden * es * T + cfg.head_dim * 4 * T, gather
 
+    def l2_resident_bytes(self):
+        """Algorithmic bytes of a step that do not cross HBM: the residual stream x, which every add-norm reads and
+        rewrites with the high L2 eviction priority (all but its first read and last write), and the cos/sin table,
+        read again by every layer's rope launch (all but the first read). Both priorities apply up to 32 MB, as in the
+        library; ncu's per-launch DRAM bytes (profiles/c5_dram_traffic_per_kernel.md) are the measured counterpart."""
+        cfg, T, es = self.cfg, self.T, self.es
+        x_bytes, table_bytes = T * cfg.hidden * es, T * cfg.head_dim * 4
+        keep = 0
+        if x_bytes <= (32 << 20):
+            keep += (2 * cfg.layers * 2 - 2) * x_bytes
+        if table_bytes <= (32 << 20):
+            keep += (cfg.layers - 1) * table_bytes
+        return keep
+
     def time_blocks(self, schedule, steps, blocks, warmup, barrier, sampler=None):
         """`blocks` timed blocks of `steps` graph launches, each between a barrier and a stream sync, timed with CUDA
         events on the launching stream. Returns the per-block milliseconds of this rank."""
@@ -401,7 +415,7 @@ def quick_configs(L, ctx, dev, stream, sampler, peak):
         ms = float(np.median(sb.time_blocks(L.capi.PASS_SCHEDULE_AUTO, 20, 5, 3, nobar, sampler))) / 20
         nbytes, _ = sb.step_bytes()
         out[key] = {"workload": cfg.name, "rows": cfg.rows, "ms_per_step": ms, "tokens_per_s": cfg.rows / (ms * 1e-3),
-                    "launches_per_step": int(sb.launches_per_step), "step_hbm_gbs": nbytes / (ms * 1e-3) / 1e9,
+                    "launches_per_step": int(sb.launches_per_step), "step_algorithmic_gbs": nbytes / (ms * 1e-3) / 1e9,
                     "step_frac": nbytes / (ms * 1e-3) / 1e9 / peak}
         sb.close()
         del sb
@@ -442,6 +456,7 @@ def ours(args, cfg, rank, world, local_rank):
         sampler.pause()
         sampler.start()
     step_bytes, gather_bytes = sb.step_bytes()
+    l2_bytes = sb.l2_resident_bytes()
 
     # ---- per-kernel timing on this GPU (rank 0 reports): L launches over distinct per-layer buffers ----
     rn, q, k, da, dm, g, u, ids, pos = sb.rn, sb.q, sb.k, sb.da, sb.dm, sb.g, sb.u, sb.ids, sb.pos
@@ -651,7 +666,8 @@ def ours(args, cfg, rank, world, local_rank):
             "blocks_ms_per_step": [b / args.steps for b in blocks_ms], "value_is": "median block of K steps, maximum over ranks per block",
             "schedule": args.schedule, "by_schedule": by_schedule,
             "host_cpus_bound_to_gpu": bound_cpus,
-            "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9, "step_algorithmic_bytes": int(step_bytes),
+            "step_algorithmic_bytes": int(step_bytes), "step_algorithmic_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+            "step_l2_resident_bytes": int(l2_bytes), "step_hbm_gbs": (step_bytes - l2_bytes) / (ms_step * 1e-3) / 1e9,
             "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": int(launches_per_step),
             "roofline": roof, "clocks": clocks, "e2e": e2e,
         }
