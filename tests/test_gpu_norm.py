@@ -175,3 +175,26 @@ def test_large_batches(ctx, dev, oracle, name, fused):
     else:
         synth.check_half(n1, ref_xn, f"{name} rmsnorm", cfg.dtype)
     synth.assert_bits_equal(x1, synth.round_to(ref_x, cfg.dtype), "x + delta")
+
+
+@pytest.mark.parametrize("dtype", [F32, F16, BF16])
+def test_l2_priority_of_the_residual_stream_changes_no_bit(ctx, dev, dtype, monkeypatch):
+    """add_rmsnorm loads and stores x with the high L2 eviction priority (a residual stream of up to 32 MB);
+    LOKAL_CUDA_NORM_L2_KEEP=0 turns the priority off. A cache hint may not change a result: both forms, a chain of
+    three calls over one x each, bit for bit."""
+    rows, dim = 4099, 1024
+    rng = np.random.default_rng(5)
+    x = synth.round_to(rng.standard_normal((rows, dim), dtype=np.float32), dtype)
+    deltas = [synth.round_to(0.1 * rng.standard_normal((rows, dim), dtype=np.float32), dtype) for _ in range(3)]
+    w = synth.round_to(1 + 0.1 * rng.standard_normal(dim, dtype=np.float32), dtype)
+    outs = []
+    for keep in ("1", "0"):
+        monkeypatch.setenv("LOKAL_CUDA_NORM_L2_KEEP", keep)
+        dx, dw = dev.put(x, dtype), dev.put(w, dtype)
+        dxn = dev.empty((3, rows, dim), dtype, fill=0.0)
+        for l in range(3):
+            ctx.add_rmsnorm(dx, dev.put(deltas[l], dtype), dw, dxn[l], rows=rows, dim=dim, eps=1e-6, dtype=dtype, w_dtype=dtype)
+        ctx.stream_sync()
+        outs.append((dev.get(dx), dev.get(dxn)))
+    synth.assert_bits_equal(outs[0][0], outs[1][0], "x after three add-norms, with and without the L2 priority")
+    synth.assert_bits_equal(outs[0][1], outs[1][1], "xn of three add-norms, with and without the L2 priority")

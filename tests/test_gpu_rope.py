@@ -334,3 +334,19 @@ def test_rows_that_fill_the_staging_budget(ctx, dev, oracle, dtype, nq, nkv, hd,
     else:
         synth.check_half(q, rq, "q", dtype, atol=ROPE_HALF_ATOL)
         synth.check_half(k, rk, "k", dtype, atol=ROPE_HALF_ATOL)
+
+
+@pytest.mark.parametrize("name", ["c2", "c5"])
+@pytest.mark.parametrize("rows", [37, 3000])
+def test_l2_priority_of_the_table_changes_no_bit(ctx, dev, name, rows, monkeypatch):
+    # The cos/sin table is loaded with the high L2 eviction priority (tables of up to 32 MB);
+    # LOKAL_CUDA_ROPE_TABLE_KEEP=0 turns it off. A cache hint may not change a result: flat, staged and register
+    # kernels (37 rows take the flat one, 3000 the staged one), bit for bit.
+    cfg = synth.CONFIGS[name]
+    d = synth.layer_inputs(cfg, rows)
+    q1, k1 = run_qk(ctx, dev, cfg, d, rows, pos0=123)
+    monkeypatch.setenv("LOKAL_CUDA_ROPE_TABLE_KEEP", "0")
+    q0, k0 = run_qk(ctx, dev, cfg, d, rows, pos0=123)
+    monkeypatch.delenv("LOKAL_CUDA_ROPE_TABLE_KEEP")
+    synth.assert_bits_equal(q1, q0, "q with and without the L2 priority of the table")
+    synth.assert_bits_equal(k1, k0, "k with and without the L2 priority of the table")
