@@ -420,6 +420,12 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uns
                  "l"(src), "r"(bytes), "r"(mbar)
                  : "memory");
 }
+// The same copy with an L2 eviction priority for the lines it reads (createpolicy).
+__device__ __forceinline__ void bulk_copy_g2s_l2(uint32_t dst, const void* src, unsigned bytes, uint32_t mbar, unsigned long long pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(mbar), "l"(pol)
+                 : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, unsigned parity) {
     unsigned ok;
     asm volatile(

@@ -49,6 +49,7 @@ struct GatherArgs {
     unsigned max_id;     // min(vocab, 2^32) - 1: an id above it is out of range
     unsigned bulk_ids;   // ids below it have their 16-byte-aligned window inside the table (all but, at most, the last row)
     unsigned out32;      // every output row starts on a 32-byte boundary: a lane may store 32 bytes at once
+    unsigned table_keep; // table rows are fetched with the high L2 eviction priority (hot rows outlive the output rows streaming through)
     unsigned dim;
     unsigned row_bytes;
     unsigned stage_bytes;  // per warp per stage, multiple of 16
@@ -686,7 +687,8 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
             if (lane == 0) {
                 const unsigned bytes = (off + a.row_bytes + 15u) & ~15u;
                 mbar_expect_tx(bar(st), bytes + a.extra_tx);
-                bulk_copy_g2s(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st));
+                if (a.table_keep) bulk_copy_g2s_l2(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st), l2_policy_keep());
+                else bulk_copy_g2s(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st));
             }
         } else {
             // The window would run past the end of the table (last row only): plain byte loads.
@@ -961,7 +963,10 @@ __global__ void __launch_bounds__(256) gather_quant_pair_kernel(const GatherArgs
         if (l16 == 0) {
             if (m == 1u) bytes = (off + a.row_bytes + 15u) & ~15u;
             mbar_expect_tx(bar(st), m == 1u ? bytes + a.extra_tx : 0u);  // an arrival either way
-            if (m == 1u) bulk_copy_g2s(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st));
+            if (m == 1u) {
+                if (a.table_keep) bulk_copy_g2s_l2(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st), l2_policy_keep());
+                else bulk_copy_g2s(smem_addr(sptr(st)), a.table + (start - off), bytes, bar(st));
+            }
         }
         if (m == 2u) {  // the window would run past the end of the table (last row only): plain byte loads
             unsigned char* dst = sptr(st) + off;
@@ -1126,12 +1131,14 @@ __global__ void __launch_bounds__(256) gather_float_kernel(const GatherArgs a, i
         // Four source vectors per lane are loaded before the first of them is stored, so a row of up to 4 x 512 bytes
         // costs its warp one memory round trip instead of one per vector.
         constexpr unsigned kAhead = 4;
+        const unsigned long long pol = a.table_keep ? l2_policy_keep() : 0ull;
         for (unsigned e0 = lane * N; e0 < a.dim; e0 += kAhead * 32 * N) {
             uint4 v[kAhead];
 #pragma unroll
             for (unsigned j = 0; j < kAhead; j++) {
                 const unsigned e = e0 + j * 32 * N;
-                v[j] = (valid && e < a.dim) ? ld_keep(row + e) : make_uint4(0, 0, 0, 0);  // all-zero bits are 0.0 in every source type
+                // all-zero bits are 0.0 in every source type; table rows carry the high L2 eviction priority (a.table_keep)
+                v[j] = (valid && e < a.dim) ? (a.table_keep ? ld_keep_l2(row + e, pol) : ld_keep(row + e)) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (unsigned j = 0; j < kAhead; j++) {
@@ -1318,6 +1325,11 @@ int launch_gather_norm(lokal_cuda_ctx* ctx, cudaStream_t s, const void* table, i
     a.err_word = ctx->err_word;
     a.wait_limit = static_cast<unsigned>(tune_env("LOKAL_CUDA_WAIT_LIMIT", kWaitLimit));
     a.extra_tx = static_cast<unsigned>(tune_env("LOKAL_CUDA_TEST_EXTRA_TX", 0)) & ~15u;
+    // Table rows are fetched with the high L2 eviction priority: the rows of frequent tokens are asked for again and
+    // again (within a call and from one call to the next), while the output rows, eight to thirty times the bytes,
+    // stream through L2 once. Measured on the 65,536-id Zipf gather run back to back: Q8_0 to f32 42.1 -> 39.2 us,
+    // Q4_K to f32 45.4 -> 41.5 us, Q8_0 to f16 24.7 -> 23.5 us. LOKAL_CUDA_GATHER_TABLE_KEEP=0 turns it off.
+    a.table_keep = tune_env("LOKAL_CUDA_GATHER_TABLE_KEEP", 1) != 0 ? 1u : 0u;
     static const struct { int type, grid; const char* name; } kGridOf[] = {
         {LOKAL_IQ2_XXS, LOKAL_GRID_IQ2XXS, "iq2xxs"}, {LOKAL_IQ2_XS, LOKAL_GRID_IQ2XS, "iq2xs"}, {LOKAL_IQ2_S, LOKAL_GRID_IQ2S, "iq2s"},
         {LOKAL_IQ3_XXS, LOKAL_GRID_IQ3XXS, "iq3xxs"}, {LOKAL_IQ3_S, LOKAL_GRID_IQ3S, "iq3s"}, {LOKAL_IQ1_S, LOKAL_GRID_IQ1S, "iq1s"},

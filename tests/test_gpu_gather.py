@@ -387,3 +387,22 @@ def test_two_rows_per_warp_against_one(ctx, dev, oracle, ty, dim, out_dtype, mon
     got = dev.get(out)
     synth.assert_bits_equal(got[good], synth.round_to(oracle.embed_gather(table, ty, vocab, dim, ids[good]), out_dtype), "valid rows")
     assert (got[bad] == 0).all() and (got[41] == 4.0).all()
+
+
+@pytest.mark.parametrize("ty,dim", [(Q8_0, 896), (Q4_K, 1024), (21, 512)])
+def test_l2_priority_of_table_rows_changes_no_bit(ctx, dev, oracle, ty, dim, monkeypatch):
+    """Table rows are fetched with the high L2 eviction priority; LOKAL_CUDA_GATHER_TABLE_KEEP=0 turns it off. A cache
+    hint may not change a result."""
+    import lokal_b200 as L
+    if ty in L.capi.GRID_TYPES:
+        from test_oracle_iq_grids import GRIDS
+        ctx.set_iq_grids(GRIDS)
+    vocab = 1777
+    table = synth.quant_table(ty, vocab, dim, seed=3)
+    ids = synth.token_ids_zipf(vocab, 5001, seed=4).astype(np.uint32)
+    for out_dtype in (F32, F16):
+        on = gather(ctx, dev, table, ty, vocab, dim, ids, out_dtype)
+        monkeypatch.setenv("LOKAL_CUDA_GATHER_TABLE_KEEP", "0")
+        off = gather(ctx, dev, table, ty, vocab, dim, ids, out_dtype)
+        monkeypatch.delenv("LOKAL_CUDA_GATHER_TABLE_KEEP")
+        synth.assert_bits_equal(on, off, "gather with and without the L2 priority of the table rows")
