@@ -880,9 +880,11 @@ __global__ void __launch_bounds__(256) gather_quant_staged_kernel(const GatherAr
 // ---- staged kernel, two rows per warp: 16-bit output rows ----
 // A row costs its warp a fixed ~120 instructions of bookkeeping (id, window, copy, wait, pointers) whatever its
 // length, and a 16-byte store of 16-bit values covers eight elements, so a warp finishes a 1024-element row in four
-// steps: for the embedding widths in use the bookkeeping is half of all instructions, and the kernel above is bound
-// by instruction issue (measured: 157 / 260 / 392 instructions per row for Q8_0 rows of 256 / 896 / 2048 elements
-// to f16, whatever the ids). Here each half of the warp owns a row: lanes 0-15 row 2p, lanes 16-31 row 2p + 1. The
+// steps: for the embedding widths in use the bookkeeping is half of all instructions (measured: 157 / 260 / 392
+// instructions per row for Q8_0 rows of 256 / 896 / 2048 elements to f16, whatever the ids; two rows per warp:
+// 110 / 201 / 354). Narrow rows and the K-quants gain from sharing it (Q4_K, 1024 wide, to f16: 28.5 -> 27.0 us;
+// 256-wide Q8_0 rows 16.3 -> 14.2 us); 896-wide Q8_0 rows, bound by the SM's store path as much as by issue, stay
+// where they were. Here each half of the warp owns a row: lanes 0-15 row 2p, lanes 16-31 row 2p + 1. The
 // bookkeeping instructions are the same ones, executed once for both rows with per-half values (ids, windows and
 // pointers differ by lane); lanes 0 and 16 issue their rows' copies in one instruction each, both against the one
 // mbarrier of the stage (two arrivals: a lane whose row needs no copy arrives with zero bytes, so every issued stage
